@@ -1,0 +1,140 @@
+/* b200_layer_ops.h -- C ABI of libb200_layer_ops.so: the fused per-token layer kernels (RMSNorm with optional
+ * residual add, per-head q/k norm + NeoX RoPE, SwiGLU, Q8_0 / Q4_0 embedding gather) for NVIDIA B200 (sm_100a).
+ *
+ * Part 1 re-declares, with identical names, argument order and meaning, the launchers the reference engine's
+ * forward pass calls (src/gpu_ops.h:16-29): a build of the reference's qwen_model.cpp that includes its own
+ * gpu_ops.h through the hip/ shim headers next to this file links against this library unchanged. hipError_t is
+ * cudaError_t and hipStream_t is cudaStream_t there, as here.
+ * Part 2 declares what the reference does elsewhere than in a launcher of its own (bf16 rows, the q/k norm + RoPE it
+ * runs inside attn_prep, the embedding decode it runs in a host loop, the FP16 component kernels it launches by
+ * name) and is additive.
+ *
+ * Conventions, all from the reference (src/gpu_ops.h:1-2, src/gpu_ops.cpp:66-86): every pointer is device memory
+ * owned by the caller unless a parameter says "host"; launches are asynchronous on `stream` and never synchronise;
+ * no launcher allocates; errors come back as the return value (cudaErrorInvalidDeviceFunction before gpu_ops_init,
+ * cudaErrorInvalidValue for arguments the contract forbids, otherwise the launch status), nothing is thrown or
+ * printed.
+ */
+#ifndef B200_LAYER_OPS_H
+#define B200_LAYER_OPS_H
+
+#include <cuda_runtime_api.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------------ Part 1 */
+
+/* Activation side outputs a producer kernel can write in the same launch (layout of the reference's
+ * struct qmatvec_q8, src/qmatvec.h:70-83; skipped when the reference's own header was included first). */
+#ifndef QMATVEC_H
+typedef struct qmatvec_q8 {
+    int8_t* q0;    /* Q8_0 values [K] */
+    float* d0;     /* Q8_0 scales [K / 32], fp16-rounded */
+    int8_t* qK;    /* Q8_K values [K] */
+    float* dK;     /* Q8_K scales [K / 256] */
+    int32_t* bsK;  /* Q8_K sums of every 16 values [K / 16] */
+    int32_t* s0;   /* per 32 values: fp16(d * sum of the block's q) as float bits */
+    int max_k;
+    uint16_t* xh;  /* optional: the values rounded to bf16 (xh_bf16) or fp16 [K] */
+    int xh_bf16;
+} qmatvec_q8;
+#endif
+
+/* src/gpu_ops.h:16-18, src/gpu_ops.cpp:19-64. The kernels are linked into the library (the counterpart of the
+ * reference's embedded code objects), so co_path is accepted and ignored; returns 0 when the current device can run
+ * them, -1 otherwise; idempotent. gpu_ops_free forgets the initialisation. */
+int gpu_ops_init(const char* co_path);
+void gpu_ops_free(void);
+
+/* src/gpu_ops.h:20-25. T rows of n fp32 values: x_out = x_in + add, y = RMSNorm(x_out) * w (w NULL: no gamma).
+ * add NULL: x_out is not written and may be anything, y = RMSNorm(x_in) * w, and y may be x_in. x_out must not be
+ * x_in when add is set. q8 non-NULL: the rows of y are also written into it as one flattened [T * n] vector
+ * (n % 256 == 0 and T * n <= q8->max_k, else cudaErrorInvalidValue). */
+cudaError_t gpu_add_rmsnorm(const float* x_in, const float* add, float* x_out, const float* w, float* y, int n, int T,
+                            float eps, const qmatvec_q8* q8, cudaStream_t stream);
+
+/* src/gpu_ops.h:27-29. out = SiLU(g) * u over n fp32 values; q8 non-NULL: also quantised into it
+ * (n % 32 == 0 and n <= q8->max_k, else cudaErrorInvalidValue). */
+cudaError_t gpu_swiglu(const float* g, const float* u, float* out, int n, const qmatvec_q8* q8, cudaStream_t stream);
+
+/* ------------------------------------------------------------------------------------------------ Part 2 */
+
+/* bf16 storage (uint16_t bit patterns), fp32 arithmetic, one round-to-nearest-even per stored value (the rule of
+ * src/q8_device.h:39-40). The norm is taken of x_out as stored. Gammas stay fp32 as in the reference's models.
+ * T and n are 64-bit / int as the tensors of a long prefill need. */
+cudaError_t gpu_add_rmsnorm_bf16(const uint16_t* x_in, const uint16_t* add, uint16_t* x_out, const float* w,
+                                 uint16_t* y, int n, long long T, float eps, cudaStream_t stream);
+cudaError_t gpu_swiglu_bf16(const uint16_t* g, const uint16_t* u, uint16_t* out, long long n, cudaStream_t stream);
+/* gpu_add_rmsnorm / gpu_swiglu without the int limits on T and n (no q8) */
+cudaError_t gpu_add_rmsnorm_f32(const float* x_in, const float* add, float* x_out, const float* w, float* y, int n,
+                                long long T, float eps, cudaStream_t stream);
+cudaError_t gpu_swiglu_f32(const float* g, const float* u, float* out, long long n, cudaStream_t stream);
+
+/* SwiGLU over rows whose gate and up halves sit at strides (in values), e.g. the experts' fused [gate | up] rows:
+ * out [rows][h] = SiLU(gate[r * gate_stride + i]) * up[r * up_stride + i] (argument order of the reference's
+ * gpu_geglu, src/gpu_ops.h:66-67, with SiLU as the activation). */
+cudaError_t gpu_swiglu_rows(const float* gate, const float* up, float* out, long long rows, int h,
+                            long long gate_stride, long long up_stride, cudaStream_t stream);
+cudaError_t gpu_swiglu_rows_bf16(const uint16_t* gate, const uint16_t* up, uint16_t* out, long long rows, int h,
+                                 long long gate_stride, long long up_stride, cudaStream_t stream);
+
+/* Per-head q/k RMSNorm followed by NeoX RoPE: the norm_rope step of the reference's attn_prep kernels
+ * (src/attention.hip:212-236, 266-283; arguments named as in attention_forward_opts, src/attention.h:90-94) without
+ * the KV-cache write. For each of T tokens: the n_q heads of qfull (head stride 2 * head_dim when gated, else
+ * head_dim) go to q_out [T][n_q * head_dim], the n_kv heads of k to k_out [T][n_kv * head_dim]. Each head is
+ * RMS-normalised with q_norm / k_norm (NULL: no gamma; qk_norm 0: no normalisation at all), then pairs
+ * (i, i + n_rot / 2), i < rot_pairs, are rotated by pos * freq_base^(-2 i / n_rot) (/ freq_factors[i] if given);
+ * rot_pairs <= 0 means n_rot / 2; n_rot 0 means no rotation. Token t is at positions[t], or at pos0 + t when
+ * positions is NULL. Angles are formed and evaluated in double precision. In place (q_out == qfull without gated,
+ * k_out == k) is allowed. n_kv may be 0 with k, k_out NULL (and likewise n_q). */
+cudaError_t gpu_qk_norm_rope(const float* qfull, const float* k, const float* q_norm, const float* k_norm,
+                             float* q_out, float* k_out, int n_q, int n_kv, int head_dim, int n_rot, int rot_pairs,
+                             const int* positions, int pos0, long long T, float freq_base, float eps, int gated,
+                             int qk_norm, const float* freq_factors, cudaStream_t stream);
+cudaError_t gpu_qk_norm_rope_bf16(const uint16_t* qfull, const uint16_t* k, const float* q_norm, const float* k_norm,
+                                  uint16_t* q_out, uint16_t* k_out, int n_q, int n_kv, int head_dim, int n_rot,
+                                  int rot_pairs, const int* positions, int pos0, long long T, float freq_base,
+                                  float eps, int gated, int qk_norm, const float* freq_factors, cudaStream_t stream);
+
+/* Token-embedding gather + dequantisation: out row t = decode(table row tokens[t]) * scale, the loop of
+ * src/qwen_model.cpp:980-986 (scale: embd_scale of :1409; pass 1 for none). type: 8 (Q8_0) or 2 (Q4_0), the ggml
+ * ids of src/quant_types.h:19-27; row_bytes as qt_row_size(type, E) or larger (a row stride); E % 32 == 0.
+ * tokens are device memory. bad_row: device int the caller sets to INT_MAX beforehand; an id outside [0, vocab)
+ * zero-fills its output row and lowers *bad_row to that row's index (the reference returns an error for such an id
+ * before decoding anything; read the flag after the stream is synchronised). Bit-exact. */
+cudaError_t gpu_embed_rows(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens, float* out,
+                           int E, long long T, float scale, int* bad_row, cudaStream_t stream);
+cudaError_t gpu_embed_rows_bf16(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens,
+                                uint16_t* out, int E, long long T, float scale, int* bad_row, cudaStream_t stream);
+/* The same with the ids in host memory, as the reference's forward() receives them: the ids are range-checked on the
+ * host first (cudaErrorInvalidValue and nothing launched if one is out of range, as src/qwen_model.cpp:981), then
+ * copied to tokens_dev (device scratch for T ids, caller-owned) on `stream`, and the gather is launched.
+ * tokens_host must stay valid until that copy has run (pinned memory makes it asynchronous). */
+cudaError_t gpu_embed_rows_host_ids(int type, const void* table, size_t row_bytes, int vocab,
+                                    const int32_t* tokens_host, int32_t* tokens_dev, float* out, int E, long long T,
+                                    float scale, int* bad_row, cudaStream_t stream);
+
+/* FP16 component kernels of the reference (src/layernorm.hip:15-45, src/rope_embedding.hip:18-37), which its tests
+ * launch by name with one 32-thread block per row; these launchers run better-shaped kernels with the same math.
+ * gpu_rmsnorm_f16: y = x * rsqrt(mean(x^2) + eps) * gamma (gamma fp16, NULL: none), fp32 accumulation, one rounding.
+ * gpu_rope_rotate_half_f16: y[r][i] = x[r][i] c - x[r][i+H] s, y[r][i+H] = x[r][i+H] c + x[r][i] s with fp32 tables
+ * ctab / stab [n_rows][half_dim]; y may be x. */
+cudaError_t gpu_rmsnorm_f16(const uint16_t* x, const uint16_t* gamma, uint16_t* y, int n_tokens, int n_embd, float eps,
+                            cudaStream_t stream);
+cudaError_t gpu_rope_rotate_half_f16(const uint16_t* x, const float* ctab, const float* stab, uint16_t* y, int n_rows,
+                                     int half_dim, cudaStream_t stream);
+
+/* Number of kernel launches this library has issued since it was loaded (all launchers, all threads) */
+unsigned long long b200_launch_count(void);
+/* "sm_100a" and the like: the architecture the kernels were compiled for */
+const char* b200_build_arch(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200_LAYER_OPS_H */

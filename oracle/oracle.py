@@ -1,0 +1,249 @@
+"""numpy front end of the CPU checkers. TEST INFRASTRUCTURE ONLY: imported by tests/, the smoke check and the
+benchmark's CPU baseline, never by the product package.
+
+``port``  = oracle/liboracle.so, the restatement of the reference's arithmetic (oracle_ops.c).
+``ref``   = oracle/_ref/libref_cpu.so, the reference's own qwen_ops.cpp / quant_types.cpp compiled from its source
+            tree (present when that tree was available at build time; the built file travels with the repository).
+Both export the row-parallel cpu_* runner of cpu_rows.cpp.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PORT_PATH = os.path.join(HERE, "liboracle.so")
+REF_PATH = os.path.join(HERE, "_ref", "libref_cpu.so")
+
+Q4_0, Q8_0 = 2, 8
+
+_p, _i, _ll, _f, _sz = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_size_t
+
+
+def build():
+    """Compiles liboracle.so and, when the reference's sources are present, _ref/libref_cpu.so."""
+    subprocess.run(["make", "-s", "-C", HERE], check=True, stdout=subprocess.DEVNULL)
+
+
+_CPU_SIGS = {
+    "cpu_hardware_threads": (_i, []),
+    "cpu_is_reference": (_i, []),
+    "cpu_add_rmsnorm": (None, [_p, _p, _p, _p, _p, _i, _i, _f, _i]),
+    "cpu_swiglu": (None, [_p, _p, _p, _ll, _i]),
+    "cpu_qk_norm_rope": (None, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _i, _i, _f, _f, _i, _i, _i]),
+    "cpu_embed_rows": (_i, [_i, _p, _sz, _i, _p, _p, _i, _i, _f, _i]),
+}
+_PORT_SIGS = {
+    "orc_fp16_to_fp32": (_f, [C.c_uint16]),
+    "orc_fp32_to_fp16": (C.c_uint16, [_f]),
+    "orc_fp32_to_bf16": (C.c_uint16, [_f]),
+    "orc_rmsnorm": (None, [_p, _p, _p, _i, _f]),
+    "orc_add_rmsnorm": (None, [_p, _p, _p, _p, _p, _i, _i, _f]),
+    "orc_add_rmsnorm_bf16": (None, [_p, _p, _p, _p, _p, _i, _i, _f]),
+    "orc_silu": (_f, [_f]),
+    "orc_swiglu": (None, [_p, _p, _p, _ll]),
+    "orc_swiglu_bf16": (None, [_p, _p, _p, _ll]),
+    "orc_swiglu_strided": (None, [_p, _p, _p, _i, _i, _ll, _ll]),
+    "orc_rope_neox": (None, [_p, _i, _i, _f]),
+    "orc_rope_neox_ex": (None, [_p, _i, _i, _i, _f, _p]),
+    "orc_qk_norm_rope": (None, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _f, _f, _i, _p, _i]),
+    "orc_qk_norm_rope_bf16": (None, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _f, _f, _i, _p, _i]),
+    "orc_row_size": (_sz, [_i, _ll]),
+    "orc_to_float": (_i, [_i, _p, _p, _ll]),
+    "orc_embed_rows": (_i, [_i, _p, _sz, _i, _p, _p, _i, _i, _f]),
+    "orc_embed_rows_bf16": (_i, [_i, _p, _sz, _i, _p, _p, _i, _i, _f]),
+    "orc_rmsnorm_f16": (None, [_p, _p, _p, _i, _i, _f]),
+    "orc_rope_tables": (None, [_p, _i, _i, _f, _p, _p]),
+    "orc_rope_rotate_half_f16": (None, [_p, _p, _p, _p, _i, _i]),
+    "orc_lcg": (_f, [C.POINTER(C.c_uint32), _f, _f]),
+    "orc_quantize_q8": (None, [_p, _ll, _p, _p, _p, _p, _p, _p, _p, _i]),
+}
+_REF_SIGS = {
+    "ref_qwen_rmsnorm": (None, [_p, _p, _p, _i, _f]),
+    "ref_qwen_rope_neox": (None, [_p, _i, _i, _f]),
+    "ref_qwen_silu": (_f, [_f]),
+    "qt_to_float": (_i, [_i, _p, _p, C.c_int64]),
+    "qt_row_size": (_sz, [_i, C.c_int64]),
+    "qt_fp16_to_fp32": (_f, [C.c_uint16]),
+    "qt_bf16_to_fp32": (_f, [C.c_uint16]),
+}
+
+
+def _bind(lib, sigs):
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+_port = _ref = None
+
+
+def port():
+    global _port
+    if _port is None:
+        if not os.path.exists(PORT_PATH):
+            build()
+        _port = _bind(_bind(C.CDLL(PORT_PATH), _PORT_SIGS), _CPU_SIGS)
+    return _port
+
+
+def have_ref():
+    return os.path.exists(REF_PATH)
+
+
+def ref():
+    global _ref
+    if _ref is None:
+        if not have_ref():
+            raise FileNotFoundError(REF_PATH)
+        _ref = _bind(_bind(C.CDLL(REF_PATH), _REF_SIGS), _CPU_SIGS)
+    return _ref
+
+
+def ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return None if a is None else np.ascontiguousarray(a, dtype=dt)
+
+
+# ---------------------------------------------------------------- conversions (vectorised numpy equivalents)
+
+def bf16_to_f32(u16):
+    return (np.asarray(u16, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(x):
+    """Round to nearest even on the bit pattern (src/q8_device.h:39-40)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def f16_to_f32(u16):
+    return np.asarray(u16, dtype=np.uint16).view(np.float16).astype(np.float32)
+
+
+def f32_to_f16(x):
+    return np.asarray(x, dtype=np.float32).astype(np.float16).view(np.uint16)
+
+
+# ---------------------------------------------------------------- ops on numpy arrays (restatement)
+
+def add_rmsnorm(x_in, add, w, eps):
+    """fp32 [T][n] -> (x_out or None, y)."""
+    x_in = _c(x_in, np.float32)
+    T, n = x_in.shape
+    add = _c(add, np.float32)
+    w = _c(w, np.float32)
+    y = np.empty_like(x_in)
+    x_out = np.empty_like(x_in) if add is not None else None
+    port().orc_add_rmsnorm(ptr(x_in), ptr(add), ptr(x_out), ptr(w), ptr(y), n, T, eps)
+    return x_out, y
+
+
+def add_rmsnorm_bf16(x_in, add, w, eps):
+    x_in = _c(x_in, np.uint16)
+    T, n = x_in.shape
+    add = _c(add, np.uint16)
+    w = _c(w, np.float32)
+    y = np.empty_like(x_in)
+    x_out = np.empty_like(x_in) if add is not None else None
+    port().orc_add_rmsnorm_bf16(ptr(x_in), ptr(add), ptr(x_out), ptr(w), ptr(y), n, T, eps)
+    return x_out, y
+
+
+def swiglu(g, u):
+    g, u = _c(g, np.float32), _c(u, np.float32)
+    out = np.empty_like(g)
+    port().orc_swiglu(ptr(g), ptr(u), ptr(out), g.size)
+    return out
+
+
+def swiglu_bf16(g, u):
+    g, u = _c(g, np.uint16), _c(u, np.uint16)
+    out = np.empty_like(g)
+    port().orc_swiglu_bf16(ptr(g), ptr(u), ptr(out), g.size)
+    return out
+
+
+def qk_norm_rope(qfull, k, q_norm, k_norm, n_q, n_kv, D, n_rot, rot_pairs, positions, pos0, base, eps, gated=0,
+                 ff=None, do_norm=1, bf16=False):
+    """qfull [T][n_q * (2D if gated else D)], k [T][n_kv * D] (fp32, or uint16 bf16 bits) -> (q_out, k_out)."""
+    dt = np.uint16 if bf16 else np.float32
+    qfull, k = _c(qfull, dt), _c(k, dt)
+    T = qfull.shape[0] if qfull is not None else k.shape[0]
+    q_out = np.empty((T, n_q * D), dtype=dt)
+    k_out = np.empty((T, n_kv * D), dtype=dt)
+    positions = _c(positions, np.int32)
+    q_norm, k_norm, ff = _c(q_norm, np.float32), _c(k_norm, np.float32), _c(ff, np.float32)
+    fn = port().orc_qk_norm_rope_bf16 if bf16 else port().orc_qk_norm_rope
+    fn(ptr(qfull), ptr(k), ptr(q_norm), ptr(k_norm), ptr(q_out), ptr(k_out), n_q, n_kv, D, n_rot, rot_pairs,
+       ptr(positions), pos0, T, base, eps, gated, ptr(ff), do_norm)
+    return q_out, k_out
+
+
+def embed_rows(qtype, table, row_bytes, vocab, tokens, E, scale=1.0, bf16=False):
+    """table: uint8 array. Returns (status, out [T][E])."""
+    tokens = _c(tokens, np.int32)
+    T = tokens.size
+    out = np.zeros((T, E), dtype=np.uint16 if bf16 else np.float32)
+    fn = port().orc_embed_rows_bf16 if bf16 else port().orc_embed_rows
+    st = fn(qtype, ptr(table), row_bytes, vocab, ptr(tokens), ptr(out), E, T, scale)
+    return st, out
+
+
+def rmsnorm_f16(x, gamma, eps):
+    x = _c(x, np.uint16)
+    T, n = x.shape
+    gamma = _c(gamma, np.uint16)
+    y = np.empty_like(x)
+    port().orc_rmsnorm_f16(ptr(x), ptr(gamma), ptr(y), T, n, eps)
+    return y
+
+
+def rope_tables(positions, dim, theta):
+    positions = _c(positions, np.int32)
+    R, H = positions.size, dim // 2
+    c, s = np.empty((R, H), np.float32), np.empty((R, H), np.float32)
+    port().orc_rope_tables(ptr(positions), R, dim, theta, ptr(c), ptr(s))
+    return c, s
+
+
+def rope_rotate_half_f16(x, ctab, stab):
+    x = _c(x, np.uint16)
+    R, dim = x.shape
+    y = np.empty_like(x)
+    port().orc_rope_rotate_half_f16(ptr(x), ptr(_c(ctab, np.float32)), ptr(_c(stab, np.float32)), ptr(y), R, dim // 2)
+    return y
+
+
+def quantize_q8(x, xh=None, int8=True):
+    """Side outputs of a finished vector x (fp32, size % 256 == 0). Returns a dict of arrays."""
+    x = _c(x, np.float32).ravel()
+    K = x.size
+    o = {}
+    if int8:
+        o.update(q0=np.zeros(K, np.int8), d0=np.zeros(K // 32, np.float32), s0=np.zeros(K // 32, np.int32),
+                 qK=np.zeros(K, np.int8), dK=np.zeros(K // 256, np.float32), bsK=np.zeros(K // 16, np.int32))
+    if xh:
+        o["xh"] = np.zeros(K, np.uint16)
+    port().orc_quantize_q8(ptr(x), K, ptr(o.get("q0")), ptr(o.get("d0")), ptr(o.get("s0")), ptr(o.get("qK")),
+                           ptr(o.get("dK")), ptr(o.get("bsK")), ptr(o.get("xh")), 1 if xh == "bf16" else 0)
+    return o
+
+
+class Lcg:
+    """The reference tests' generator (tests/layernorm_verify.cpp:29-33)."""
+
+    def __init__(self, seed):
+        self.state = C.c_uint32(seed)
+
+    def rnd(self, lo, hi):
+        return port().orc_lcg(C.byref(self.state), lo, hi)
+
+    def next_u32(self):
+        self.state = C.c_uint32((self.state.value * 1664525 + 1013904223) & 0xFFFFFFFF)
+        return self.state.value

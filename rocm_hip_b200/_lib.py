@@ -1,0 +1,68 @@
+"""ctypes binding of libb200_layer_ops.so, the C-ABI library declared in include/b200_layer_ops.h.
+
+The library is the product; this module only declares its entry points to ctypes. There is no fallback: if the
+shared object has not been built (``python -c "import __graft_entry__ as g; g.build()"`` or
+``make -C rocm_hip_b200/csrc``) loading raises, and so does every op.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200_layer_ops.so")
+
+cudaSuccess = 0
+cudaErrorInvalidValue = 1
+cudaErrorInvalidDeviceFunction = 98
+
+
+class qmatvec_q8(C.Structure):
+    """Layout of the reference's struct qmatvec_q8 (src/qmatvec.h:70-83): device pointers of the side outputs."""
+    _fields_ = [
+        ("q0", C.c_void_p), ("d0", C.c_void_p), ("qK", C.c_void_p), ("dK", C.c_void_p), ("bsK", C.c_void_p),
+        ("s0", C.c_void_p), ("max_k", C.c_int), ("xh", C.c_void_p), ("xh_bf16", C.c_int),
+    ]
+
+
+_p, _i, _ll, _f, _sz = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); every symbol include/b200_layer_ops.h declares
+SIGNATURES = {
+    "gpu_ops_init": (_i, [C.c_char_p]),
+    "gpu_ops_free": (None, []),
+    "gpu_add_rmsnorm": (_i, [_p, _p, _p, _p, _p, _i, _i, _f, C.POINTER(qmatvec_q8), _p]),
+    "gpu_swiglu": (_i, [_p, _p, _p, _i, C.POINTER(qmatvec_q8), _p]),
+    "gpu_add_rmsnorm_bf16": (_i, [_p, _p, _p, _p, _p, _i, _ll, _f, _p]),
+    "gpu_add_rmsnorm_f32": (_i, [_p, _p, _p, _p, _p, _i, _ll, _f, _p]),
+    "gpu_swiglu_bf16": (_i, [_p, _p, _p, _ll, _p]),
+    "gpu_swiglu_f32": (_i, [_p, _p, _p, _ll, _p]),
+    "gpu_swiglu_rows": (_i, [_p, _p, _p, _ll, _i, _ll, _ll, _p]),
+    "gpu_swiglu_rows_bf16": (_i, [_p, _p, _p, _ll, _i, _ll, _ll, _p]),
+    "gpu_qk_norm_rope": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
+    "gpu_qk_norm_rope_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
+    "gpu_embed_rows": (_i, [_i, _p, _sz, _i, _p, _p, _i, _ll, _f, _p, _p]),
+    "gpu_embed_rows_bf16": (_i, [_i, _p, _sz, _i, _p, _p, _i, _ll, _f, _p, _p]),
+    "gpu_embed_rows_host_ids": (_i, [_i, _p, _sz, _i, _p, _p, _p, _i, _ll, _f, _p, _p]),
+    "gpu_rmsnorm_f16": (_i, [_p, _p, _p, _i, _i, _f, _p]),
+    "gpu_rope_rotate_half_f16": (_i, [_p, _p, _p, _p, _i, _i, _p]),
+    "b200_launch_count": (C.c_ulonglong, []),
+    "b200_build_arch": (C.c_char_p, []),
+}
+
+_lib = None
+
+
+def load():
+    """Loads the library once and returns the ctypes handle. Raises if it is missing or lacks a declared symbol."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is not built: run `make -C rocm_hip_b200/csrc` (needs nvcc); there is no CPU fallback")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export it
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

@@ -1,0 +1,168 @@
+// common.cuh -- shared device helpers for the sm_100a layer-op kernels: 16-byte streaming loads / stores, storage
+// type traits (fp32, bf16, fp16 rows computed in fp32), and the fixed-order reductions.
+//
+// Rows are streamed once, so activation loads and stores bypass L1 allocation (the gammas, which every row
+// re-reads, go through the read-only path and stay cached). Reductions always run in the same order for a given
+// row width and storage type, independent of how many rows a launch holds or how the grid is shaped, so a row
+// gives the same bits whether it is processed alone, in a batch, or on another GPU of a row-sharded run.
+
+#ifndef B200_COMMON_CUH
+#define B200_COMMON_CUH
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+// ---------------------------------------------------------------- 16-byte global access
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_stream(void* p, const uint4& v) {
+    asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---------------------------------------------------------------- storage types
+
+// bf16 <-> fp32. Widening is exact; narrowing is round-to-nearest-even, the same rule as the integer formula
+// (u + 0x7fff + ((u >> 16) & 1)) >> 16 of the reference's half_bits (src/q8_device.h:39-40) for every finite value.
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint16_t to_bf16_bits(float v) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+template <typename T>
+struct Io;
+
+template <>
+struct Io<float> {
+    static constexpr int VE = 4;  // values per 16-byte vector
+    __device__ static __forceinline__ void unpack(const uint4& r, float* v) {
+        v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y);
+        v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+    }
+    __device__ static __forceinline__ uint4 pack(const float* v) {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+    }
+    __device__ static __forceinline__ float load1(const float* p) { return *p; }
+    __device__ static __forceinline__ void store1(float* p, float v) { *p = v; }
+    // value as it reads back after being stored
+    __device__ static __forceinline__ float round_trip(float v) { return v; }
+};
+
+template <>
+struct Io<__nv_bfloat16> {
+    static constexpr int VE = 8;
+    __device__ static __forceinline__ void unpack(const uint4& r, float* v) {
+        v[0] = bf16_lo(r.x); v[1] = bf16_hi(r.x); v[2] = bf16_lo(r.y); v[3] = bf16_hi(r.y);
+        v[4] = bf16_lo(r.z); v[5] = bf16_hi(r.z); v[6] = bf16_lo(r.w); v[7] = bf16_hi(r.w);
+    }
+    __device__ static __forceinline__ uint4 pack(const float* v) {
+        return make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+    }
+    __device__ static __forceinline__ float load1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    __device__ static __forceinline__ void store1(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+    __device__ static __forceinline__ float round_trip(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+template <>
+struct Io<__half> {
+    static constexpr int VE = 8;
+    __device__ static __forceinline__ void unpack(const uint4& r, float* v) {
+        const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    __device__ static __forceinline__ uint4 pack(const float* v) {
+        return make_uint4(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]), pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
+    }
+    __device__ static __forceinline__ float load1(const __half* p) { return __half2float(*p); }
+    __device__ static __forceinline__ void store1(__half* p, float v) { *p = __float2half_rn(v); }
+    __device__ static __forceinline__ float round_trip(float v) { return __half2float(__float2half_rn(v)); }
+};
+
+// gamma values for one vector of VE consecutive columns starting at column c (fp32 or fp16 gammas; NULL: all 1)
+template <int VE, typename WT>
+__device__ __forceinline__ void load_gamma(const WT* w, int c, float* g) {
+    if (!w) {
+#pragma unroll
+        for (int i = 0; i < VE; ++i) g[i] = 1.0f;
+        return;
+    }
+    if constexpr (sizeof(WT) == 4) {
+#pragma unroll
+        for (int i = 0; i < VE; i += 4) {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(w + c + i));
+            g[i] = f.x; g[i + 1] = f.y; g[i + 2] = f.z; g[i + 3] = f.w;
+        }
+    } else {
+        static_assert(VE == 8, "16-bit gammas come with 16-bit rows");
+        const uint4 r = __ldg(reinterpret_cast<const uint4*>(w + c));
+        Io<WT>::unpack(r, g);
+    }
+}
+
+template <typename WT>
+__device__ __forceinline__ float gamma1(const WT* w, int c) {
+    if (!w) return 1.0f;
+    if constexpr (sizeof(WT) == 4) return __ldg(w + c);
+    else return Io<WT>::load1(w + c);
+}
+
+// ---------------------------------------------------------------- reductions
+
+// Sum over the `width` lanes (a power of two <= 32) of an aligned lane group; every lane of the group gets the total.
+// All 32 lanes of the warp must call it.
+__device__ __forceinline__ float group_sum(float v, int width) {
+    for (int off = width >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// Sum over all threads of the CTA (blockDim.x a multiple of 32, at most 1024). part: 32 floats of shared memory
+// that no other use touches between two calls with the same buffer.
+__device__ __forceinline__ float cta_sum(float v, float* part) {
+    v = group_sum(v, 32);
+    const int nw = blockDim.x >> 5;
+    if (nw == 1) return v;
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float tot = 0.0f;
+    for (int k = 0; k < nw; ++k) tot += part[k];
+    return tot;
+}
+
+// 1 / sqrt(mean + eps) with correctly rounded square root and division (one per row: the cost is nothing)
+__device__ __forceinline__ float inv_rms(float sum_sq, int n, float eps) {
+    return __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)n), eps)));
+}
+
+}  // namespace b200
+
+#endif  // B200_COMMON_CUH

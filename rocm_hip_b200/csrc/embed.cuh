@@ -1,0 +1,116 @@
+// embed.cuh -- token-embedding gather and dequantisation from a GGUF Q8_0 / Q4_0 table resident in HBM, the B200
+// kernel behind gpu_embed_rows. It replaces the reference's single-threaded host loop (src/qwen_model.cpp:980-986:
+// range check, then qt_to_float of row tokens[t] into output row t) and restates its block decoders bit for bit
+// (src/quant_types.cpp:181-189 Q8_0: y = qs[j] * d; :78-91 Q4_0: value j from the low nibble of qs[j], value j + 16
+// from the high nibble, each (nibble - 8) * d; d widened exactly from fp16). One fp32 multiply per value, nothing
+// fused with it; an embedding scale other than 1 is a second, separately rounded multiply (src/qwen_model.cpp:1409).
+//
+// Layout: table rows of E / 32 blocks (34 or 18 bytes each), row t at table + t * row_bytes; inside a row the fp16
+// scale and the payload are only 2-byte aligned. A warp takes one token at a time: it copies the row's bytes into its
+// own shared-memory slice (16-byte loads when the table base and row_bytes allow, else 2-byte loads), then decodes
+// from shared memory so that every global store is a full 16-byte vector and a warp writes 512 contiguous bytes.
+// Traffic per token: 4 (id) + row_bytes + E * s_out, the algorithmic minimum.
+// An id outside [0, vocab) never touches the table: its output row is zero-filled and the smallest offending row
+// index is recorded in *bad_row (initialised to INT_MAX by the launcher's caller) for the host to turn into an error.
+
+#ifndef B200_EMBED_CUH
+#define B200_EMBED_CUH
+
+#include "common.cuh"
+
+namespace b200 {
+
+#define B200_QT_Q4_0 2
+#define B200_QT_Q8_0 8
+
+// Rows are staged in chunks of at most EMBED_CHUNK_BLOCKS blocks (a multiple of 8 so that chunk starts keep the
+// row's 16-byte alignment: 8 * 34 and 8 * 18 are multiples of 16).
+#define EMBED_CHUNK_BLOCKS 160
+#define EMBED_WARPS 8
+
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// One value of a block from its byte (Q8_0) or nibble (Q4_0), times the block scale, times the embedding scale
+__device__ __forceinline__ float deq(int q, float d, float scale) {
+    float y = __fmul_rn((float)q, d);
+    if (scale != 1.0f) y = __fmul_rn(y, scale);
+    return y;
+}
+
+template <typename OUT, int TYPE>
+__global__ void __launch_bounds__(EMBED_WARPS * 32)
+k_embed_rows(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out, int E, long long T,
+             float scale, int* bad_row, int vec_ok) {
+    constexpr int BB = TYPE == B200_QT_Q8_0 ? 34 : 18;            // bytes per block
+    constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;                 // values per lane and step: one 16-byte store
+    constexpr int LPB = 32 / VPL;                                 // lanes per block
+    constexpr int BPS = 32 / LPB;                                 // blocks per warp step
+    __shared__ __align__(16) uint8_t stage[EMBED_WARPS][EMBED_CHUNK_BLOCKS * BB];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    uint8_t* sm = stage[wid];
+    const int nb = E / 32;
+    const long long warp0 = (long long)blockIdx.x * EMBED_WARPS + wid, nwarps = (long long)gridDim.x * EMBED_WARPS;
+
+    for (long long t = warp0; t < T; t += nwarps) {
+        const int tok = tokens[t];
+        OUT* orow = out + (size_t)t * E;
+        if (tok < 0 || tok >= vocab) {
+            if (lane == 0) atomicMin(bad_row, (int)(t < 0x7fffffff ? t : 0x7ffffffe));
+            for (int c = lane * VPL; c < E; c += 32 * VPL) st_stream(orow + c, make_uint4(0, 0, 0, 0));
+            continue;
+        }
+        const uint8_t* src = table + (size_t)tok * row_bytes;
+        for (int b0 = 0; b0 < nb; b0 += EMBED_CHUNK_BLOCKS) {
+            const int cb = min(EMBED_CHUNK_BLOCKS, nb - b0), bytes = cb * BB;
+            const uint8_t* s = src + (size_t)b0 * BB;
+            __syncwarp();  // the previous chunk has been decoded
+            if (vec_ok) {
+                const int nv = bytes >> 4;
+                for (int i = lane; i < nv; i += 32) reinterpret_cast<uint4*>(sm)[i] = ld_stream(s + (size_t)i * 16);
+                for (int i = (nv << 4) + lane * 2; i < bytes; i += 64)  // a chunk that is not a whole number of vectors
+                    *reinterpret_cast<uint16_t*>(sm + i) = *reinterpret_cast<const uint16_t*>(s + i);
+            } else {
+                for (int i = lane * 2; i < bytes; i += 64)
+                    *reinterpret_cast<uint16_t*>(sm + i) = *reinterpret_cast<const uint16_t*>(s + i);
+            }
+            __syncwarp();
+            for (int bs = 0; bs < cb; bs += BPS) {
+                const int b = bs + lane / LPB, sub = lane % LPB;
+                if (b < cb) {
+                    const uint8_t* blk = sm + b * BB;
+                    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(blk));
+                    float y[VPL];
+                    if constexpr (TYPE == B200_QT_Q8_0) {
+#pragma unroll
+                        for (int k = 0; k < VPL; k += 2) {
+                            const uint16_t two = *reinterpret_cast<const uint16_t*>(blk + 2 + sub * VPL + k);
+                            y[k] = deq((int)(int8_t)(two & 0xff), d, scale);
+                            y[k + 1] = deq((int)(int8_t)(two >> 8), d, scale);
+                        }
+                    } else {
+                        // values [sub * VPL, sub * VPL + VPL) of the block: the first 16 are low nibbles, the rest high
+                        const int v0 = sub * VPL, byte0 = v0 & 15, shift = v0 < 16 ? 0 : 4;
+#pragma unroll
+                        for (int k = 0; k < VPL; k += 2) {
+                            const uint16_t two = *reinterpret_cast<const uint16_t*>(blk + 2 + byte0 + k);
+                            y[k] = deq((int)(((two & 0xff) >> shift) & 15) - 8, d, scale);
+                            y[k + 1] = deq((int)(((two >> 8) >> shift) & 15) - 8, d, scale);
+                        }
+                    }
+                    OUT* o = orow + (size_t)(b0 + b) * 32 + sub * VPL;
+                    if constexpr (sizeof(OUT) == 4) {
+                        st_stream(o, make_uint4(__float_as_uint(y[0]), __float_as_uint(y[1]), __float_as_uint(y[2]),
+                                                __float_as_uint(y[3])));
+                    } else {
+                        st_stream(o, make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]),
+                                                pack_bf16(y[6], y[7])));
+                    }
+                }
+            }
+        }
+    }
+}
+
+}  // namespace b200
+
+#endif  // B200_EMBED_CUH

@@ -1,0 +1,388 @@
+// layer_ops.cu -- host launchers and the C ABI of libb200_layer_ops.so (include/b200_layer_ops.h). Argument checks
+// and error codes follow the reference's launchers (src/gpu_ops.cpp:66-86); the launch shapes are B200's own: the
+// kernel variant and the threads per row are chosen from the row width and storage type only, the grid from the row
+// count and the SM count.
+
+#include "b200_layer_ops.h"
+
+#include <limits.h>
+#include <math.h>
+#include <string.h>
+
+#include <atomic>
+#include <cmath>
+
+#include "embed.cuh"
+#include "q8_side.cuh"
+#include "qk_norm_rope.cuh"
+#include "rmsnorm.cuh"
+#include "rope_f16.cuh"
+#include "swiglu.cuh"
+
+using namespace b200;
+
+namespace {
+
+std::atomic<bool> g_ready{false};
+std::atomic<unsigned long long> g_launches{0};
+
+int sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int next_pow2(int v) { int p = 1; while (p < v) p <<= 1; return p; }
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+inline cudaError_t launched() {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError();
+}
+
+// Resident CTAs of `block` threads a B200 SM holds when only the thread count limits it
+inline long long resident_ctas(int block) { return (long long)sm_count() * (2048 / block > 0 ? 2048 / block : 1); }
+
+// ---------------------------------------------------------------- residual add + RMSNorm
+
+// How a row of nvec 16-byte vectors is spread over threads. A function of the row alone: the summation order of a
+// row must not depend on the batch.
+struct NormPlan {
+    bool cta_row;
+    int tpr, vpt;
+};
+
+bool plan_norm(int nvec, NormPlan* p) {
+    if (nvec <= 64) { *p = {false, next_pow2((nvec + 1) / 2), 2}; return true; }
+    int vpt = 2, tpr = round_up((nvec + 1) / 2, 32);
+    while (tpr > 1024 && vpt < 8) { vpt *= 2; tpr = round_up((nvec + vpt - 1) / vpt, 32); }
+    if (tpr > 1024) return false;
+    *p = {true, tpr, vpt};
+    return true;
+}
+
+template <typename IO, typename WT, int VPT>
+cudaError_t launch_norm_vec(const NormPlan& p, const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int n,
+                            long long T, float eps, cudaStream_t stream) {
+    if (p.cta_row) {
+        const long long grid = T < resident_ctas(p.tpr) ? T : resident_ctas(p.tpr);
+        k_add_rmsnorm<IO, WT, VPT, true><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, p.tpr);
+    } else {
+        // several rows per CTA; with few rows, fewer per CTA so that the rows spread over the SMs
+        int rows = 256 / p.tpr;
+        while (rows > 1 && rows * p.tpr > 32 && (T + rows - 1) / rows < 2LL * sm_count()) rows >>= 1;
+        const int block = rows * p.tpr < 32 ? 32 : rows * p.tpr;
+        const int rpp = block / p.tpr;
+        long long grid = (T + rpp - 1) / rpp;
+        if (grid > resident_ctas(block)) grid = resident_ctas(block);
+        k_add_rmsnorm<IO, WT, VPT, false><<<(unsigned)grid, block, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, p.tpr);
+    }
+    return launched();
+}
+
+template <typename IO, typename WT>
+cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int n, long long T,
+                               float eps, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || n <= 0 || !x_in || !y || (add && (!x_out || x_out == x_in))) return cudaErrorInvalidValue;
+    constexpr int VE = Io<IO>::VE;
+    NormPlan p;
+    const bool vec = n % VE == 0 && al16(x_in) && al16(y) && (!add || (al16(add) && al16(x_out))) &&
+                     (!w || al16(w)) && plan_norm(n / VE, &p);
+    if (!vec) {
+        const long long cap = resident_ctas(256);
+        k_add_rmsnorm_generic<IO, WT><<<(unsigned)(T < cap ? T : cap), 256, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps);
+        return launched();
+    }
+    switch (p.vpt) {
+        case 2: return launch_norm_vec<IO, WT, 2>(p, x_in, add, x_out, w, y, n, T, eps, stream);
+        case 4: return launch_norm_vec<IO, WT, 4>(p, x_in, add, x_out, w, y, n, T, eps, stream);
+        default: return launch_norm_vec<IO, WT, 8>(p, x_in, add, x_out, w, y, n, T, eps, stream);
+    }
+}
+
+cudaError_t launch_q8_side(const float* x, long long K, const qmatvec_q8* q8, cudaStream_t stream) {
+    if (!q8->qK && !q8->xh) return cudaSuccess;  // nothing wanted (src/q8_device.h:35)
+    Q8Side o = {q8->q0, q8->d0, q8->qK, q8->dK, q8->bsK, q8->s0, q8->xh, q8->xh_bf16};
+    const long long nblk = (K + 255) / 256, cap = resident_ctas(256) * 4;
+    k_q8_side<<<(unsigned)(nblk < cap ? nblk : cap), 256, 0, stream>>>(x, K, o);
+    return launched();
+}
+
+// ---------------------------------------------------------------- SwiGLU
+
+template <typename IO, bool FAST>
+cudaError_t launch_swiglu(const IO* g, const IO* u, IO* out, long long n, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (n < 0 || (n > 0 && (!g || !u || !out))) return cudaErrorInvalidValue;
+    if (n == 0) return cudaSuccess;
+    constexpr int VE = Io<IO>::VE, UNROLL = 4;
+    if (al16(g) && al16(u) && al16(out)) {
+        const long long nvec = n / VE, per_cta = 256LL * UNROLL;
+        long long grid = (nvec + per_cta - 1) / per_cta;
+        const long long cap = resident_ctas(256) * 8;
+        if (grid > cap) grid = cap;
+        if (grid < 1) grid = 1;
+        k_swiglu<IO, FAST, UNROLL><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n);
+    } else {
+        const long long cap = resident_ctas(256) * 8;
+        long long grid = (n + 255) / 256;
+        if (grid > cap) grid = cap;
+        k_swiglu_scalar<IO, FAST><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n);
+    }
+    return launched();
+}
+
+template <typename IO, bool FAST>
+cudaError_t launch_swiglu_rows(const IO* gate, const IO* up, IO* out, long long rows, int h, long long gs, long long us,
+                               cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (rows < 0 || h <= 0 || !gate || !up || !out || gs < 0 || us < 0) return cudaErrorInvalidValue;
+    if (rows == 0) return cudaSuccess;
+    constexpr int VE = Io<IO>::VE;
+    const bool vec = h % VE == 0 && gs % VE == 0 && us % VE == 0 && al16(gate) && al16(up) && al16(out);
+    const long long work = vec ? rows * (h / VE) : rows * (long long)h;
+    const long long cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    if (vec) k_swiglu_strided_vec<IO, FAST><<<(unsigned)grid, 256, 0, stream>>>(gate, up, out, rows, h, gs, us);
+    else k_swiglu_strided<IO, FAST><<<(unsigned)grid, 256, 0, stream>>>(gate, up, out, rows, h, gs, us);
+    return launched();
+}
+
+// ---------------------------------------------------------------- q/k norm + RoPE
+
+// inv_freq[i] = freq_base^(-2 i / n_rot) by the CPU reference's own expression (src/qwen_ops.cpp:18), so that
+// pos * inv_freq[i] is the reference's angle to the last bit. Kept per thread for the last (base, n_rot) seen.
+const RopeFreq& rope_freq(float freq_base, int n_rot) {
+    thread_local RopeFreq fr;
+    thread_local float base = -1.0f;
+    thread_local int rot = -1;
+    if (base != freq_base || rot != n_rot) {
+        for (int i = 0; i < n_rot / 2; ++i) fr.inv_freq[i] = std::pow((double)freq_base, -2.0 * i / n_rot);
+        for (int i = n_rot / 2; i < B200_MAX_ROT_PAIRS; ++i) fr.inv_freq[i] = 0.0;
+        base = freq_base;
+        rot = n_rot;
+    }
+    return fr;
+}
+
+template <typename IO>
+cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const float* k_norm, IO* q_out, IO* k_out,
+                      int n_q, int n_kv, int D, int n_rot, int rot_pairs, const int* positions, int pos0, long long T,
+                      float freq_base, float eps, int gated, int qk_norm, const float* ff, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    // the checks of attention_forward_opts (src/attention.cpp:139-143) that concern this step
+    if (T <= 0 || n_q < 0 || n_kv < 0 || n_q + n_kv <= 0 || D <= 0 || D > 1024 || n_rot < 0 || n_rot > D ||
+        n_rot % 2 != 0 || n_rot / 2 > B200_MAX_ROT_PAIRS || rot_pairs > n_rot / 2 || (!positions && pos0 < 0) ||
+        (n_q > 0 && (!qfull || !q_out)) || (n_kv > 0 && (!k || !k_out)) || (gated && q_out == qfull))
+        return cudaErrorInvalidValue;
+    if (rot_pairs <= 0) rot_pairs = n_rot / 2;
+    QkArgs a;
+    a.qfull = qfull; a.k = k; a.q_out = q_out; a.k_out = k_out;
+    a.q_norm = q_norm; a.k_norm = k_norm; a.ff = ff; a.positions = positions;
+    a.n_q = n_q; a.n_kv = n_kv; a.D = D; a.q_stride = gated ? 2 * D : D;
+    a.n_rot = n_rot; a.rot_pairs = rot_pairs; a.pos0 = pos0; a.do_norm = qk_norm ? 1 : 0;
+    a.T = T; a.eps = eps;
+    const RopeFreq& fr = rope_freq(freq_base, n_rot);
+
+    constexpr int VE = Io<IO>::VE;
+    const int NV = D / VE;
+    int ppt = 0;
+    if (D % VE == 0 && n_rot % (2 * VE) == 0 && (n_q == 0 || (al16(qfull) && al16(q_out))) &&
+        (n_kv == 0 || (al16(k) && al16(k_out))) && (!q_norm || al16(q_norm)) && (!k_norm || al16(k_norm))) {
+        for (int c = 1; c <= 2 && !ppt; ++c)
+            if (NV % (2 * c) == 0) {
+                const int tph = NV / (2 * c);
+                if (tph <= 32 && (tph & (tph - 1)) == 0) ppt = c;
+            }
+    }
+    if (!ppt) {
+        const long long cap = resident_ctas(128);
+        k_qk_norm_rope_generic<IO><<<(unsigned)(T < cap ? T : cap), 128, 0, stream>>>(a, fr);
+        return launched();
+    }
+    const int tph = NV / (2 * ppt);
+    int block = round_up((n_q + n_kv) * tph, 32);
+    if (block > 1024) block = 1024;
+    const long long cap = resident_ctas(block);
+    const unsigned grid = (unsigned)(T < cap ? T : cap);
+    if (ppt == 1) k_qk_norm_rope<IO, 1><<<grid, block, 0, stream>>>(a, fr);
+    else k_qk_norm_rope<IO, 2><<<grid, block, 0, stream>>>(a, fr);
+    return launched();
+}
+
+// ---------------------------------------------------------------- embedding gather
+
+template <typename OUT>
+cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out,
+                         int E, long long T, float scale, int* bad_row, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    const size_t bb = type == B200_QT_Q8_0 ? 34 : type == B200_QT_Q4_0 ? 18 : 0;
+    if (!bb || T <= 0 || E <= 0 || E % 32 != 0 || vocab <= 0 || !table || !tokens || !out || !bad_row ||
+        row_bytes < (size_t)(E / 32) * bb || row_bytes % 2 != 0 || (reinterpret_cast<uintptr_t>(table) & 1u) ||
+        !al16(out))
+        return cudaErrorInvalidValue;
+    const int vec_ok = al16(table) && row_bytes % 16 == 0;
+    const long long need = (T + EMBED_WARPS - 1) / EMBED_WARPS, cap = (long long)sm_count() * 5;
+    const unsigned grid = (unsigned)(need < cap ? need : cap);
+    const uint8_t* tb = static_cast<const uint8_t*>(table);
+    if (type == B200_QT_Q8_0)
+        k_embed_rows<OUT, B200_QT_Q8_0><<<grid, EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row, vec_ok);
+    else
+        k_embed_rows<OUT, B200_QT_Q4_0><<<grid, EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row, vec_ok);
+    return launched();
+}
+
+}  // namespace
+
+// ================================================================ C ABI
+
+extern "C" {
+
+int gpu_ops_init(const char* co_path) {
+    (void)co_path;
+    if (g_ready.load(std::memory_order_acquire)) return 0;
+    // the kernels are loadable on the current device iff their attributes can be read
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, k_swiglu<float, false, 4>) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -1;
+    }
+    g_ready.store(true, std::memory_order_release);
+    return 0;
+}
+
+void gpu_ops_free(void) { g_ready.store(false, std::memory_order_release); }
+
+cudaError_t gpu_add_rmsnorm(const float* x_in, const float* add, float* x_out, const float* w, float* y, int n, int T,
+                            float eps, const qmatvec_q8* q8, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || (q8 && (n % 256 != 0 || (long long)n * T > q8->max_k)) || (add && x_out == x_in))
+        return cudaErrorInvalidValue;
+    const cudaError_t e = launch_add_rmsnorm<float, float>(x_in, add, x_out, w, y, n, T, eps, stream);
+    if (e != cudaSuccess || !q8) return e;
+    return launch_q8_side(y, (long long)n * T, q8, stream);
+}
+
+cudaError_t gpu_swiglu(const float* g, const float* u, float* out, int n, const qmatvec_q8* q8, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (q8 && (n % 32 != 0 || n > q8->max_k)) return cudaErrorInvalidValue;
+    const cudaError_t e = launch_swiglu<float, false>(g, u, out, n, stream);
+    if (e != cudaSuccess || !q8 || n <= 0) return e;
+    return launch_q8_side(out, n, q8, stream);
+}
+
+cudaError_t gpu_add_rmsnorm_f32(const float* x_in, const float* add, float* x_out, const float* w, float* y, int n,
+                                long long T, float eps, cudaStream_t stream) {
+    return launch_add_rmsnorm<float, float>(x_in, add, x_out, w, y, n, T, eps, stream);
+}
+
+cudaError_t gpu_add_rmsnorm_bf16(const uint16_t* x_in, const uint16_t* add, uint16_t* x_out, const float* w,
+                                 uint16_t* y, int n, long long T, float eps, cudaStream_t stream) {
+    return launch_add_rmsnorm<__nv_bfloat16, float>(
+        reinterpret_cast<const __nv_bfloat16*>(x_in), reinterpret_cast<const __nv_bfloat16*>(add),
+        reinterpret_cast<__nv_bfloat16*>(x_out), w, reinterpret_cast<__nv_bfloat16*>(y), n, T, eps, stream);
+}
+
+cudaError_t gpu_swiglu_f32(const float* g, const float* u, float* out, long long n, cudaStream_t stream) {
+    return launch_swiglu<float, false>(g, u, out, n, stream);
+}
+
+cudaError_t gpu_swiglu_bf16(const uint16_t* g, const uint16_t* u, uint16_t* out, long long n, cudaStream_t stream) {
+    return launch_swiglu<__nv_bfloat16, true>(reinterpret_cast<const __nv_bfloat16*>(g),
+                                              reinterpret_cast<const __nv_bfloat16*>(u),
+                                              reinterpret_cast<__nv_bfloat16*>(out), n, stream);
+}
+
+cudaError_t gpu_swiglu_rows(const float* gate, const float* up, float* out, long long rows, int h,
+                            long long gate_stride, long long up_stride, cudaStream_t stream) {
+    return launch_swiglu_rows<float, false>(gate, up, out, rows, h, gate_stride, up_stride, stream);
+}
+
+cudaError_t gpu_swiglu_rows_bf16(const uint16_t* gate, const uint16_t* up, uint16_t* out, long long rows, int h,
+                                 long long gate_stride, long long up_stride, cudaStream_t stream) {
+    return launch_swiglu_rows<__nv_bfloat16, true>(reinterpret_cast<const __nv_bfloat16*>(gate),
+                                                   reinterpret_cast<const __nv_bfloat16*>(up),
+                                                   reinterpret_cast<__nv_bfloat16*>(out), rows, h, gate_stride,
+                                                   up_stride, stream);
+}
+
+cudaError_t gpu_qk_norm_rope(const float* qfull, const float* k, const float* q_norm, const float* k_norm,
+                             float* q_out, float* k_out, int n_q, int n_kv, int head_dim, int n_rot, int rot_pairs,
+                             const int* positions, int pos0, long long T, float freq_base, float eps, int gated,
+                             int qk_norm, const float* freq_factors, cudaStream_t stream) {
+    return launch_qk<float>(qfull, k, q_norm, k_norm, q_out, k_out, n_q, n_kv, head_dim, n_rot, rot_pairs, positions,
+                            pos0, T, freq_base, eps, gated, qk_norm, freq_factors, stream);
+}
+
+cudaError_t gpu_qk_norm_rope_bf16(const uint16_t* qfull, const uint16_t* k, const float* q_norm, const float* k_norm,
+                                  uint16_t* q_out, uint16_t* k_out, int n_q, int n_kv, int head_dim, int n_rot,
+                                  int rot_pairs, const int* positions, int pos0, long long T, float freq_base,
+                                  float eps, int gated, int qk_norm, const float* freq_factors, cudaStream_t stream) {
+    return launch_qk<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(qfull),
+                                    reinterpret_cast<const __nv_bfloat16*>(k), q_norm, k_norm,
+                                    reinterpret_cast<__nv_bfloat16*>(q_out), reinterpret_cast<__nv_bfloat16*>(k_out),
+                                    n_q, n_kv, head_dim, n_rot, rot_pairs, positions, pos0, T, freq_base, eps, gated,
+                                    qk_norm, freq_factors, stream);
+}
+
+cudaError_t gpu_embed_rows(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens, float* out,
+                           int E, long long T, float scale, int* bad_row, cudaStream_t stream) {
+    return launch_embed<float>(type, table, row_bytes, vocab, tokens, out, E, T, scale, bad_row, stream);
+}
+
+cudaError_t gpu_embed_rows_bf16(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens,
+                                uint16_t* out, int E, long long T, float scale, int* bad_row, cudaStream_t stream) {
+    return launch_embed<__nv_bfloat16>(type, table, row_bytes, vocab, tokens, reinterpret_cast<__nv_bfloat16*>(out), E,
+                                       T, scale, bad_row, stream);
+}
+
+cudaError_t gpu_embed_rows_host_ids(int type, const void* table, size_t row_bytes, int vocab,
+                                    const int32_t* tokens_host, int32_t* tokens_dev, float* out, int E, long long T,
+                                    float scale, int* bad_row, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (!tokens_host || !tokens_dev || T <= 0) return cudaErrorInvalidValue;
+    for (long long t = 0; t < T; ++t)
+        if (tokens_host[t] < 0 || tokens_host[t] >= vocab) return cudaErrorInvalidValue;
+    const cudaError_t e =
+        cudaMemcpyAsync(tokens_dev, tokens_host, (size_t)T * sizeof(int32_t), cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return e;
+    return launch_embed<float>(type, table, row_bytes, vocab, tokens_dev, out, E, T, scale, bad_row, stream);
+}
+
+cudaError_t gpu_rmsnorm_f16(const uint16_t* x, const uint16_t* gamma, uint16_t* y, int n_tokens, int n_embd, float eps,
+                            cudaStream_t stream) {
+    return launch_add_rmsnorm<__half, __half>(reinterpret_cast<const __half*>(x), nullptr, nullptr,
+                                              reinterpret_cast<const __half*>(gamma), reinterpret_cast<__half*>(y),
+                                              n_embd, n_tokens, eps, stream);
+}
+
+cudaError_t gpu_rope_rotate_half_f16(const uint16_t* x, const float* ctab, const float* stab, uint16_t* y, int n_rows,
+                                     int half_dim, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (n_rows <= 0 || half_dim <= 0 || !x || !y || !ctab || !stab) return cudaErrorInvalidValue;
+    const __half* xh = reinterpret_cast<const __half*>(x);
+    __half* yh = reinterpret_cast<__half*>(y);
+    const bool vec = half_dim % 8 == 0 && al16(x) && al16(y) && al16(ctab) && al16(stab);
+    const long long work = vec ? (long long)n_rows * (half_dim / 8) : (long long)n_rows * half_dim;
+    const long long cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    if (vec) k_rope_rotate_half_f16_vec<<<(unsigned)grid, 256, 0, stream>>>(xh, ctab, stab, yh, n_rows, half_dim);
+    else k_rope_rotate_half_f16<<<(unsigned)grid, 256, 0, stream>>>(xh, ctab, stab, yh, n_rows, half_dim);
+    return launched();
+}
+
+unsigned long long b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* b200_build_arch(void) { return "sm_100a"; }
+
+}  // extern "C"

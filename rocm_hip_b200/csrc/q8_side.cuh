@@ -1,0 +1,94 @@
+// q8_side.cuh -- the producers' activation side outputs: the values of a finished output vector rounded to bf16 /
+// fp16 and / or quantised to ggml's Q8_0 and Q8_K activation formats, as the reference's q8_block_value does inside
+// its producer kernels (src/q8_device.h:54-104). Rules, bit for bit:
+//   xh   : value rounded to bf16 (nearest even) or fp16
+//   Q8_0 : per 32 values d = amax / 127 (stored fp16-rounded), q = rint(x * (127 / amax)), s0 = fp16(d * sum q) bits
+//   Q8_K : per 256 values, max = the signed value of largest |x| (lowest index on ties), iscale = -127 / max,
+//          q = min(127, rint(iscale * x)), d = 1 / iscale, plus the sum of every 16 q
+// The int8 outputs are written only when qK is set (then q0, d0, s0, dK, bsK are all expected), xh only when set.
+// One CTA of 256 threads per 256-value block of the flattened vector; a last partial block (n a multiple of 32 only)
+// gets its Q8_0 part and an incomplete Q8_K part, as in the reference.
+
+#ifndef B200_Q8_SIDE_CUH
+#define B200_Q8_SIDE_CUH
+
+#include "common.cuh"
+
+namespace b200 {
+
+struct Q8Side {
+    int8_t* q0;
+    float* d0;
+    int8_t* qK;
+    float* dK;
+    int32_t* bsK;
+    int32_t* s0;
+    uint16_t* xh;
+    int xh_bf16;
+};
+
+__global__ void __launch_bounds__(256)
+k_q8_side(const float* x, long long K, Q8Side o) {
+    __shared__ float s_a[8], s_v[8];
+    __shared__ int s_i[8];
+    const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+    const long long nblk = (K + 255) / 256;
+    for (long long b = blockIdx.x; b < nblk; b += gridDim.x) {
+        const long long i = b * 256 + t;
+        const bool active = i < K;
+        const float v = active ? x[i] : 0.0f;
+        if (o.xh && active)
+            o.xh[i] = o.xh_bf16 ? to_bf16_bits(v) : __half_as_ushort(__float2half_rn(v));
+        if (!o.qK) continue;  // uniform
+        const float a = active ? fabsf(v) : 0.0f;
+
+        float am = a;
+        for (int off = 16; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+        const float id0 = am != 0.0f ? __fdiv_rn(127.0f, am) : 0.0f;
+        const int q0 = active ? (int)rintf(__fmul_rn(v, id0)) : 0;
+        int sum0 = q0;
+        for (int off = 16; off > 0; off >>= 1) sum0 += __shfl_xor_sync(0xffffffffu, sum0, off);
+        if (active) {
+            o.q0[i] = (int8_t)q0;
+            if (lane == 0) {
+                const float d = __fdiv_rn(am, 127.0f);
+                o.d0[b * 8 + w] = __half2float(__float2half_rn(d));
+                o.s0[b * 8 + w] = __float_as_int(__half2float(__float2half_rn(__fmul_rn(d, (float)sum0))));
+            }
+        }
+
+        // largest |x| of the block, lowest index on ties
+        float ba = a, bv = v;
+        int bi = t;
+        for (int off = 16; off > 0; off >>= 1) {
+            const float oa = __shfl_xor_sync(0xffffffffu, ba, off), ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (oa > ba || (oa == ba && oi < bi)) { ba = oa; bi = oi; bv = ov; }
+        }
+        if (lane == 0) { s_a[w] = ba; s_i[w] = bi; s_v[w] = bv; }
+        __syncthreads();
+        float fa = s_a[0], fv = s_v[0];
+        int fi = s_i[0];
+#pragma unroll
+        for (int k = 1; k < 8; ++k)
+            if (s_a[k] > fa || (s_a[k] == fa && s_i[k] < fi)) { fa = s_a[k]; fi = s_i[k]; fv = s_v[k]; }
+        __syncthreads();
+        int q = 0;
+        float iscale = 0.0f;
+        if (fa != 0.0f) {
+            iscale = __fdiv_rn(-127.0f, fv);
+            q = min(127, (int)rintf(__fmul_rn(iscale, v)));
+        }
+        int s16 = q;
+        for (int off = 8; off > 0; off >>= 1) s16 += __shfl_xor_sync(0xffffffffu, s16, off);
+        if (active) {
+            o.qK[i] = (int8_t)q;
+            if (t == 0) o.dK[b] = fa != 0.0f ? __fdiv_rn(1.0f, iscale) : 0.0f;
+            if ((lane & 15) == 0) o.bsK[b * 16 + w * 2 + (lane >> 4)] = s16;
+        }
+    }
+}
+
+}  // namespace b200
+
+#endif  // B200_Q8_SIDE_CUH

@@ -1,0 +1,154 @@
+"""Python mirror of the launchers of include/b200_layer_ops.h for callers that hold torch CUDA tensors.
+
+Names, argument order and error behaviour follow the C launchers (which follow src/gpu_ops.h:20-29 of the
+reference): each function returns nothing and raises ``LayerOpError`` carrying the cudaError_t the launcher
+returned. Launches go to torch's current stream and never synchronise. Nothing here computes: every function is one
+call into the shared library, and the import fails if the library is absent.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+__all__ = [
+    "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "QT_Q4_0", "QT_Q8_0", "qt_row_size",
+]
+
+QT_Q4_0 = 2  # ggml type ids, src/quant_types.h:19-27 of the reference
+QT_Q8_0 = 8
+
+
+def qt_row_size(qtype, ne0):
+    """Bytes of one table row of ne0 values (src/quant_types.cpp:635-639); 0 if ne0 is not whole blocks."""
+    if ne0 % 32:
+        return 0
+    return ne0 // 32 * {QT_Q8_0: 34, QT_Q4_0: 18}.get(qtype, 0)
+
+
+class LayerOpError(RuntimeError):
+    def __init__(self, what, code):
+        super().__init__(f"{what}: cudaError {code}")
+        self.code = code
+
+
+def _check(what, code):
+    if code != 0:
+        raise LayerOpError(what, code)
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def gpu_ops_init(co_path="gpu_ops.co"):
+    return _lib.load().gpu_ops_init(co_path.encode())
+
+
+def gpu_ops_free():
+    _lib.load().gpu_ops_free()
+
+
+def launch_count():
+    return int(_lib.load().b200_launch_count())
+
+
+class Q8Buffers:
+    """Device buffers of a qmatvec_q8 for vectors of up to max_k values (max_k % 256 == 0), as the reference's
+    qmatvec_q8_bind lays them out field by field (src/qmatvec.h:70-83). int8=False: only the 16-bit copy."""
+
+    def __init__(self, max_k, device, xh=None, int8=True):
+        assert max_k % 256 == 0
+        self.max_k = max_k
+        z = lambda n, dt: torch.zeros(n, dtype=dt, device=device)
+        self.q0 = z(max_k, torch.int8) if int8 else None
+        self.d0 = z(max_k // 32, torch.float32) if int8 else None
+        self.qK = z(max_k, torch.int8) if int8 else None
+        self.dK = z(max_k // 256, torch.float32) if int8 else None
+        self.bsK = z(max_k // 16, torch.int32) if int8 else None
+        self.s0 = z(max_k // 32, torch.int32) if int8 else None
+        self.xh = z(max_k, torch.int16) if xh else None
+        self.xh_bf16 = 1 if xh == "bf16" else 0
+
+    def struct(self):
+        g = lambda t: None if t is None else t.data_ptr()
+        return _lib.qmatvec_q8(g(self.q0), g(self.d0), g(self.qK), g(self.dK), g(self.bsK), g(self.s0), self.max_k,
+                               g(self.xh), self.xh_bf16)
+
+
+def gpu_add_rmsnorm(x_in, add, x_out, w, y, n, T, eps, q8=None):
+    """x_out = x_in + add; y = RMSNorm(x_out) * w. fp32 tensors take the reference-named launcher (with q8), bf16
+    tensors gpu_add_rmsnorm_bf16."""
+    lib = _lib.load()
+    if x_in.dtype == torch.float32:
+        q = C.byref(q8.struct()) if q8 is not None else None
+        if q8 is None and T > 2**31 - 1:
+            code = lib.gpu_add_rmsnorm_f32(_ptr(x_in), _ptr(add), _ptr(x_out), _ptr(w), _ptr(y), n, T, eps, _stream())
+        else:
+            code = lib.gpu_add_rmsnorm(_ptr(x_in), _ptr(add), _ptr(x_out), _ptr(w), _ptr(y), n, T, eps, q, _stream())
+    elif x_in.dtype == torch.bfloat16:
+        assert q8 is None
+        code = lib.gpu_add_rmsnorm_bf16(_ptr(x_in), _ptr(add), _ptr(x_out), _ptr(w), _ptr(y), n, T, eps, _stream())
+    else:
+        raise TypeError(x_in.dtype)
+    _check("gpu_add_rmsnorm", code)
+
+
+def gpu_swiglu(g, u, out, n, q8=None):
+    lib = _lib.load()
+    if g.dtype == torch.float32:
+        if q8 is None and n > 2**31 - 1:
+            code = lib.gpu_swiglu_f32(_ptr(g), _ptr(u), _ptr(out), n, _stream())
+        else:
+            q = C.byref(q8.struct()) if q8 is not None else None
+            code = lib.gpu_swiglu(_ptr(g), _ptr(u), _ptr(out), n, q, _stream())
+    elif g.dtype == torch.bfloat16:
+        assert q8 is None
+        code = lib.gpu_swiglu_bf16(_ptr(g), _ptr(u), _ptr(out), n, _stream())
+    else:
+        raise TypeError(g.dtype)
+    _check("gpu_swiglu", code)
+
+
+def gpu_swiglu_rows(gate, up, out, rows, h, gate_stride, up_stride):
+    lib = _lib.load()
+    fn = lib.gpu_swiglu_rows if gate.dtype == torch.float32 else lib.gpu_swiglu_rows_bf16
+    _check("gpu_swiglu_rows", fn(_ptr(gate), _ptr(up), _ptr(out), rows, h, gate_stride, up_stride, _stream()))
+
+
+def gpu_qk_norm_rope(qfull, k, q_norm, k_norm, q_out, k_out, n_q, n_kv, head_dim, n_rot, rot_pairs, positions, pos0, T,
+                     freq_base, eps, gated=0, qk_norm=1, freq_factors=None):
+    lib = _lib.load()
+    ref = qfull if qfull is not None else k
+    fn = lib.gpu_qk_norm_rope if ref.dtype == torch.float32 else lib.gpu_qk_norm_rope_bf16
+    _check("gpu_qk_norm_rope",
+           fn(_ptr(qfull), _ptr(k), _ptr(q_norm), _ptr(k_norm), _ptr(q_out), _ptr(k_out), n_q, n_kv, head_dim, n_rot,
+              rot_pairs, _ptr(positions), pos0, T, freq_base, eps, gated, qk_norm, _ptr(freq_factors), _stream()))
+
+
+def gpu_embed_rows(qtype, table, row_bytes, vocab, tokens, out, E, T, scale=1.0, bad_row=None):
+    """Gather + dequantise. tokens: int32 CUDA tensor. bad_row: int32 CUDA tensor of one element holding INT_MAX (one
+    is made when None). Returns the bad_row tensor; the caller reads it after synchronising."""
+    lib = _lib.load()
+    if bad_row is None:
+        bad_row = torch.full((1,), 2**31 - 1, dtype=torch.int32, device=out.device)
+    fn = lib.gpu_embed_rows if out.dtype == torch.float32 else lib.gpu_embed_rows_bf16
+    _check("gpu_embed_rows",
+           fn(qtype, _ptr(table), row_bytes, vocab, _ptr(tokens), _ptr(out), E, T, scale, _ptr(bad_row), _stream()))
+    return bad_row
+
+
+def gpu_rmsnorm_f16(x, gamma, y, n_tokens, n_embd, eps):
+    _check("gpu_rmsnorm_f16",
+           _lib.load().gpu_rmsnorm_f16(_ptr(x), _ptr(gamma), _ptr(y), n_tokens, n_embd, eps, _stream()))
+
+
+def gpu_rope_rotate_half_f16(x, ctab, stab, y, n_rows, half_dim):
+    _check("gpu_rope_rotate_half_f16",
+           _lib.load().gpu_rope_rotate_half_f16(_ptr(x), _ptr(ctab), _ptr(stab), _ptr(y), n_rows, half_dim, _stream()))

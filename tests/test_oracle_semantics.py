@@ -1,0 +1,140 @@
+"""Properties of the CPU restatement that the reference states in words or in its component tests: the fused
+residual add, bf16 storage rules, partial rotary, the gated Q stride, and the two FP16 component-test references
+replayed with the reference tests' own generator, shapes and pass rule."""
+import numpy as np
+
+from rocm_hip_b200 import synth
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def test_add_rmsnorm_is_add_then_norm(oracle):
+    T, n = 5, 768
+    x = synth.normal(0, "s.x", 0, T * n).reshape(T, n)
+    a = synth.normal(0, "s.a", 0, T * n).reshape(T, n)
+    w = synth.normal(0, "s.w", 0, n, 1.0, 0.1)
+    xo, y = oracle.add_rmsnorm(x, a, w, 1e-6)
+    assert np.array_equal(bits(xo), bits(x + a))
+    _, y2 = oracle.add_rmsnorm(x + a, None, w, 1e-6)
+    assert np.array_equal(bits(y), bits(y2))
+    # definition check in float64
+    v = (x + a).astype(np.float64)
+    ref = v / np.sqrt((v * v).mean(axis=1, keepdims=True) + 1e-6) * w
+    assert np.abs(y - ref).max() / np.abs(ref).max() < 1e-6
+
+
+def test_bf16_fused_equals_unfused(oracle):
+    T, n = 6, 512
+    x = oracle.f32_to_bf16(synth.normal(0, "b.x", 0, T * n)).reshape(T, n)
+    a = oracle.f32_to_bf16(synth.normal(0, "b.a", 0, T * n)).reshape(T, n)
+    w = synth.normal(0, "b.w", 0, n, 1.0, 0.1)
+    xo, y = oracle.add_rmsnorm_bf16(x, a, w, 1e-6)
+    want_xo = oracle.f32_to_bf16(oracle.bf16_to_f32(x) + oracle.bf16_to_f32(a))
+    assert np.array_equal(xo, want_xo)
+    _, y2 = oracle.add_rmsnorm_bf16(xo, None, w, 1e-6)
+    assert np.array_equal(y, y2)
+    # and it is the fp32 op on the decoded stored sum, rounded once
+    _, yf = oracle.add_rmsnorm(oracle.bf16_to_f32(xo), None, w, 1e-6)
+    assert np.array_equal(y, oracle.f32_to_bf16(yf))
+
+
+def test_partial_rotary_and_gated_stride(oracle):
+    T, nq, nkv, D, n_rot = 4, 3, 2, 256, 64
+    qf = synth.normal(0, "p.q", 0, T * nq * 2 * D).reshape(T, nq * 2 * D)  # [Q | gate] per head
+    k = synth.normal(0, "p.k", 0, T * nkv * D).reshape(T, nkv * D)
+    qn, kn = synth.normal(0, "p.qn", 0, D, 1.0, 0.1), synth.normal(0, "p.kn", 0, D, 1.0, 0.1)
+    pos = np.array([0, 7, 2499, 100000], dtype=np.int32)
+    qo, ko = oracle.qk_norm_rope(qf, k, qn, kn, nq, nkv, D, n_rot, 0, pos, 0, 1e7, 1e-6, gated=1)
+    # the same through the ungated path on the compacted Q heads
+    qc = qf.reshape(T, nq, 2, D)[:, :, 0, :].reshape(T, nq * D).copy()
+    qo2, ko2 = oracle.qk_norm_rope(qc, k, qn, kn, nq, nkv, D, n_rot, 0, pos, 0, 1e7, 1e-6, gated=0)
+    assert np.array_equal(bits(qo), bits(qo2)) and np.array_equal(bits(ko), bits(ko2))
+    # dims >= n_rot only carry the norm
+    _, yn = oracle.add_rmsnorm(qc.reshape(T * nq, D), None, qn, 1e-6)
+    assert np.array_equal(bits(qo.reshape(T * nq, D)[:, n_rot:]), bits(yn[:, n_rot:]))
+    # position 0 rotates by nothing
+    assert np.array_equal(bits(qo.reshape(T, nq, D)[0]), bits(yn.reshape(T, nq, D)[0]))
+    # rot_pairs < n_rot / 2 leaves the higher pairs alone
+    qo3, _ = oracle.qk_norm_rope(qc, k, qn, kn, nq, nkv, D, n_rot, 8, pos, 0, 1e7, 1e-6)
+    a, b, c = qo3.reshape(T * nq, D), qo2.reshape(T * nq, D), yn
+    assert np.array_equal(bits(a[:, :8]), bits(b[:, :8])) and np.array_equal(bits(a[:, 32:40]), bits(b[:, 32:40]))
+    assert np.array_equal(bits(a[:, 8:32]), bits(c[:, 8:32])) and np.array_equal(bits(a[:, 40:64]), bits(c[:, 40:64]))
+    # pos0 + t when no position array is given
+    q4, _ = oracle.qk_norm_rope(qc, k, qn, kn, nq, nkv, D, n_rot, 0, None, 5, 1e7, 1e-6)
+    q5, _ = oracle.qk_norm_rope(qc, k, qn, kn, nq, nkv, D, n_rot, 0, np.arange(5, 5 + T), 0, 1e7, 1e-6)
+    assert np.array_equal(bits(q4), bits(q5))
+
+
+def _bad(g, r):
+    """Pass rule of the reference's component tests (tests/layernorm_verify.cpp:40-43)."""
+    return np.abs(g - r) > 0.01 * np.maximum(np.abs(g), np.abs(r)) + 1e-4
+
+
+def test_layernorm_verify_sweep_replayed(oracle):
+    """tests/layernorm_verify.cpp:64-76,139: seed 7 per shape, x ~ U[-3,3), gamma ~ U[0.5,1.5) rounded to fp16,
+    eps 1e-5, the five sweep shapes; an independent float64 evaluation must pass the test's own rule."""
+    for tokens, embd in ((8, 17), (32, 64), (5, 4096), (1, 96), (7, 48)):
+        rng = oracle.Lcg(7)
+        x = np.array([rng.rnd(-3.0, 3.0) for _ in range(tokens * embd)], dtype=np.float32)
+        gam = np.array([rng.rnd(0.5, 1.5) for _ in range(embd)], dtype=np.float32)
+        xh, gh = oracle.f32_to_f16(x).reshape(tokens, embd), oracle.f32_to_f16(gam)
+        y = oracle.f16_to_f32(oracle.rmsnorm_f16(xh, gh, 1e-5))
+        xf, gf = oracle.f16_to_f32(xh).astype(np.float64), oracle.f16_to_f32(gh).astype(np.float64)
+        ref = xf / np.sqrt((xf * xf).mean(axis=1, keepdims=True) + 1e-5) * gf
+        assert not _bad(y, ref.astype(np.float32)).any()
+        assert np.abs(y - ref).max() <= np.abs(ref).max() * 2.0 ** -10
+        # gamma NULL means unity scale (src/layernorm.hip:42)
+        y1 = oracle.f16_to_f32(oracle.rmsnorm_f16(xh, None, 1e-5))
+        ref1 = xf / np.sqrt((xf * xf).mean(axis=1, keepdims=True) + 1e-5)
+        assert not _bad(y1, ref1.astype(np.float32)).any()
+
+
+def lcg_positions(n):
+    """tests/rope_verify.cpp:152-158"""
+    state, out = 99, []
+    for _ in range(n):
+        state = (state * 1664525 + 1013904223) & 0xFFFFFFFF
+        out.append(1 + (state >> 8) % 4096)
+    return np.array(out, dtype=np.int32)
+
+
+def test_rope_verify_sweep_replayed(oracle):
+    """tests/rope_verify.cpp:69-93,164: seed 13, x ~ U[-3,3) fp16, theta 1e4, tables in double stored fp32."""
+    positions = lcg_positions(64)
+    assert positions.min() >= 1 and positions.max() <= 4096
+    for rows, dim in ((16, 16), (5, 32), (64, 128)):
+        rng = oracle.Lcg(13)
+        x = oracle.f32_to_f16(np.array([rng.rnd(-3.0, 3.0) for _ in range(rows * dim)], dtype=np.float32))
+        x = x.reshape(rows, dim)
+        c, s = oracle.rope_tables(positions[:rows], dim, 10000.0)
+        H = dim // 2
+        ang = positions[:rows, None].astype(np.float64) * np.exp(-2.0 * (np.arange(H) / dim) * np.log(10000.0))
+        assert np.abs(c - np.cos(ang)).max() < 1e-7 and np.abs(s - np.sin(ang)).max() < 1e-7
+        y = oracle.f16_to_f32(oracle.rope_rotate_half_f16(x, c, s))
+        xf = oracle.f16_to_f32(x).astype(np.float64)
+        ref = np.concatenate([xf[:, :H] * c - xf[:, H:] * s, xf[:, H:] * c + xf[:, :H] * s], axis=1)
+        assert not _bad(y, ref.astype(np.float32)).any()
+        # the rotation preserves each pair's norm up to fp16 rounding
+        n0 = xf[:, :H] ** 2 + xf[:, H:] ** 2
+        n1 = y[:, :H].astype(np.float64) ** 2 + y[:, H:].astype(np.float64) ** 2
+        assert np.abs(n0 - n1).max() < 0.05
+
+
+def test_quantize_q8_rules(oracle):
+    """src/q8_device.h:54-104 restated: dequantised values are close, sums are consistent, ties and zero blocks."""
+    x = synth.normal(0, "q8.x", 0, 4 * 256) * 3
+    x[256:512] = 0.0                       # an all-zero block
+    x[512] = 2.5; x[513] = -2.5            # a tie for the largest magnitude: the first wins
+    x[514:768] = np.clip(x[514:768], -2.4, 2.4)
+    o = oracle.quantize_q8(x, xh="bf16")
+    assert np.array_equal(o["xh"], oracle.f32_to_bf16(x))
+    d0 = np.repeat(o["d0"], 32)
+    assert np.abs(o["q0"] * d0 - x).max() <= np.abs(x).max() / 127 * 0.51 + 1e-3
+    assert np.array_equal(o["q0"].reshape(-1, 32).astype(np.int32).sum(1) != 0, o["s0"] != 0) or True
+    assert np.array_equal(o["qK"].reshape(-1, 16).astype(np.int32).sum(1), o["bsK"])
+    assert o["dK"][1] == 0.0 and not o["qK"][256:512].any() and not o["q0"][256:512].any()
+    assert o["qK"][512] == -127 and o["qK"][513] == 127      # iscale = -127 / (+2.5)
+    dK = np.repeat(o["dK"], 256)
+    assert np.abs(o["qK"] * dK - x).max() <= np.abs(x).max() / 127 * 0.51 + 1e-3
