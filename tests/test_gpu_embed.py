@@ -1,0 +1,124 @@
+"""CUDA embedding gather + dequantisation against the CPU oracle through the C ABI: bit-exact (memcmp), as the
+reference's dequant_verify demands of its decoders (tests/dequant_verify.cpp:106-125)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from rocm_hip_b200 import synth
+from util import dev, host
+
+pytestmark = pytest.mark.gpu
+INT_MAX = 2**31 - 1
+
+
+def gather(ops, qt, table, vocab, ids, E, scale=1.0, bf16=False, row_bytes=None):
+    T = ids.size
+    dt = dev(table)
+    out = torch.full((T, E), float("nan"), device="cuda", dtype=torch.bfloat16 if bf16 else torch.float32)
+    bad = ops.gpu_embed_rows(qt, dt, row_bytes or table.shape[1], vocab, dev(ids.astype(np.int32)), out, E, T, scale)
+    torch.cuda.synchronize()
+    return host(out), int(bad.item())
+
+
+def test_c1_q8_0_full_table(ops, oracle):
+    """Qwen3-0.6B: Q8_0 table 151,936 x 1,024 (165 MB), 2,427 ids uniform over the vocabulary."""
+    vocab, E, T = 151936, 1024, 2427
+    table = synth.q8_0_table(0, "c1.embd", vocab, E)
+    ids = synth.randint(0, "c1.ids", 0, T, 0, vocab)
+    st, want = oracle.embed_rows(oracle.Q8_0, table, table.shape[1], vocab, ids, E)
+    got, bad = gather(ops, ops.QT_Q8_0, table, vocab, ids, E)
+    assert st == 0 and bad == INT_MAX
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    got, _ = gather(ops, ops.QT_Q8_0, table, vocab, ids, E, bf16=True)
+    _, want = oracle.embed_rows(oracle.Q8_0, table, table.shape[1], vocab, ids, E, bf16=True)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("E", [32, 96, 256, 2560, 5120, 8192])
+def test_q4_0_and_q8_0_widths(ops, oracle, E):
+    """Row widths whose byte length is and is not a multiple of 16 (staging by 16-byte or 2-byte loads), rows longer
+    than one staging chunk (8192), fp32 and bf16 outputs, every row of the table once plus repeats."""
+    vocab = 777
+    for qt, maker in ((oracle.Q8_0, synth.q8_0_table), (oracle.Q4_0, synth.q4_0_table)):
+        table = maker(1, f"w{E}", vocab, E)
+        ids = np.concatenate([np.arange(vocab), synth.randint(1, "w.ids", 0, 300, 0, vocab)])
+        for bf16 in (False, True):
+            st, want = oracle.embed_rows(qt, table, table.shape[1], vocab, ids, E, bf16=bf16)
+            got, bad = gather(ops, qt, table, vocab, ids, E, bf16=bf16)
+            assert st == 0 and bad == INT_MAX and np.array_equal(got.view(np.uint8), want.view(np.uint8))
+
+
+def test_golden_tables(ops):
+    """The reference's own decode of tables with special fp16 scales (zero, subnormal, largest), tests/golden/dequant.npz."""
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "dequant.npz"))
+    for name, qt in (("q8_0", 8), ("q4_0", 2)):
+        table, want = g[name + "_table"], g[name + "_out"]
+        rows, E = want.shape
+        got, bad = gather(ops, qt, table, rows, np.arange(rows), E)
+        assert bad == INT_MAX and np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_embedding_scale_and_row_stride(ops, oracle):
+    vocab, E = 100, 256
+    table = synth.q8_0_table(2, "sc", vocab, E)
+    ids = synth.randint(2, "sc.ids", 0, 64, 0, vocab)
+    _, want = oracle.embed_rows(oracle.Q8_0, table, table.shape[1], vocab, ids, E, scale=16.0)
+    got, _ = gather(ops, 8, table, vocab, ids, E, scale=16.0)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    _, want = oracle.embed_rows(oracle.Q8_0, table, table.shape[1], vocab, ids, E, scale=0.3)
+    got, _ = gather(ops, 8, table, vocab, ids, E, scale=0.3)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # rows at a stride larger than their payload
+    stride = table.shape[1] + 6
+    padded = np.zeros((vocab, stride), dtype=np.uint8)
+    padded[:, : table.shape[1]] = table
+    _, want = oracle.embed_rows(oracle.Q8_0, padded, stride, vocab, ids, E)
+    got, _ = gather(ops, 8, padded, vocab, ids, E, row_bytes=stride)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_out_of_range_ids(ops, oracle):
+    """An id outside [0, vocab) (src/qwen_model.cpp:981) is reported through the flag as the first offending row,
+    its row is zero-filled, the table is not read there, and the other rows are still right. The host-id entry point
+    refuses before launching anything."""
+    vocab, E, T = 50, 128, 40
+    table = synth.q8_0_table(3, "bad", vocab, E)
+    ids = synth.randint(3, "bad.ids", 0, T, 0, vocab).astype(np.int32)
+    good = ids.copy()
+    ids[[7, 23]] = [vocab, -5]
+    got, bad = gather(ops, 8, table, vocab, ids, E)
+    assert bad == 7
+    assert not got[7].any() and not got[23].any()
+    _, want = oracle.embed_rows(oracle.Q8_0, table, table.shape[1], vocab, good, E)
+    keep = np.ones(T, bool); keep[[7, 23]] = False
+    assert np.array_equal(got[keep].view(np.uint32), want[keep].view(np.uint32))
+    assert oracle.embed_rows(oracle.Q8_0, table, table.shape[1], vocab, ids, E)[0] == -1
+
+    import ctypes as C
+    from rocm_hip_b200 import _lib
+    lib = _lib.load()
+    out = torch.zeros(T, E, device="cuda")
+    scratch = torch.zeros(T, dtype=torch.int32, device="cuda")
+    flag = torch.full((1,), INT_MAX, dtype=torch.int32, device="cuda")
+    p = lambda t: C.c_void_p(t.data_ptr())
+    before = ops.launch_count()
+    code = lib.gpu_embed_rows_host_ids(8, p(dev(table)), table.shape[1], vocab, C.c_void_p(ids.ctypes.data), p(scratch),
+                                       p(out), E, T, 1.0, p(flag), None)
+    assert code == 1 and ops.launch_count() == before
+    dt = dev(table)
+    code = lib.gpu_embed_rows_host_ids(8, p(dt), table.shape[1], vocab, C.c_void_p(good.ctypes.data), p(scratch),
+                                       p(out), E, T, 1.0, p(flag), None)
+    torch.cuda.synchronize()
+    assert code == 0 and np.array_equal(host(out).view(np.uint32), want.view(np.uint32))
+
+
+def test_argument_errors(ops):
+    t = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    ids = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = torch.zeros(4, 64, device="cuda")
+    for qt, E, rb in ((7, 64, 68), (8, 48, 68), (8, 64, 60), (8, 64, 69)):
+        with pytest.raises(ops.LayerOpError) as e:
+            ops.gpu_embed_rows(qt, t, rb, 10, ids, out, E, 4)
+        assert e.value.code == 1
