@@ -128,6 +128,34 @@ cudaError_t gpu_rmsnorm_f16(const uint16_t* x, const uint16_t* gamma, uint16_t* 
 cudaError_t gpu_rope_rotate_half_f16(const uint16_t* x, const float* ctab, const float* stab, uint16_t* y, int n_rows,
                                      int half_dim, cudaStream_t stream);
 
+/* ------------------------------------------------------------------------------------------------ Part 3 */
+
+/* Host-buffer entry points: the same operations for a caller whose rows live in HOST memory, as the reference's CPU
+ * functions take them (qwen_rmsnorm / qwen_rope_neox / qwen_silu, src/qwen_ops.h:17-48; the gather loop,
+ * src/qwen_model.cpp:980-986). A context owns, on the device that was current when it was created, `n_slots` staging
+ * slots of `slot_bytes` each and one stream per slot. A call cuts the rows into chunks that fit a slot and runs
+ * chunk after chunk through copy-in -> kernel -> copy-out, slot after slot, so that the copies of one chunk overlap
+ * the kernel and the copies of its neighbours. Calls are synchronous: they return when the outputs are in host
+ * memory. Page-locked host buffers make the copies asynchronous (pageable ones work, without overlap). One call at a
+ * time per context. Row pointers are host memory; the embedding table is device memory (a weight, uploaded once).
+ * Errors: cudaErrorInvalidValue for bad arguments or a row too large for a slot, else the first CUDA error met. */
+typedef struct b200_host_ctx b200_host_ctx;
+b200_host_ctx* b200_host_ctx_create(size_t slot_bytes, int n_slots);   /* NULL on failure */
+void b200_host_ctx_destroy(b200_host_ctx* ctx);
+
+/* elem: 4 = fp32 rows, 2 = bf16 rows (bit patterns), as the device launchers of parts 1 and 2 */
+cudaError_t b200_host_add_rmsnorm(b200_host_ctx* ctx, int elem, const void* x_in, const void* add, void* x_out,
+                                  const float* w, void* y, int n, long long T, float eps);
+cudaError_t b200_host_swiglu(b200_host_ctx* ctx, int elem, const void* g, const void* u, void* out, long long rows,
+                             int width);
+cudaError_t b200_host_qk_norm_rope(b200_host_ctx* ctx, int elem, const void* qfull, const void* k, const float* q_norm,
+                                   const float* k_norm, void* q_out, void* k_out, int n_q, int n_kv, int head_dim,
+                                   int n_rot, int rot_pairs, const int* positions, int pos0, long long T,
+                                   float freq_base, float eps, int gated, int qk_norm, const float* freq_factors);
+/* table_dev: device memory. tokens: host. An out-of-range id returns cudaErrorInvalidValue before anything runs. */
+cudaError_t b200_host_embed_rows(b200_host_ctx* ctx, int elem, int type, const void* table_dev, size_t row_bytes,
+                                 int vocab, const int32_t* tokens, void* out, int E, long long T, float scale);
+
 /* Number of kernel launches this library has issued since it was loaded (all launchers, all threads) */
 unsigned long long b200_launch_count(void);
 /* "sm_100a" and the like: the architecture the kernels were compiled for */

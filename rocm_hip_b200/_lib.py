@@ -44,6 +44,12 @@ SIGNATURES = {
     "gpu_embed_rows_host_ids": (_i, [_i, _p, _sz, _i, _p, _p, _p, _i, _ll, _f, _p, _p]),
     "gpu_rmsnorm_f16": (_i, [_p, _p, _p, _i, _i, _f, _p]),
     "gpu_rope_rotate_half_f16": (_i, [_p, _p, _p, _p, _i, _i, _p]),
+    "b200_host_ctx_create": (_p, [_sz, _i]),
+    "b200_host_ctx_destroy": (None, [_p]),
+    "b200_host_add_rmsnorm": (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _ll, _f]),
+    "b200_host_swiglu": (_i, [_p, _i, _p, _p, _p, _ll, _i]),
+    "b200_host_qk_norm_rope": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p]),
+    "b200_host_embed_rows": (_i, [_p, _i, _i, _p, _sz, _i, _p, _p, _i, _ll, _f]),
     "b200_launch_count": (C.c_ulonglong, []),
     "b200_build_arch": (C.c_char_p, []),
 }

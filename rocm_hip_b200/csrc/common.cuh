@@ -108,6 +108,62 @@ struct Io<__half> {
     __device__ static __forceinline__ float round_trip(float v) { return __half2float(__float2half_rn(v)); }
 };
 
+// ---------------------------------------------------------------- packed fp32 pairs
+//
+// sm_100 has two-wide fp32 instructions (add / sub / mul / fma .f32x2 on a 64-bit register holding two floats). Each
+// lane rounds to nearest exactly like the scalar instruction, so results are bit-identical, at half the instruction
+// count: these kernels are bound by instruction issue long before arithmetic throughput.
+typedef unsigned long long f2;
+
+__device__ __forceinline__ f2 pk2(float a, float b) { f2 r; asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void upk2(f2 v, float& a, float& b) { asm("mov.b64 {%0,%1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f2 mul2(f2 a, f2 b) { f2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f2 add2(f2 a, f2 b) { f2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f2 sub2(f2 a, f2 b) { f2 r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+
+// A 16-byte vector of stored values as VE / 2 packed pairs, and back (one rounding to the storage type)
+template <typename T>
+struct Io2;
+
+template <>
+struct Io2<float> {
+    static constexpr int NP = 2;
+    __device__ static __forceinline__ void unpack(const uint4& r, f2* v) {
+        v[0] = ((f2)r.y << 32) | r.x;
+        v[1] = ((f2)r.w << 32) | r.z;
+    }
+    __device__ static __forceinline__ uint4 pack(const f2* v) {
+        return make_uint4((uint32_t)v[0], (uint32_t)(v[0] >> 32), (uint32_t)v[1], (uint32_t)(v[1] >> 32));
+    }
+};
+
+template <>
+struct Io2<__nv_bfloat16> {
+    static constexpr int NP = 4;
+    __device__ static __forceinline__ void unpack(const uint4& r, f2* v) {
+        v[0] = pk2(bf16_lo(r.x), bf16_hi(r.x));
+        v[1] = pk2(bf16_lo(r.y), bf16_hi(r.y));
+        v[2] = pk2(bf16_lo(r.z), bf16_hi(r.z));
+        v[3] = pk2(bf16_lo(r.w), bf16_hi(r.w));
+    }
+    __device__ static __forceinline__ uint32_t pack1(f2 v) {
+        float a, b;
+        upk2(v, a, b);
+        return pack_bf16(a, b);
+    }
+    __device__ static __forceinline__ uint4 pack(const f2* v) {
+        return make_uint4(pack1(v[0]), pack1(v[1]), pack1(v[2]), pack1(v[3]));
+    }
+};
+
+// sum += a^2 + b^2 of a packed pair, in double
+__device__ __forceinline__ void sumsq2(f2 v, double& s0, double& s1) {
+    float a, b;
+    upk2(v, a, b);
+    s0 = fma((double)a, (double)a, s0);
+    s1 = fma((double)b, (double)b, s1);
+}
+
 // gamma values for one vector of VE consecutive columns starting at column c (fp32 or fp16 gammas; NULL: all 1)
 template <int VE, typename WT>
 __device__ __forceinline__ void load_gamma(const WT* w, int c, float* g) {
@@ -139,28 +195,40 @@ __device__ __forceinline__ float gamma1(const WT* w, int c) {
 // ---------------------------------------------------------------- reductions
 
 // Sum over the `width` lanes (a power of two <= 32) of an aligned lane group; every lane of the group gets the total.
-// All 32 lanes of the warp must call it.
-__device__ __forceinline__ float group_sum(float v, int width) {
+// All 32 lanes of the warp must call it. Sums of squares are carried in double, as the CPU reference does
+// (src/qwen_ops.cpp:9-10): on a bandwidth-bound kernel it is free, and it makes 1/rms the reference's to the bit.
+__device__ __forceinline__ double group_sum(double v, int width) {
     for (int off = width >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
     return v;
 }
 
-// Sum over all threads of the CTA (blockDim.x a multiple of 32, at most 1024). part: 32 floats of shared memory
+// Sum over all threads of the CTA (blockDim.x a multiple of 32, at most 1024). part: 32 doubles of shared memory
 // that no other use touches between two calls with the same buffer.
-__device__ __forceinline__ float cta_sum(float v, float* part) {
+__device__ __forceinline__ double cta_sum(double v, double* part) {
     v = group_sum(v, 32);
     const int nw = blockDim.x >> 5;
     if (nw == 1) return v;
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
     __syncthreads();
-    float tot = 0.0f;
+    double tot = 0.0;
     for (int k = 0; k < nw; ++k) tot += part[k];
     return tot;
 }
 
-// 1 / sqrt(mean + eps) with correctly rounded square root and division (one per row: the cost is nothing)
-__device__ __forceinline__ float inv_rms(float sum_sq, int n, float eps) {
-    return __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)n), eps)));
+// (float)(1 / sqrt(sum_sq / n + eps)), the CPU reference's double-precision expression (src/qwen_ops.cpp:11), without
+// its ~70-instruction double division and square root: the hardware's single-precision rsqrt seeds two Newton steps in
+// double (relative error 2^-22 -> 2^-44 -> below 2^-52), so the float it rounds to is the reference's unless the exact
+// value lies within a few double ulps of a float rounding boundary. inv_n is 1.0 / n. Mean squares outside the range
+// where the single-precision seed is safe take the plain expression.
+__device__ __forceinline__ float inv_rms(double sum_sq, double inv_n, float eps) {
+    const double d = fma(sum_sq, inv_n, (double)eps);
+    const float df = (float)d;
+    if (!(df > 1e-30f && df < 1e30f)) return (float)(1.0 / sqrt(d));
+    double r = (double)rsqrtf(df);
+    const double h = -0.5 * d;
+    r = r * fma(h * r, r, 1.5);
+    r = r * fma(h * r, r, 1.5);
+    return (float)r;
 }
 
 }  // namespace b200

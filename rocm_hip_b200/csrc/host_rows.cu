@@ -1,0 +1,243 @@
+// host_rows.cu -- the host-buffer entry points (part 3 of include/b200_layer_ops.h): rows that live in host memory are
+// cut into chunks and streamed through copy-in -> kernel -> copy-out on a ring of staging slots, one stream per
+// slot, so PCIe transfers in both directions overlap the kernels. This is the drop-in for callers of the reference's
+// CPU functions (src/qwen_ops.h:17-48, the gather loop of src/qwen_model.cpp:980-986), which own host arrays.
+// Rows are independent, so chunk boundaries never change a result: each row gets the bits the device launchers give.
+
+#include "b200_layer_ops.h"
+
+#include <string.h>
+
+#include <new>
+#include <vector>
+
+struct b200_host_ctx {
+    int device = 0;
+    size_t slot_bytes = 0;
+    std::vector<char*> slots;
+    std::vector<cudaStream_t> streams;
+    char* consts = nullptr;  // gammas, frequency factors, the bad-id flag
+};
+
+namespace {
+
+constexpr size_t kConstBytes = 1u << 20;
+constexpr size_t kAlign = 256;
+constexpr int kMaxBufs = 4;
+
+inline size_t up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+struct RowBufs {
+    const void* in[kMaxBufs];
+    size_t in_bpr[kMaxBufs];
+    int n_in = 0;
+    void* out[kMaxBufs];
+    size_t out_bpr[kMaxBufs];
+    int n_out = 0;
+    void add_in(const void* p, size_t bpr) { in[n_in] = p; in_bpr[n_in++] = bpr; }
+    void add_out(void* p, size_t bpr) { out[n_out] = p; out_bpr[n_out++] = bpr; }
+};
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+// launch(dev_in, dev_out, rows, row0, stream) -> cudaError_t
+template <class F>
+cudaError_t run_rows(b200_host_ctx* ctx, long long T, const RowBufs& io, F launch) {
+    size_t per_row = 0;
+    for (int i = 0; i < io.n_in; ++i) per_row += io.in_bpr[i];
+    for (int i = 0; i < io.n_out; ++i) per_row += io.out_bpr[i];
+    const size_t slack = kAlign * (size_t)(io.n_in + io.n_out);
+    if (per_row == 0 || ctx->slot_bytes <= slack || (ctx->slot_bytes - slack) / per_row == 0) return cudaErrorInvalidValue;
+    long long chunk = (long long)((ctx->slot_bytes - slack) / per_row);
+    // at least two chunks per slot when the work allows, so the ring actually overlaps
+    const long long want = (T + 2 * (long long)ctx->slots.size() - 1) / (2 * (long long)ctx->slots.size());
+    if (chunk > want && want >= 64) chunk = want;
+    cudaError_t err = cudaSuccess;
+    long long c = 0;
+    for (long long row0 = 0; row0 < T && err == cudaSuccess; row0 += chunk, ++c) {
+        const long long rows = T - row0 < chunk ? T - row0 : chunk;
+        const size_t s = (size_t)(c % (long long)ctx->slots.size());
+        cudaStream_t st = ctx->streams[s];
+        char* base = ctx->slots[s];
+        void* din[kMaxBufs];
+        void* dout[kMaxBufs];
+        size_t off = 0;
+        for (int i = 0; i < io.n_in; ++i) { din[i] = base + off; off += up((size_t)chunk * io.in_bpr[i]); }
+        for (int i = 0; i < io.n_out; ++i) { dout[i] = base + off; off += up((size_t)chunk * io.out_bpr[i]); }
+        for (int i = 0; i < io.n_in && err == cudaSuccess; ++i)
+            err = cudaMemcpyAsync(din[i], (const char*)io.in[i] + (size_t)row0 * io.in_bpr[i], (size_t)rows * io.in_bpr[i],
+                                  cudaMemcpyHostToDevice, st);
+        if (err == cudaSuccess) err = launch(din, dout, rows, row0, st);
+        for (int i = 0; i < io.n_out && err == cudaSuccess; ++i)
+            err = cudaMemcpyAsync((char*)io.out[i] + (size_t)row0 * io.out_bpr[i], dout[i], (size_t)rows * io.out_bpr[i],
+                                  cudaMemcpyDeviceToHost, st);
+    }
+    for (cudaStream_t st : ctx->streams) {
+        const cudaError_t e = cudaStreamSynchronize(st);
+        if (err == cudaSuccess) err = e;
+    }
+    return err;
+}
+
+// Copies small read-only arrays (gammas and the like) to the context's constant area before the chunks start
+struct ConstArea {
+    b200_host_ctx* ctx;
+    size_t off = 0;
+    cudaError_t err = cudaSuccess;
+    explicit ConstArea(b200_host_ctx* c) : ctx(c) {}
+    template <typename T>
+    const T* put(const T* host, size_t count) {
+        if (!host) return nullptr;
+        const size_t bytes = count * sizeof(T);
+        if (off + up(bytes) > kConstBytes) { err = cudaErrorInvalidValue; return nullptr; }
+        char* d = ctx->consts + off;
+        off += up(bytes);
+        const cudaError_t e = cudaMemcpy(d, host, bytes, cudaMemcpyHostToDevice);
+        if (err == cudaSuccess) err = e;
+        return reinterpret_cast<const T*>(d);
+    }
+};
+
+}  // namespace
+
+extern "C" {
+
+b200_host_ctx* b200_host_ctx_create(size_t slot_bytes, int n_slots) {
+    if (slot_bytes < (1u << 16) || n_slots < 1 || n_slots > 16) return nullptr;
+    b200_host_ctx* ctx = new (std::nothrow) b200_host_ctx;
+    if (!ctx) return nullptr;
+    ctx->slot_bytes = slot_bytes;
+    bool ok = cudaGetDevice(&ctx->device) == cudaSuccess && gpu_ops_init("gpu_ops.co") == 0 &&
+              cudaMalloc((void**)&ctx->consts, kConstBytes) == cudaSuccess;
+    for (int i = 0; ok && i < n_slots; ++i) {
+        char* p = nullptr;
+        cudaStream_t st = nullptr;
+        ok = cudaMalloc((void**)&p, slot_bytes) == cudaSuccess;
+        if (ok) ctx->slots.push_back(p);
+        ok = ok && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
+        if (ok) ctx->streams.push_back(st);
+    }
+    if (!ok) {
+        (void)cudaGetLastError();
+        b200_host_ctx_destroy(ctx);
+        return nullptr;
+    }
+    return ctx;
+}
+
+void b200_host_ctx_destroy(b200_host_ctx* ctx) {
+    if (!ctx) return;
+    DeviceGuard g(ctx->device);
+    for (cudaStream_t st : ctx->streams) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+    for (char* p : ctx->slots) cudaFree(p);
+    if (ctx->consts) cudaFree(ctx->consts);
+    delete ctx;
+}
+
+cudaError_t b200_host_add_rmsnorm(b200_host_ctx* ctx, int elem, const void* x_in, const void* add, void* x_out,
+                                  const float* w, void* y, int n, long long T, float eps) {
+    if (!ctx || (elem != 2 && elem != 4) || !x_in || !y || n <= 0 || T <= 0 || (add && (!x_out || x_out == x_in)))
+        return cudaErrorInvalidValue;
+    DeviceGuard g(ctx->device);
+    ConstArea ca(ctx);
+    const float* dw = ca.put(w, (size_t)n);
+    if (ca.err != cudaSuccess) return ca.err;
+    const size_t bpr = (size_t)n * elem;
+    RowBufs io;
+    io.add_in(x_in, bpr);
+    if (add) { io.add_in(add, bpr); io.add_out(x_out, bpr); }
+    io.add_out(y, bpr);
+    const bool has_add = add != nullptr;
+    return run_rows(ctx, T, io, [=](void** din, void** dout, long long rows, long long, cudaStream_t st) {
+        void* dxo = has_add ? dout[0] : nullptr;
+        void* dy = has_add ? dout[1] : dout[0];
+        const void* da = has_add ? din[1] : nullptr;
+        if (elem == 4)
+            return gpu_add_rmsnorm_f32((const float*)din[0], (const float*)da, (float*)dxo, dw, (float*)dy, n, rows, eps, st);
+        return gpu_add_rmsnorm_bf16((const uint16_t*)din[0], (const uint16_t*)da, (uint16_t*)dxo, dw, (uint16_t*)dy, n,
+                                    rows, eps, st);
+    });
+}
+
+cudaError_t b200_host_swiglu(b200_host_ctx* ctx, int elem, const void* g, const void* u, void* out, long long rows,
+                             int width) {
+    if (!ctx || (elem != 2 && elem != 4) || !g || !u || !out || rows <= 0 || width <= 0) return cudaErrorInvalidValue;
+    DeviceGuard dg(ctx->device);
+    const size_t bpr = (size_t)width * elem;
+    RowBufs io;
+    io.add_in(g, bpr);
+    io.add_in(u, bpr);
+    io.add_out(out, bpr);
+    return run_rows(ctx, rows, io, [=](void** din, void** dout, long long r, long long, cudaStream_t st) {
+        if (elem == 4) return gpu_swiglu_f32((const float*)din[0], (const float*)din[1], (float*)dout[0], r * width, st);
+        return gpu_swiglu_bf16((const uint16_t*)din[0], (const uint16_t*)din[1], (uint16_t*)dout[0], r * width, st);
+    });
+}
+
+cudaError_t b200_host_qk_norm_rope(b200_host_ctx* ctx, int elem, const void* qfull, const void* k, const float* q_norm,
+                                   const float* k_norm, void* q_out, void* k_out, int n_q, int n_kv, int head_dim,
+                                   int n_rot, int rot_pairs, const int* positions, int pos0, long long T,
+                                   float freq_base, float eps, int gated, int qk_norm, const float* freq_factors) {
+    if (!ctx || (elem != 2 && elem != 4) || T <= 0 || n_q < 0 || n_kv < 0 || n_q + n_kv <= 0 || head_dim <= 0 ||
+        (n_q > 0 && (!qfull || !q_out)) || (n_kv > 0 && (!k || !k_out)) || n_rot < 0 || n_rot > head_dim)
+        return cudaErrorInvalidValue;
+    DeviceGuard dg(ctx->device);
+    ConstArea ca(ctx);
+    const float* dqn = ca.put(q_norm, (size_t)head_dim);
+    const float* dkn = ca.put(k_norm, (size_t)head_dim);
+    const float* dff = ca.put(freq_factors, (size_t)(n_rot / 2));
+    if (ca.err != cudaSuccess) return ca.err;
+    const size_t qs = (size_t)(gated ? 2 * head_dim : head_dim);
+    RowBufs io;
+    int iq = -1, ik = -1, ip = -1, oq = -1, ok = -1;
+    if (n_q > 0) { iq = io.n_in; io.add_in(qfull, (size_t)n_q * qs * elem); oq = io.n_out; io.add_out(q_out, (size_t)n_q * head_dim * elem); }
+    if (n_kv > 0) { ik = io.n_in; io.add_in(k, (size_t)n_kv * head_dim * elem); ok = io.n_out; io.add_out(k_out, (size_t)n_kv * head_dim * elem); }
+    if (positions) { ip = io.n_in; io.add_in(positions, sizeof(int)); }
+    return run_rows(ctx, T, io, [=](void** din, void** dout, long long rows, long long row0, cudaStream_t st) {
+        const void* dq = iq >= 0 ? din[iq] : nullptr;
+        const void* dk = ik >= 0 ? din[ik] : nullptr;
+        void* dqo = oq >= 0 ? dout[oq] : nullptr;
+        void* dko = ok >= 0 ? dout[ok] : nullptr;
+        const int* dp = ip >= 0 ? (const int*)din[ip] : nullptr;
+        const int p0 = dp ? 0 : pos0 + (int)row0;
+        if (elem == 4)
+            return gpu_qk_norm_rope((const float*)dq, (const float*)dk, dqn, dkn, (float*)dqo, (float*)dko, n_q, n_kv,
+                                    head_dim, n_rot, rot_pairs, dp, p0, rows, freq_base, eps, gated, qk_norm, dff, st);
+        return gpu_qk_norm_rope_bf16((const uint16_t*)dq, (const uint16_t*)dk, dqn, dkn, (uint16_t*)dqo, (uint16_t*)dko,
+                                     n_q, n_kv, head_dim, n_rot, rot_pairs, dp, p0, rows, freq_base, eps, gated, qk_norm,
+                                     dff, st);
+    });
+}
+
+cudaError_t b200_host_embed_rows(b200_host_ctx* ctx, int elem, int type, const void* table_dev, size_t row_bytes,
+                                 int vocab, const int32_t* tokens, void* out, int E, long long T, float scale) {
+    if (!ctx || (elem != 2 && elem != 4) || !table_dev || !tokens || !out || E <= 0 || T <= 0 || vocab <= 0)
+        return cudaErrorInvalidValue;
+    for (long long t = 0; t < T; ++t)  // the reference's range check, before any decode (src/qwen_model.cpp:981)
+        if (tokens[t] < 0 || tokens[t] >= vocab) return cudaErrorInvalidValue;
+    DeviceGuard dg(ctx->device);
+    const int int_max = 0x7fffffff;
+    ConstArea ca(ctx);
+    int* flag = const_cast<int*>(ca.put(&int_max, 1));
+    if (ca.err != cudaSuccess) return ca.err;
+    RowBufs io;
+    io.add_in(tokens, sizeof(int32_t));
+    io.add_out(out, (size_t)E * elem);
+    return run_rows(ctx, T, io, [=](void** din, void** dout, long long rows, long long, cudaStream_t st) {
+        if (elem == 4)
+            return gpu_embed_rows(type, table_dev, row_bytes, vocab, (const int32_t*)din[0], (float*)dout[0], E, rows,
+                                  scale, flag, st);
+        return gpu_embed_rows_bf16(type, table_dev, row_bytes, vocab, (const int32_t*)din[0], (uint16_t*)dout[0], E, rows,
+                                   scale, flag, st);
+    });
+}
+
+}  // extern "C"

@@ -11,6 +11,7 @@
 
 #include <atomic>
 #include <cmath>
+#include <type_traits>
 
 #include "embed.cuh"
 #include "q8_side.cuh"
@@ -61,7 +62,10 @@ struct NormPlan {
 
 bool plan_norm(int nvec, NormPlan* p) {
     if (nvec <= 64) { *p = {false, next_pow2((nvec + 1) / 2), 2}; return true; }
-    int vpt = 2, tpr = round_up((nvec + 1) / 2, 32);
+    // four vectors per thread when that fills whole warps (64 bytes of a row in flight per thread), else two
+    int vpt = nvec % 128 == 0 ? 4 : 2;
+    if (nvec == 128) { *p = {true, 32, 4}; return true; }
+    int tpr = round_up((nvec + vpt - 1) / vpt, 32);
     while (tpr > 1024 && vpt < 8) { vpt *= 2; tpr = round_up((nvec + vpt - 1) / vpt, 32); }
     if (tpr > 1024) return false;
     *p = {true, tpr, vpt};
@@ -96,6 +100,18 @@ cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const W
     NormPlan p;
     const bool vec = n % VE == 0 && al16(x_in) && al16(y) && (!add || (al16(add) && al16(x_out))) &&
                      (!w || al16(w)) && plan_norm(n / VE, &p);
+    if constexpr (std::is_same<WT, float>::value && !std::is_same<IO, __half>::value) {
+        // exact fit of whole warps with gammas: the trimmed kernel
+        if (vec && p.cta_row && w && (n / VE) == p.tpr * p.vpt && (p.vpt == 2 || p.vpt == 4)) {
+            long long grid = (long long)sm_count() * (2048 / p.tpr > 32 ? 32 : 2048 / p.tpr);
+            if (grid > T) grid = T;
+#define NORM_FAST(V, A) k_add_rmsnorm_fast<IO, V, A><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps)
+            if (p.vpt == 4) { if (add) NORM_FAST(4, true); else NORM_FAST(4, false); }
+            else { if (add) NORM_FAST(2, true); else NORM_FAST(2, false); }
+#undef NORM_FAST
+            return launched();
+        }
+    }
     if (!vec) {
         const long long cap = resident_ctas(256);
         k_add_rmsnorm_generic<IO, WT><<<(unsigned)(T < cap ? T : cap), 256, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps);
@@ -159,6 +175,24 @@ cudaError_t launch_swiglu_rows(const IO* gate, const IO* up, IO* out, long long 
 
 // ---------------------------------------------------------------- q/k norm + RoPE
 
+// Stand-in for a missing gamma in the vector kernel (multiplying by 1.0f leaves every bit alone)
+__device__ float g_ones[1024];
+bool g_ones_ready[64];
+
+const float* ones_vector() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_ones) != cudaSuccess) return nullptr;
+    if (!g_ones_ready[dev]) {
+        float h[1024];
+        for (int i = 0; i < 1024; ++i) h[i] = 1.0f;
+        if (cudaMemcpy(p, h, sizeof(h), cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
+        g_ones_ready[dev] = true;
+    }
+    return p;
+}
+
 // inv_freq[i] = freq_base^(-2 i / n_rot) by the CPU reference's own expression (src/qwen_ops.cpp:18), so that
 // pos * inv_freq[i] is the reference's angle to the last bit. Kept per thread for the last (base, n_rot) seen.
 const RopeFreq& rope_freq(float freq_base, int n_rot) {
@@ -209,13 +243,25 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
         k_qk_norm_rope_generic<IO><<<(unsigned)(T < cap ? T : cap), 128, 0, stream>>>(a, fr);
         return launched();
     }
+    if (qk_norm && (!q_norm || !k_norm)) {
+        const float* ones = ones_vector();
+        if (!ones) return cudaErrorInvalidDeviceFunction;
+        if (!q_norm) a.q_norm = ones;
+        if (!k_norm) a.k_norm = ones;
+    }
     const int tph = NV / (2 * ppt);
     int block = round_up((n_q + n_kv) * tph, 32);
-    if (block > 1024) block = 1024;
-    const long long cap = resident_ctas(block);
-    const unsigned grid = (unsigned)(T < cap ? T : cap);
-    if (ppt == 1) k_qk_norm_rope<IO, 1><<<grid, block, 0, stream>>>(a, fr);
-    else k_qk_norm_rope<IO, 2><<<grid, block, 0, stream>>>(a, fr);
+    if (block > 384) block = 384 / tph * tph;   // the kernel is built for at most 384 threads, two CTAs per SM
+    // tokens per CTA pass: 4 for long batches (64 to 128 bytes of loads in flight per thread), 1 when there are so
+    // few tokens that spreading them over the SMs matters more
+    const int tt = T >= 8LL * sm_count() ? (ppt == 1 ? 4 : 2) : 1;
+    const long long tiles = (T + tt - 1) / tt, cap = resident_ctas(block);
+    const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
+    const size_t smem = 2 * 2 * (size_t)tt * (n_rot / 2 > 0 ? n_rot / 2 : 4) * sizeof(float);
+    if (ppt == 1 && tt == 4) k_qk_norm_rope<IO, 1, 4><<<grid, block, smem, stream>>>(a, fr);
+    else if (ppt == 1) k_qk_norm_rope<IO, 1, 1><<<grid, block, smem, stream>>>(a, fr);
+    else if (tt == 2) k_qk_norm_rope<IO, 2, 2><<<grid, block, smem, stream>>>(a, fr);
+    else k_qk_norm_rope<IO, 2, 1><<<grid, block, smem, stream>>>(a, fr);
     return launched();
 }
 
@@ -256,6 +302,7 @@ int gpu_ops_init(const char* co_path) {
         (void)cudaGetLastError();
         return -1;
     }
+    (void)ones_vector();  // one-time set-up of the current device (other devices: at their first use)
     g_ready.store(true, std::memory_order_release);
     return 0;
 }

@@ -44,119 +44,181 @@ struct QkArgs {
     float eps;
 };
 
-// cos / sin of this token's angles into cs[pair] = (cos, sin); threads 0 .. rot_pairs-1 take one pair each
-// (in steps of blockDim.x)
-__device__ __forceinline__ void token_cos_sin(float2* cs, const QkArgs& a, const RopeFreq& fr, long long t) {
-    if ((int)threadIdx.x >= a.rot_pairs) return;
-    const int pos = a.positions ? a.positions[t] : a.pos0 + (int)t;
-    for (int i = threadIdx.x; i < a.rot_pairs; i += blockDim.x) {
-        double theta = (double)pos * fr.inv_freq[i];
-        if (a.ff) theta /= (double)a.ff[i];
-        double s, c;
-        sincos(theta, &s, &c);
-        cs[i] = make_float2((float)c, (float)s);
+// Rotates two pairs at once: (x0, x1) -> (x0 c - x1 s, x0 s + x1 c) with every product and sum rounded separately, as
+// the CPU reference evaluates it (src/qwen_ops.cpp:21-22). The four products are two-wide multiplies; the sums are
+// scalar add.rn / sub.rn because the assembler contracts a two-wide multiply that feeds a two-wide add into a fused
+// multiply-add even when both carry .rn (measured: 26 % of results differ in the last bit), which it never does to
+// the scalar forms.
+__device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, float* hi) {
+    float a0, a1, b0, b1, c0, c1, d0, d1;
+    upk2(mul2(x0, c), a0, a1);
+    upk2(mul2(x1, s), b0, b1);
+    upk2(mul2(x0, s), c0, c1);
+    upk2(mul2(x1, c), d0, d1);
+    lo[0] = __fsub_rn(a0, b0);
+    lo[1] = __fsub_rn(a1, b1);
+    hi[0] = __fadd_rn(c0, d0);
+    hi[1] = __fadd_rn(c1, d1);
+}
+
+// cos / sin of the angles of `nt` consecutive tokens starting at t0, spread over all threads of the CTA:
+// cos_t / sin_t [token][n_rot / 2]. Pairs at or beyond rot_pairs get (1, 0): x0 * 1 - x1 * 0 is x0 to the bit, so the
+// rotation loop needs no per-pair test.
+__device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const QkArgs& a, const RopeFreq& fr,
+                                               long long t0, int nt) {
+    const int half = a.n_rot >> 1, total = nt * half;
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        const int tt = idx / half, i = idx - tt * half;
+        float c = 1.0f, s = 0.0f;
+        if (i < a.rot_pairs) {
+            const int pos = a.positions ? a.positions[t0 + tt] : a.pos0 + (int)(t0 + tt);
+            double theta = (double)pos * fr.inv_freq[i];
+            if (a.ff) theta /= (double)a.ff[i];
+            double ds, dc;
+            sincos(theta, &ds, &dc);
+            c = (float)dc;
+            s = (float)ds;
+        }
+        cos_t[idx] = c;
+        sin_t[idx] = s;
     }
 }
 
 // PPT: pairs of vectors per thread. Threads per head tph = D / VE / (2 PPT), a power of two <= 32.
-template <typename IO, int PPT>
-__global__ void __launch_bounds__(1024)
+// TT: tokens per CTA pass. All of a pass's loads are issued before its cos / sin are computed, so TT * 2 PPT 16-byte
+// loads per thread are in flight while the double-precision sincos runs; the tables of the pass are shared by all heads.
+// Dynamic shared memory: 2 passes x (cos, sin) x TT x n_rot / 2 floats (a pass writes one half while slower threads
+// may still read the other). Values travel as packed fp32 pairs (two-wide multiplies, adds and subtractions, each lane
+// rounded as the scalar instruction would).
+template <typename IO, int PPT, int TT>
+__global__ void __launch_bounds__(384, 2)
 k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
-    constexpr int VE = Io<IO>::VE;
-    __shared__ float2 cs[2][B200_MAX_ROT_PAIRS];
+    constexpr int VE = Io<IO>::VE, NP = VE / 2;
+    extern __shared__ __align__(16) float tab_all[];
     const int D = a.D, NV = D / VE, tph = NV / (2 * PPT);
     const int R = a.n_rot / VE;      // vectors in the rotary part
     const int P = R / 2;             // pairs of vectors (low half, high half)
+    const int half = a.n_rot >> 1;
     const int heads = a.n_q + a.n_kv;
     const int heads_per_pass = blockDim.x / tph;
     const int l = threadIdx.x % tph, hslot = threadIdx.x / tph;
+    const double inv_n = 1.0 / (double)D;
 
-    // this thread's vector slots within a head: slot s < P pairs vector s with s + P; the rest pair up neighbours
+    // this thread's vector slots within a head: slot s < P pairs vector s with s + P (a rotation pair's two halves);
+    // the vectors past the rotary part are split the same way, first half / second half, so that the lanes of a head
+    // always touch consecutive vectors
     int vlo[PPT], vhi[PPT];
     bool rot[PPT];
+    const int Q = (NV - R) / 2;
 #pragma unroll
     for (int p = 0; p < PPT; ++p) {
         const int s = l + p * tph;  // 0 .. NV/2-1
         rot[p] = s < P;
-        vlo[p] = rot[p] ? s : R + 2 * (s - P);
-        vhi[p] = rot[p] ? s + P : R + 2 * (s - P) + 1;
+        vlo[p] = rot[p] ? s : R + (s - P);
+        vhi[p] = rot[p] ? s + P : R + (s - P) + Q;
     }
 
     int flip = 0;
-    for (long long t = blockIdx.x; t < a.T; t += gridDim.x, flip ^= 1) {
-        const IO* qrow = static_cast<const IO*>(a.qfull) + (size_t)t * a.n_q * a.q_stride;
-        const IO* krow = static_cast<const IO*>(a.k) + (size_t)t * a.n_kv * D;
-        IO* qo = static_cast<IO*>(a.q_out) + (size_t)t * a.n_q * D;
-        IO* ko = static_cast<IO*>(a.k_out) + (size_t)t * a.n_kv * D;
+    const long long ntiles = (a.T + TT - 1) / TT;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, flip ^= 1) {
+        const long long t0 = tile * TT;
+        const int nt = (int)(a.T - t0 < TT ? a.T - t0 : TT);
+        float* cos_t = tab_all + (size_t)flip * 2 * TT * half;
+        float* sin_t = cos_t + TT * half;
         bool tables_done = false;
         for (int h0 = 0; h0 < heads; h0 += heads_per_pass) {
             const int h = h0 + hslot;
             const bool live = h < heads;
             const bool isq = h < a.n_q;
-            const IO* src = isq ? qrow + (size_t)h * a.q_stride : krow + (size_t)(h - a.n_q) * D;
-            IO* dst = isq ? qo + (size_t)h * D : ko + (size_t)(h - a.n_q) * D;
             const float* gamma = isq ? a.q_norm : a.k_norm;
-            uint4 rlo[PPT], rhi[PPT];
-            if (live) {
+            const size_t in_tok = isq ? (size_t)a.n_q * a.q_stride : (size_t)a.n_kv * D;   // values per token row
+            const size_t out_tok = isq ? (size_t)a.n_q * D : (size_t)a.n_kv * D;
+            const uint4* src = reinterpret_cast<const uint4*>(
+                isq ? static_cast<const IO*>(a.qfull) + (size_t)t0 * in_tok + (size_t)h * a.q_stride
+                    : static_cast<const IO*>(a.k) + (size_t)t0 * in_tok + (size_t)(h - a.n_q) * D);
+            uint4* dst = reinterpret_cast<uint4*>(
+                isq ? static_cast<IO*>(a.q_out) + (size_t)t0 * out_tok + (size_t)h * D
+                    : static_cast<IO*>(a.k_out) + (size_t)t0 * out_tok + (size_t)(h - a.n_q) * D);
+            const unsigned in_vec = (unsigned)(in_tok / VE), out_vec = (unsigned)(out_tok / VE);  // vectors per token
+            uint4 rlo[TT][PPT], rhi[TT][PPT];
 #pragma unroll
-                for (int p = 0; p < PPT; ++p) {
-                    rlo[p] = ld_stream(reinterpret_cast<const uint4*>(src) + vlo[p]);
-                    rhi[p] = ld_stream(reinterpret_cast<const uint4*>(src) + vhi[p]);
+            for (int tt = 0; tt < TT; ++tt) {
+                if (live && tt < nt) {
+#pragma unroll
+                    for (int p = 0; p < PPT; ++p) {
+                        rlo[tt][p] = ld_stream(src + (tt * in_vec + (unsigned)vlo[p]));
+                        rhi[tt][p] = ld_stream(src + (tt * in_vec + (unsigned)vhi[p]));
+                    }
                 }
             }
             if (!tables_done) {  // uniform over the CTA
-                token_cos_sin(cs[flip], a, fr, t);
+                tokens_cos_sin(cos_t, sin_t, a, fr, t0, nt);
                 __syncthreads();
                 tables_done = true;
             }
-            float lo[PPT][VE], hi[PPT][VE];
-            float ss = 0.0f;
-            if (live) {
 #pragma unroll
-                for (int p = 0; p < PPT; ++p) {
-                    Io<IO>::unpack(rlo[p], lo[p]);
-                    Io<IO>::unpack(rhi[p], hi[p]);
-#pragma unroll
-                    for (int e = 0; e < VE; ++e) ss = fmaf(lo[p][e], lo[p][e], ss);
-#pragma unroll
-                    for (int e = 0; e < VE; ++e) ss = fmaf(hi[p][e], hi[p][e], ss);
-                }
-            }
-            if (a.do_norm) {  // uniform
-                const float tot = group_sum(ss, tph);
-                const float inv = inv_rms(tot, D, a.eps);
+            for (int tt = 0; tt < TT; ++tt) {
+                if (tt >= nt) break;  // uniform
+                f2 lo[PPT][NP], hi[PPT][NP];
+                double s0 = 0.0, s1 = 0.0;
                 if (live) {
 #pragma unroll
                     for (int p = 0; p < PPT; ++p) {
-                        float gl[VE], gh[VE];
-                        load_gamma<VE, float>(gamma, vlo[p] * VE, gl);
-                        load_gamma<VE, float>(gamma, vhi[p] * VE, gh);
+                        Io2<IO>::unpack(rlo[tt][p], lo[p]);
+                        Io2<IO>::unpack(rhi[tt][p], hi[p]);
+                        if (a.do_norm) {
 #pragma unroll
-                        for (int e = 0; e < VE; ++e) {
-                            lo[p][e] = __fmul_rn(__fmul_rn(lo[p][e], inv), gl[e]);
-                            hi[p][e] = __fmul_rn(__fmul_rn(hi[p][e], inv), gh[e]);
+                            for (int k = 0; k < NP; ++k) sumsq2(lo[p][k], s0, s1);
+#pragma unroll
+                            for (int k = 0; k < NP; ++k) sumsq2(hi[p][k], s0, s1);
                         }
                     }
                 }
-            }
-            if (live) {
+                if (a.do_norm) {  // uniform
+                    const float inv = inv_rms(group_sum(s0 + s1, tph), inv_n, a.eps);
+                    const f2 inv2 = pk2(inv, inv);
+                    if (live) {
 #pragma unroll
-                for (int p = 0; p < PPT; ++p) {
-                    if (rot[p]) {
-                        const int i0 = vlo[p] * VE;  // first pair index of this vector
+                        for (int p = 0; p < PPT; ++p) {
 #pragma unroll
-                        for (int e = 0; e < VE; ++e) {
-                            if (i0 + e < a.rot_pairs) {
-                                const float2 c = cs[flip][i0 + e];
-                                const float x0 = lo[p][e], x1 = hi[p][e];
-                                // src/qwen_ops.cpp:21-22: x0 c - x1 s and x0 s + x1 c, each product rounded
-                                lo[p][e] = __fsub_rn(__fmul_rn(x0, c.x), __fmul_rn(x1, c.y));
-                                hi[p][e] = __fadd_rn(__fmul_rn(x0, c.y), __fmul_rn(x1, c.x));
+                            for (int k = 0; k < NP; k += 2) {
+                                // (the launcher substitutes a vector of ones for a missing gamma)
+                                const ulonglong2 gl = __ldg(reinterpret_cast<const ulonglong2*>(gamma + vlo[p] * VE) + (k >> 1));
+                                const ulonglong2 gh = __ldg(reinterpret_cast<const ulonglong2*>(gamma + vhi[p] * VE) + (k >> 1));
+                                lo[p][k] = mul2(mul2(lo[p][k], inv2), gl.x);
+                                hi[p][k] = mul2(mul2(hi[p][k], inv2), gh.x);
+                                if (k + 1 < NP) {
+                                    lo[p][k + 1] = mul2(mul2(lo[p][k + 1], inv2), gl.y);
+                                    hi[p][k + 1] = mul2(mul2(hi[p][k + 1], inv2), gh.y);
+                                }
                             }
                         }
                     }
-                    st_stream(reinterpret_cast<uint4*>(dst) + vlo[p], Io<IO>::pack(lo[p]));
-                    st_stream(reinterpret_cast<uint4*>(dst) + vhi[p], Io<IO>::pack(hi[p]));
+                }
+                if (live) {
+#pragma unroll
+                    for (int p = 0; p < PPT; ++p) {
+                        float flo[VE], fhi[VE];
+                        if (rot[p]) {
+                            // pairs vlo * VE .. + VE - 1 of this token's tables
+                            const ulonglong2* ct = reinterpret_cast<const ulonglong2*>(cos_t + tt * half + vlo[p] * VE);
+                            const ulonglong2* st = reinterpret_cast<const ulonglong2*>(sin_t + tt * half + vlo[p] * VE);
+#pragma unroll
+                            for (int k = 0; k < NP; k += 2) {
+                                const ulonglong2 c = ct[k >> 1], sn = st[k >> 1];
+                                rotate2(lo[p][k], hi[p][k], c.x, sn.x, flo + 2 * k, fhi + 2 * k);
+                                rotate2(lo[p][k + 1], hi[p][k + 1], c.y, sn.y, flo + 2 * k + 2, fhi + 2 * k + 2);
+                            }
+                        } else {
+#pragma unroll
+                            for (int k = 0; k < NP; ++k) {
+                                upk2(lo[p][k], flo[2 * k], flo[2 * k + 1]);
+                                upk2(hi[p][k], fhi[2 * k], fhi[2 * k + 1]);
+                            }
+                        }
+                        st_stream(dst + (tt * out_vec + (unsigned)vlo[p]), Io<IO>::pack(flo));
+                        st_stream(dst + (tt * out_vec + (unsigned)vhi[p]), Io<IO>::pack(fhi));
+                    }
                 }
             }
         }
@@ -169,14 +231,15 @@ k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
 template <typename IO>
 __global__ void __launch_bounds__(128)
 k_qk_norm_rope_generic(const QkArgs a, const __grid_constant__ RopeFreq fr) {
-    __shared__ float2 cs[B200_MAX_ROT_PAIRS];
+    __shared__ float cos_t[B200_MAX_ROT_PAIRS], sin_t[B200_MAX_ROT_PAIRS];
     __shared__ float v[1024];
-    __shared__ float part[2][32];
+    __shared__ double part[2][32];
     const int D = a.D, half = a.n_rot / 2, heads = a.n_q + a.n_kv;
+    const double inv_n = 1.0 / (double)a.D;
     int flip = 0;
     for (long long t = blockIdx.x; t < a.T; t += gridDim.x) {
         __syncthreads();  // the previous token's tables and head are no longer read
-        token_cos_sin(cs, a, fr, t);
+        tokens_cos_sin(cos_t, sin_t, a, fr, t, 1);
         for (int h = 0; h < heads; ++h) {
             const bool isq = h < a.n_q;
             const IO* src = isq ? static_cast<const IO*>(a.qfull) + ((size_t)t * a.n_q + h) * a.q_stride
@@ -184,15 +247,15 @@ k_qk_norm_rope_generic(const QkArgs a, const __grid_constant__ RopeFreq fr) {
             IO* dst = isq ? static_cast<IO*>(a.q_out) + ((size_t)t * a.n_q + h) * D
                           : static_cast<IO*>(a.k_out) + ((size_t)t * a.n_kv + (h - a.n_q)) * D;
             const float* gamma = isq ? a.q_norm : a.k_norm;
-            float ss = 0.0f;
+            double ss = 0.0;
             for (int d = threadIdx.x; d < D; d += blockDim.x) {
                 const float x = Io<IO>::load1(src + d);
                 v[d] = x;
-                ss = fmaf(x, x, ss);
+                ss = fma((double)x, (double)x, ss);
             }
             float inv = 1.0f;
             if (a.do_norm) {
-                inv = inv_rms(cta_sum(ss, part[flip]), D, a.eps);
+                inv = inv_rms(cta_sum(ss, part[flip]), inv_n, a.eps);
                 flip ^= 1;
                 for (int d = threadIdx.x; d < D; d += blockDim.x)  // this thread's own values
                     v[d] = __fmul_rn(__fmul_rn(v[d], inv), gamma1(gamma, d));
@@ -202,10 +265,10 @@ k_qk_norm_rope_generic(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                 float x = v[d];
                 const int i = d < half ? d : d - half;
                 if (d < a.n_rot && i < a.rot_pairs) {
-                    const float2 c = cs[i];
+                    const float c = cos_t[i], sn = sin_t[i];
                     const float x0 = v[i], x1 = v[i + half];
-                    x = d < half ? __fsub_rn(__fmul_rn(x0, c.x), __fmul_rn(x1, c.y))
-                                 : __fadd_rn(__fmul_rn(x0, c.y), __fmul_rn(x1, c.x));
+                    x = d < half ? __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn))
+                                 : __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
                 }
                 Io<IO>::store1(dst + d, x);
             }

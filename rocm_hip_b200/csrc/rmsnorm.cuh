@@ -1,17 +1,21 @@
 // rmsnorm.cuh -- residual add + RMSNorm over rows, the B200 kernels behind gpu_add_rmsnorm and its bf16 / fp16
-// siblings. Math of the reference's add_rmsnorm / add_rmsnorm_rows (src/gpu_ops.hip:24-101):
-//   v = x_in + add (when add is set; v is stored to x_out), y = v * rsqrt(mean(v^2) + eps) * w, two multiplies
-//   left to right as src/qwen_ops.cpp:12 and src/gpu_ops.hip:52 evaluate them.
-// For 16-bit rows the arithmetic is fp32 and the norm is taken of the value as stored in x_out (rounded), so a
-// fused call gives the bits of a separate add followed by a norm.
+// siblings. Math of the reference's add_rmsnorm / add_rmsnorm_rows (src/gpu_ops.hip:24-101) with the accumulation of
+// its CPU reference (src/qwen_ops.cpp:8-13):
+//   v = x_in + add (when add is set; v is stored to x_out); ss = sum of v^2 in double; inv = (float)(1 / sqrt(ss / n + eps));
+//   y = (v * inv) * w, two fp32 multiplies left to right.
+// The double sum costs nothing on a bandwidth-bound kernel and makes inv, hence y, the CPU reference's to the bit
+// except when a double lands within an ulp of a float rounding boundary. For 16-bit rows the arithmetic is fp32 /
+// double and the norm is taken of the value as stored in x_out (rounded), so a fused call gives the bits of a
+// separate add followed by a norm.
 //
-// Layout: rows [T][n] contiguous. A row is read exactly once with 16-byte loads into registers (VPT vectors per
-// thread), reduced, scaled and written with 16-byte stores: 2 n s bytes per row without add, 4 n s with (s = bytes
-// per value), which is the algorithmic minimum. Two shapes:
+// Layout: rows [T][n] contiguous. A row is read exactly once with 16-byte loads, VPT vectors per thread, kept packed
+// in registers (so that many loads are in flight per thread at little register cost), reduced, scaled and written
+// with 16-byte stores: 2 n s bytes per row without add, 4 n s with (s = bytes per value), the algorithmic minimum.
+// The gammas are re-read per row through the read-only path and stay in L1. Two shapes:
 //   * rows of up to 32 * VPT vectors: a lane group of tpr <= 32 threads per row, several rows per CTA, shuffles only;
 //   * wider rows: one CTA of tpr threads per row (tpr a multiple of 32), one shared-memory exchange per row.
 // The launcher picks (tpr, VPT) from n and the storage type alone, never from T or the grid, so the summation
-// order of a row is fixed. CTAs walk rows with a grid stride, which lets the gammas stay in registers.
+// order of a row is fixed. CTAs walk rows with a grid stride.
 
 #ifndef B200_RMSNORM_CUH
 #define B200_RMSNORM_CUH
@@ -26,19 +30,13 @@ template <typename IO, typename WT, int VPT, bool CTA_ROW>
 __global__ void __launch_bounds__(CTA_ROW ? 1024 : 256)
 k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int n, long long T, float eps, int tpr) {
     constexpr int VE = Io<IO>::VE;
-    __shared__ float part[2][32];
+    __shared__ double part[2][32];
     const int nvec = n / VE;
     const int l = CTA_ROW ? (int)threadIdx.x : (int)threadIdx.x % tpr;
     const int g = CTA_ROW ? 0 : (int)threadIdx.x / tpr;
     const int rows_per_pass = CTA_ROW ? 1 : (int)blockDim.x / tpr;
 
-    float gam[VPT][VE];
-#pragma unroll
-    for (int j = 0; j < VPT; ++j) {
-        const int vi = l + j * tpr;
-        if (vi < nvec) load_gamma<VE, WT>(w, vi * VE, gam[j]);
-    }
-
+    const double inv_n = 1.0 / (double)n;
     int flip = 0;
     // every thread of a warp runs the same number of passes (shuffles need all lanes); rows past T are masked
     for (long long base = (long long)blockIdx.x * rows_per_pass; base < T; base += (long long)gridDim.x * rows_per_pass) {
@@ -59,38 +57,103 @@ k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int 
                 if (pa) ra[j] = ld_stream(pa + vi);
             }
         }
-        float v[VPT][VE];
-        float ss = 0.0f;
+        double ss = 0.0;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int vi = l + j * tpr;
             if (live && vi < nvec) {
-                Io<IO>::unpack(rx[j], v[j]);
+                float v[VE];
+                Io<IO>::unpack(rx[j], v);
                 if (pa) {
                     float a[VE];
                     Io<IO>::unpack(ra[j], a);
 #pragma unroll
-                    for (int e = 0; e < VE; ++e) v[j][e] = __fadd_rn(v[j][e], a[e]);
-                    const uint4 packed = Io<IO>::pack(v[j]);
-                    st_stream(po + vi, packed);
-                    if (sizeof(IO) < 4) Io<IO>::unpack(packed, v[j]);  // the norm sees the stored value
+                    for (int e = 0; e < VE; ++e) v[e] = __fadd_rn(v[e], a[e]);
+                    rx[j] = Io<IO>::pack(v);              // the value as stored: the norm is taken of it
+                    st_stream(po + vi, rx[j]);
+                    if (sizeof(IO) < 4) Io<IO>::unpack(rx[j], v);
                 }
 #pragma unroll
-                for (int e = 0; e < VE; ++e) ss = fmaf(v[j][e], v[j][e], ss);
+                for (int e = 0; e < VE; ++e) ss = fma((double)v[e], (double)v[e], ss);
             }
         }
-        const float tot = CTA_ROW ? cta_sum(ss, part[flip]) : group_sum(ss, tpr);
+        const double tot = CTA_ROW ? cta_sum(ss, part[flip]) : group_sum(ss, tpr);
         flip ^= 1;
-        const float inv = inv_rms(tot, n, eps);
+        const float inv = inv_rms(tot, inv_n, eps);
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int vi = l + j * tpr;
             if (live && vi < nvec) {
-                float o[VE];
+                float v[VE], gam[VE];
+                Io<IO>::unpack(rx[j], v);
+                load_gamma<VE, WT>(w, vi * VE, gam);
 #pragma unroll
-                for (int e = 0; e < VE; ++e) o[e] = __fmul_rn(__fmul_rn(v[j][e], inv), gam[j][e]);
-                st_stream(py + vi, Io<IO>::pack(o));
+                for (int e = 0; e < VE; ++e) v[e] = __fmul_rn(__fmul_rn(v[e], inv), gam[e]);
+                st_stream(py + vi, Io<IO>::pack(v));
             }
+        }
+    }
+}
+
+// The common case, trimmed to the fewest instructions (these kernels are limited by instruction issue before HBM):
+// one CTA per row, the row exactly tpr * VPT vectors (no masking anywhere), gammas present, fp32 or bf16 rows.
+// Values travel as packed fp32 pairs: the add, the two multiplies and the bf16 packing are two-wide instructions,
+// each lane rounded as the scalar instruction would. Same summation order as k_add_rmsnorm is NOT promised: a row
+// width always maps to the same kernel, so a row's bits are still a function of the row alone.
+template <typename IO, int VPT, bool HAS_ADD>
+__global__ void __launch_bounds__(1024)
+k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO* y, int n, long long T, float eps) {
+    constexpr int NP = Io2<IO>::NP;
+    __shared__ double part[2][32];
+    const int tpr = blockDim.x, l = threadIdx.x;
+    const size_t row_vecs = (size_t)tpr * VPT;
+    const double inv_n = 1.0 / (double)n;
+    const uint4* px = reinterpret_cast<const uint4*>(x_in) + l;
+    const uint4* pa = reinterpret_cast<const uint4*>(add) + l;
+    uint4* po = reinterpret_cast<uint4*>(x_out) + l;
+    uint4* py = reinterpret_cast<uint4*>(y) + l;
+    const ulonglong2* pw = reinterpret_cast<const ulonglong2*>(w) + (size_t)l * (NP / 2);
+    size_t off = (size_t)blockIdx.x * row_vecs;
+    const size_t step = (size_t)gridDim.x * row_vecs;
+    int flip = 0;
+    for (long long row = blockIdx.x; row < T; row += gridDim.x, off += step, flip ^= 1) {
+        uint4 rx[VPT], ra[VPT];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            rx[j] = ld_stream(px + off + j * tpr);
+            if (HAS_ADD) ra[j] = ld_stream(pa + off + j * tpr);
+        }
+        double s0 = 0.0, s1 = 0.0;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            f2 v[NP];
+            Io2<IO>::unpack(rx[j], v);
+            if (HAS_ADD) {
+                f2 a[NP];
+                Io2<IO>::unpack(ra[j], a);
+#pragma unroll
+                for (int k = 0; k < NP; ++k) v[k] = add2(v[k], a[k]);
+                rx[j] = Io2<IO>::pack(v);                    // the value as stored: the norm is taken of it
+                st_stream(po + off + j * tpr, rx[j]);
+                if (sizeof(IO) < 4) Io2<IO>::unpack(rx[j], v);
+            }
+#pragma unroll
+            for (int k = 0; k < NP; ++k) sumsq2(v[k], s0, s1);
+        }
+        const double tot = cta_sum(s0 + s1, part[flip]);
+        const float inv = inv_rms(tot, inv_n, eps);
+        const f2 inv2 = pk2(inv, inv);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            f2 v[NP];
+            Io2<IO>::unpack(rx[j], v);
+#pragma unroll
+            for (int h = 0; h < NP / 2; ++h) {
+                const ulonglong2 g = __ldg(pw + (size_t)j * tpr * (NP / 2) + h);
+                v[2 * h] = mul2(mul2(v[2 * h], inv2), g.x);
+                v[2 * h + 1] = mul2(mul2(v[2 * h + 1], inv2), g.y);
+            }
+            st_stream(py + off + j * tpr, Io2<IO>::pack(v));
         }
     }
 }
@@ -100,7 +163,8 @@ k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int 
 template <typename IO, typename WT>
 __global__ void __launch_bounds__(256)
 k_add_rmsnorm_generic(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int n, long long T, float eps) {
-    __shared__ float part[2][32];
+    __shared__ double part[2][32];
+    const double inv_n = 1.0 / (double)n;
     int flip = 0;
     for (long long row = blockIdx.x; row < T; row += gridDim.x) {
         const size_t off = (size_t)row * (size_t)n;
@@ -108,7 +172,7 @@ k_add_rmsnorm_generic(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO*
         const IO* ai = add ? add + off : nullptr;
         IO* xo = x_out + off;
         IO* yo = y + off;
-        float ss = 0.0f;
+        double ss = 0.0;
         for (int c = threadIdx.x; c < n; c += blockDim.x) {
             float v = Io<IO>::load1(xi + c);
             if (ai) {
@@ -116,11 +180,11 @@ k_add_rmsnorm_generic(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO*
                 Io<IO>::store1(xo + c, v);
                 v = Io<IO>::round_trip(v);
             }
-            ss = fmaf(v, v, ss);
+            ss = fma((double)v, (double)v, ss);
         }
-        const float tot = cta_sum(ss, part[flip]);
+        const double tot = cta_sum(ss, part[flip]);
         flip ^= 1;
-        const float inv = inv_rms(tot, n, eps);
+        const float inv = inv_rms(tot, inv_n, eps);
         for (int c = threadIdx.x; c < n; c += blockDim.x) {
             // with add, the value is re-read from x_out: this thread wrote it above
             const float v = ai ? Io<IO>::load1(xo + c) : Io<IO>::load1(xi + c);

@@ -22,43 +22,80 @@ template <bool FAST>
 __device__ __forceinline__ float silu_mul(float g, float u) {
     if constexpr (FAST) {
         float e, r;
-        asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
-        asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(g, -1.4426950408889634f)));
+        asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(__fadd_rn(1.0f, e)));
         return __fmul_rn(__fmul_rn(g, r), u);
     } else {
         return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
     }
 }
 
+// SiLU(g) * u on packed pairs. FAST (16-bit rows): ex2.approx / rcp.approx, the scalings and products two-wide.
+// ex2 flushes subnormal results to zero (they only occur for gates above 87, where 1 + e is 1 either way); rcp does
+// not, so that a gate below -87 still yields its tiny product instead of zero.
+template <bool FAST>
+__device__ __forceinline__ f2 silu_mul2(f2 g, f2 u) {
+    float g0, g1;
+    upk2(g, g0, g1);
+    if constexpr (FAST) {
+        float t0, t1, e0, e1, r0, r1;
+        upk2(mul2(g, pk2(-1.4426950408889634f, -1.4426950408889634f)), t0, t1);
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(t0));
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(t1));
+        upk2(add2(pk2(e0, e1), pk2(1.0f, 1.0f)), t0, t1);
+        asm("rcp.approx.f32 %0, %1;" : "=f"(r0) : "f"(t0));
+        asm("rcp.approx.f32 %0, %1;" : "=f"(r1) : "f"(t1));
+        return mul2(mul2(g, pk2(r0, r1)), u);
+    } else {
+        float u0, u1;
+        upk2(u, u0, u1);
+        return pk2(silu_mul<false>(g0, u0), silu_mul<false>(g1, u1));
+    }
+}
+
+// Each CTA walks tiles of 256 * UNROLL vectors; inside a tile a thread's vectors are at tile + k * 256 + tid, so the
+// per-access index arithmetic is 32-bit and only the tile base is 64-bit. All UNROLL loads of g and of u are issued
+// before the first use.
 template <typename IO, bool FAST, int UNROLL>
 __global__ void __launch_bounds__(256)
 k_swiglu(const IO* g, const IO* u, IO* out, long long n) {
-    constexpr int VE = Io<IO>::VE;
+    constexpr int VE = Io<IO>::VE, NP = VE / 2;
     const long long nvec = n / VE;
-    const uint4* pg = reinterpret_cast<const uint4*>(g);
-    const uint4* pu = reinterpret_cast<const uint4*>(u);
-    uint4* po = reinterpret_cast<uint4*>(out);
-    const long long step = (long long)gridDim.x * blockDim.x * UNROLL;
-    for (long long base = (long long)blockIdx.x * blockDim.x * UNROLL + threadIdx.x; base < nvec; base += step) {
+    constexpr int TILE = 256 * UNROLL;
+    const long long ntiles = (nvec + TILE - 1) / TILE;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const long long v0 = tile * TILE;
+        const uint4* pg = reinterpret_cast<const uint4*>(g) + v0 + threadIdx.x;
+        const uint4* pu = reinterpret_cast<const uint4*>(u) + v0 + threadIdx.x;
+        uint4* po = reinterpret_cast<uint4*>(out) + v0 + threadIdx.x;
+        const int left = (int)(nvec - v0 < TILE ? nvec - v0 : TILE) - (int)threadIdx.x;  // vectors from this thread's first
         uint4 rg[UNROLL], ru[UNROLL];
+        if (left > (UNROLL - 1) * 256) {   // whole tile for this thread: no per-access checks
 #pragma unroll
-        for (int k = 0; k < UNROLL; ++k) {
-            const long long i = base + (long long)k * blockDim.x;
-            if (i < nvec) {
-                rg[k] = ld_stream(pg + i);
-                ru[k] = ld_stream(pu + i);
+            for (int k = 0; k < UNROLL; ++k) {
+                rg[k] = ld_stream(pg + k * 256);
+                ru[k] = ld_stream(pu + k * 256);
             }
-        }
 #pragma unroll
-        for (int k = 0; k < UNROLL; ++k) {
-            const long long i = base + (long long)k * blockDim.x;
-            if (i < nvec) {
-                float a[VE], b[VE], o[VE];
-                Io<IO>::unpack(rg[k], a);
-                Io<IO>::unpack(ru[k], b);
+            for (int k = 0; k < UNROLL; ++k) {
+                f2 a[NP], b[NP];
+                Io2<IO>::unpack(rg[k], a);
+                Io2<IO>::unpack(ru[k], b);
 #pragma unroll
-                for (int e = 0; e < VE; ++e) o[e] = silu_mul<FAST>(a[e], b[e]);
-                st_stream(po + i, Io<IO>::pack(o));
+                for (int e = 0; e < NP; ++e) a[e] = silu_mul2<FAST>(a[e], b[e]);
+                st_stream(po + k * 256, Io2<IO>::pack(a));
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < UNROLL; ++k) {
+                if (k * 256 < left) {
+                    f2 a[NP], b[NP];
+                    Io2<IO>::unpack(ld_stream(pg + k * 256), a);
+                    Io2<IO>::unpack(ld_stream(pu + k * 256), b);
+#pragma unroll
+                    for (int e = 0; e < NP; ++e) a[e] = silu_mul2<FAST>(a[e], b[e]);
+                    st_stream(po + k * 256, Io2<IO>::pack(a));
+                }
             }
         }
     }

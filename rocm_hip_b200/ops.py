@@ -14,7 +14,7 @@ from . import _lib
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
     "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
-    "QT_Q4_0", "QT_Q8_0", "qt_row_size",
+    "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows",
 ]
 
 QT_Q4_0 = 2  # ggml type ids, src/quant_types.h:19-27 of the reference
@@ -152,3 +152,62 @@ def gpu_rmsnorm_f16(x, gamma, y, n_tokens, n_embd, eps):
 def gpu_rope_rotate_half_f16(x, ctab, stab, y, n_rows, half_dim):
     _check("gpu_rope_rotate_half_f16",
            _lib.load().gpu_rope_rotate_half_f16(_ptr(x), _ptr(ctab), _ptr(stab), _ptr(y), n_rows, half_dim, _stream()))
+
+
+class HostRows:
+    """The host-buffer entry points (b200_host_*): rows in host memory (numpy arrays or CPU torch tensors, ideally
+    page-locked) are streamed through the device in chunks. Calls are synchronous. The embedding table stays a CUDA
+    tensor. One context per device and caller thread."""
+
+    def __init__(self, slot_bytes=64 << 20, n_slots=4):
+        self._lib = _lib.load()
+        self._ctx = self._lib.b200_host_ctx_create(slot_bytes, n_slots)
+        if not self._ctx:
+            raise LayerOpError("b200_host_ctx_create", -1)
+
+    def close(self):
+        if self._ctx:
+            self._lib.b200_host_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _h(a):
+        if a is None:
+            return None
+        if isinstance(a, torch.Tensor):
+            assert not a.is_cuda and a.is_contiguous()
+            return C.c_void_p(a.data_ptr())
+        assert a.flags["C_CONTIGUOUS"]
+        return C.c_void_p(a.ctypes.data)
+
+    @staticmethod
+    def _elem(a):
+        return a.element_size() if isinstance(a, torch.Tensor) else a.dtype.itemsize
+
+    def add_rmsnorm(self, x_in, add, x_out, w, y, n, T, eps):
+        h = self._h
+        _check("b200_host_add_rmsnorm", self._lib.b200_host_add_rmsnorm(
+            self._ctx, self._elem(x_in), h(x_in), h(add), h(x_out), h(w), h(y), n, T, eps))
+
+    def swiglu(self, g, u, out, rows, width):
+        h = self._h
+        _check("b200_host_swiglu", self._lib.b200_host_swiglu(self._ctx, self._elem(g), h(g), h(u), h(out), rows, width))
+
+    def qk_norm_rope(self, qfull, k, q_norm, k_norm, q_out, k_out, n_q, n_kv, head_dim, n_rot, rot_pairs, positions,
+                     pos0, T, freq_base, eps, gated=0, qk_norm=1, freq_factors=None):
+        h = self._h
+        ref = qfull if qfull is not None else k
+        _check("b200_host_qk_norm_rope", self._lib.b200_host_qk_norm_rope(
+            self._ctx, self._elem(ref), h(qfull), h(k), h(q_norm), h(k_norm), h(q_out), h(k_out), n_q, n_kv, head_dim,
+            n_rot, rot_pairs, h(positions), pos0, T, freq_base, eps, gated, qk_norm, h(freq_factors)))
+
+    def embed_rows(self, qtype, table_dev, row_bytes, vocab, tokens, out, E, T, scale=1.0):
+        h = self._h
+        _check("b200_host_embed_rows", self._lib.b200_host_embed_rows(
+            self._ctx, self._elem(out), qtype, _ptr(table_dev), row_bytes, vocab, h(tokens), h(out), E, T, scale))
