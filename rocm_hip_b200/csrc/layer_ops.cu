@@ -51,6 +51,30 @@ inline cudaError_t launched() {
 // Resident CTAs of `block` threads a B200 SM holds when only the thread count limits it
 inline long long resident_ctas(int block) { return (long long)sm_count() * (2048 / block > 0 ? 2048 / block : 1); }
 
+// CTAs of this kernel that are resident on the whole device at once (registers and shared memory counted): the grid
+// of a kernel whose CTAs walk their rows with a grid stride, so that no CTA waits for another to retire. Cached per
+// kernel and launch shape (the occupancy query costs microseconds).
+template <typename K>
+long long persistent_grid(K kernel, int block, size_t smem) {
+    struct Entry { const void* f; int block; size_t smem; int dev; int per_sm; };
+    thread_local Entry cache[16];
+    thread_local int used = 0;
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    const void* f = reinterpret_cast<const void*>(kernel);
+    for (int i = 0; i < used; ++i)
+        if (cache[i].f == f && cache[i].block == block && cache[i].smem == smem && cache[i].dev == dev)
+            return (long long)cache[i].per_sm * sm_count();
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, smem) != cudaSuccess || per_sm < 1) {
+        (void)cudaGetLastError();
+        per_sm = 1;
+    }
+    cache[used % 16] = {f, block, smem, dev, per_sm};
+    if (used < 16) ++used;
+    return (long long)per_sm * sm_count();
+}
+
 // ---------------------------------------------------------------- residual add + RMSNorm
 
 // How a row of nvec 16-byte vectors is spread over threads. A function of the row alone: the summation order of a
@@ -76,7 +100,8 @@ template <typename IO, typename WT, int VPT>
 cudaError_t launch_norm_vec(const NormPlan& p, const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int n,
                             long long T, float eps, cudaStream_t stream) {
     if (p.cta_row) {
-        const long long grid = T < resident_ctas(p.tpr) ? T : resident_ctas(p.tpr);
+        const long long res = persistent_grid(k_add_rmsnorm<IO, WT, VPT, true>, p.tpr, 0);
+        const long long grid = T < res ? T : res;
         k_add_rmsnorm<IO, WT, VPT, true><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, p.tpr);
     } else {
         // several rows per CTA; with few rows, fewer per CTA so that the rows spread over the SMs
@@ -85,7 +110,8 @@ cudaError_t launch_norm_vec(const NormPlan& p, const IO* x_in, const IO* add, IO
         const int block = rows * p.tpr < 32 ? 32 : rows * p.tpr;
         const int rpp = block / p.tpr;
         long long grid = (T + rpp - 1) / rpp;
-        if (grid > resident_ctas(block)) grid = resident_ctas(block);
+        const long long res = persistent_grid(k_add_rmsnorm<IO, WT, VPT, false>, block, 0);
+        if (grid > res) grid = res;
         k_add_rmsnorm<IO, WT, VPT, false><<<(unsigned)grid, block, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, p.tpr);
     }
     return launched();
@@ -102,12 +128,17 @@ cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const W
                      (!w || al16(w)) && plan_norm(n / VE, &p);
     if constexpr (std::is_same<WT, float>::value && !std::is_same<IO, __half>::value) {
         // exact fit of whole warps with gammas: the trimmed kernel
-        if (vec && p.cta_row && w && (n / VE) == p.tpr * p.vpt && (p.vpt == 2 || p.vpt == 4)) {
-            long long grid = (long long)sm_count() * (2048 / p.tpr > 32 ? 32 : 2048 / p.tpr);
-            if (grid > T) grid = T;
-#define NORM_FAST(V, A) k_add_rmsnorm_fast<IO, V, A><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps)
+        if (vec && p.cta_row && w && p.tpr <= 512 && (n / VE) == p.tpr * p.vpt && (p.vpt == 2 || p.vpt == 4)) {
+#define NORM_FAST2(V, A, M)                                                                    \
+    do {                                                                                       \
+        long long grid = persistent_grid(k_add_rmsnorm_fast<IO, V, A, M>, p.tpr, 0);           \
+        if (grid > T) grid = T;                                                                \
+        k_add_rmsnorm_fast<IO, V, A, M><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps); \
+    } while (0)
+#define NORM_FAST(V, A) do { if (p.tpr <= 160) NORM_FAST2(V, A, 160); else NORM_FAST2(V, A, 512); } while (0)
             if (p.vpt == 4) { if (add) NORM_FAST(4, true); else NORM_FAST(4, false); }
             else { if (add) NORM_FAST(2, true); else NORM_FAST(2, false); }
+#undef NORM_FAST2
 #undef NORM_FAST
             return launched();
         }
@@ -255,13 +286,18 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     // tokens per CTA pass: 4 for long batches (64 to 128 bytes of loads in flight per thread), 1 when there are so
     // few tokens that spreading them over the SMs matters more
     const int tt = T >= 8LL * sm_count() ? (ppt == 1 ? 4 : 2) : 1;
-    const long long tiles = (T + tt - 1) / tt, cap = resident_ctas(block);
-    const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
+    const long long tiles = (T + tt - 1) / tt;
     const size_t smem = 2 * 2 * (size_t)tt * (n_rot / 2 > 0 ? n_rot / 2 : 4) * sizeof(float);
-    if (ppt == 1 && tt == 4) k_qk_norm_rope<IO, 1, 4><<<grid, block, smem, stream>>>(a, fr);
-    else if (ppt == 1) k_qk_norm_rope<IO, 1, 1><<<grid, block, smem, stream>>>(a, fr);
-    else if (tt == 2) k_qk_norm_rope<IO, 2, 2><<<grid, block, smem, stream>>>(a, fr);
-    else k_qk_norm_rope<IO, 2, 1><<<grid, block, smem, stream>>>(a, fr);
+#define QK_LAUNCH(P, TTV)                                                                  \
+    do {                                                                                   \
+        const long long res = persistent_grid(k_qk_norm_rope<IO, P, TTV>, block, smem);    \
+        k_qk_norm_rope<IO, P, TTV><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(a, fr); \
+    } while (0)
+    if (ppt == 1 && tt == 4) QK_LAUNCH(1, 4);
+    else if (ppt == 1) QK_LAUNCH(1, 1);
+    else if (tt == 2) QK_LAUNCH(2, 2);
+    else QK_LAUNCH(2, 1);
+#undef QK_LAUNCH
     return launched();
 }
 
@@ -277,13 +313,15 @@ cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int voca
         !al16(out))
         return cudaErrorInvalidValue;
     const int vec_ok = al16(table) && row_bytes % 16 == 0;
-    const long long need = (T + EMBED_WARPS - 1) / EMBED_WARPS, cap = (long long)sm_count() * 5;
-    const unsigned grid = (unsigned)(need < cap ? need : cap);
+    const long long need = (T + EMBED_WARPS - 1) / EMBED_WARPS;
     const uint8_t* tb = static_cast<const uint8_t*>(table);
-    if (type == B200_QT_Q8_0)
-        k_embed_rows<OUT, B200_QT_Q8_0><<<grid, EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row, vec_ok);
-    else
-        k_embed_rows<OUT, B200_QT_Q4_0><<<grid, EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row, vec_ok);
+    if (type == B200_QT_Q8_0) {
+        const long long res = persistent_grid(k_embed_rows<OUT, B200_QT_Q8_0>, EMBED_WARPS * 32, 0);
+        k_embed_rows<OUT, B200_QT_Q8_0><<<(unsigned)(need < res ? need : res), EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row, vec_ok);
+    } else {
+        const long long res = persistent_grid(k_embed_rows<OUT, B200_QT_Q4_0>, EMBED_WARPS * 32, 0);
+        k_embed_rows<OUT, B200_QT_Q4_0><<<(unsigned)(need < res ? need : res), EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row, vec_ok);
+    }
     return launched();
 }
 

@@ -100,8 +100,9 @@ k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int 
 // Values travel as packed fp32 pairs: the add, the two multiplies and the bf16 packing are two-wide instructions,
 // each lane rounded as the scalar instruction would. Same summation order as k_add_rmsnorm is NOT promised: a row
 // width always maps to the same kernel, so a row's bits are still a function of the row alone.
-template <typename IO, int VPT, bool HAS_ADD>
-__global__ void __launch_bounds__(1024)
+// MAXT: largest CTA the instance is launched with; small CTAs are held to 96 registers so that four fit an SM.
+template <typename IO, int VPT, bool HAS_ADD, int MAXT>
+__global__ void __launch_bounds__(MAXT, MAXT <= 160 ? 4 : 1)
 k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO* y, int n, long long T, float eps) {
     constexpr int NP = Io2<IO>::NP;
     __shared__ double part[2][32];
@@ -112,16 +113,43 @@ k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO*
     const uint4* pa = reinterpret_cast<const uint4*>(add) + l;
     uint4* po = reinterpret_cast<uint4*>(x_out) + l;
     uint4* py = reinterpret_cast<uint4*>(y) + l;
-    const ulonglong2* pw = reinterpret_cast<const ulonglong2*>(w) + (size_t)l * (NP / 2);
+    // this thread's gammas stay in registers for all of the CTA's rows: re-reading them per row would put twice the
+    // row's own bytes through L1 (fp32 gammas against 16-bit rows), and L1 throughput, not HBM, then sets the pace
+    f2 gam[VPT][NP];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+#pragma unroll
+        for (int h = 0; h < NP / 2; ++h) {
+            const ulonglong2 g = __ldg(reinterpret_cast<const ulonglong2*>(w) + ((size_t)l + (size_t)j * tpr) * (NP / 2) + h);
+            gam[j][2 * h] = g.x;
+            gam[j][2 * h + 1] = g.y;
+        }
+    }
     size_t off = (size_t)blockIdx.x * row_vecs;
     const size_t step = (size_t)gridDim.x * row_vecs;
     int flip = 0;
+    // Without the residual a thread holds only VPT vectors, so the next row's loads are issued before this row's
+    // reduction (two rows in flight per CTA); with it, x and add already double the bytes in flight.
+    uint4 rn[VPT];
+    if (!HAS_ADD && (long long)blockIdx.x < T) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) rn[j] = ld_stream(px + off + j * tpr);
+    }
     for (long long row = blockIdx.x; row < T; row += gridDim.x, off += step, flip ^= 1) {
         uint4 rx[VPT], ra[VPT];
+        if (HAS_ADD) {
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            rx[j] = ld_stream(px + off + j * tpr);
-            if (HAS_ADD) ra[j] = ld_stream(pa + off + j * tpr);
+            for (int j = 0; j < VPT; ++j) {
+                rx[j] = ld_stream(px + off + j * tpr);
+                ra[j] = ld_stream(pa + off + j * tpr);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) rx[j] = rn[j];
+            if (row + gridDim.x < T) {
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) rn[j] = ld_stream(px + off + step + j * tpr);
+            }
         }
         double s0 = 0.0, s1 = 0.0;
 #pragma unroll
@@ -148,11 +176,7 @@ k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO*
             f2 v[NP];
             Io2<IO>::unpack(rx[j], v);
 #pragma unroll
-            for (int h = 0; h < NP / 2; ++h) {
-                const ulonglong2 g = __ldg(pw + (size_t)j * tpr * (NP / 2) + h);
-                v[2 * h] = mul2(mul2(v[2 * h], inv2), g.x);
-                v[2 * h + 1] = mul2(mul2(v[2 * h + 1], inv2), g.y);
-            }
+            for (int k = 0; k < NP; ++k) v[k] = mul2(mul2(v[k], inv2), gam[j][k]);
             st_stream(py + off + j * tpr, Io2<IO>::pack(v));
         }
     }
