@@ -50,9 +50,7 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-def shard(T, rank, world):
-    """Contiguous row range of this rank (rows [lo, hi))."""
-    return T * rank // world, T * (rank + 1) // world
+from rocm_hip_b200.sharding import shard  # noqa: E402  (contiguous row range of a rank)
 
 
 class ClockSampler:
