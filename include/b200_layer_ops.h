@@ -118,6 +118,18 @@ cudaError_t gpu_embed_rows_host_ids(int type, const void* table, size_t row_byte
                                     const int32_t* tokens_host, int32_t* tokens_dev, float* out, int E, long long T,
                                     float scale, int* bad_row, cudaStream_t stream);
 
+/* No counterpart in the reference. gpu_embed_rows_host_ids for a caller that cannot supply device scratch (an engine
+ * that handed out all of HBM at start-up, a serving loop where cudaMalloc is off limits): the device copy of the ids
+ * and the bad-id flag live in an array built into the library, so the call allocates nothing and takes no scratch
+ * arguments. Limits: T <= 262144 ids per call (cudaErrorInvalidValue beyond that; the array costs every GPU that
+ * loads the library 1 MiB for the life of the process); all calls on a device share the array, so calls whose GPU work
+ * may overlap race; the first call on a device resolves the array's address and should precede any stream capture.
+ * Ids are range-checked on the host first: an id outside [0, vocab) returns cudaErrorInvalidValue and queues nothing.
+ * tokens_host must stay valid until its copy has run on `stream`. fp32 output, same bits as gpu_embed_rows. */
+cudaError_t gpu_embed_rows_static_scratch(int type, const void* table, size_t row_bytes, int vocab,
+                                          const int32_t* tokens_host, float* out, int E, long long T, float scale,
+                                          cudaStream_t stream);
+
 /* FP16 component kernels of the reference (src/layernorm.hip:15-45, src/rope_embedding.hip:18-37), which its tests
  * launch by name with one 32-thread block per row; these launchers run better-shaped kernels with the same math.
  * gpu_rmsnorm_f16: y = x * rsqrt(mean(x^2) + eps) * gamma (gamma fp16, NULL: none), fp32 accumulation, one rounding.

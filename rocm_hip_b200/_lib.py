@@ -42,6 +42,7 @@ SIGNATURES = {
     "gpu_embed_rows": (_i, [_i, _p, _sz, _i, _p, _p, _i, _ll, _f, _p, _p]),
     "gpu_embed_rows_bf16": (_i, [_i, _p, _sz, _i, _p, _p, _i, _ll, _f, _p, _p]),
     "gpu_embed_rows_host_ids": (_i, [_i, _p, _sz, _i, _p, _p, _p, _i, _ll, _f, _p, _p]),
+    "gpu_embed_rows_static_scratch": (_i, [_i, _p, _sz, _i, _p, _p, _i, _ll, _f, _p]),
     "gpu_rmsnorm_f16": (_i, [_p, _p, _p, _i, _i, _f, _p]),
     "gpu_rope_rotate_half_f16": (_i, [_p, _p, _p, _p, _i, _i, _p]),
     "b200_host_ctx_create": (_p, [_sz, _i]),
