@@ -282,6 +282,37 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     }
     const int tph = NV / (2 * ppt);
     int block = round_up((n_q + n_kv) * tph, 32);
+    // The trimmed kernel: one head chunk of exactly block threads, long batches, normalisation on, n_rot / 2 a
+    // multiple of 4 floats (16-byte table reads). It takes the whole tiles of 4 tokens; the 0..3 tokens left over go
+    // through the general kernel below (a row's bits do not depend on which of the two processed it).
+    constexpr int FTT = 4;
+    if (ppt == 1 && qk_norm && (n_q + n_kv) * tph == block && block <= 384 && T >= 8LL * sm_count() && n_rot > 0 &&
+        (n_rot / 2) % 4 == 0) {
+        const long long tiles = T / FTT;
+        const size_t smem = (2 * (size_t)D + 2 * 2 * FTT * (size_t)(n_rot / 2)) * sizeof(float);
+        QkArgs m = a;
+        m.T = tiles * FTT;
+        if (n_rot == D) {
+            const long long res = persistent_grid(k_qk_norm_rope_fast<IO, FTT, true>, block, smem);
+            k_qk_norm_rope_fast<IO, FTT, true><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(m, fr);
+        } else {
+            const long long res = persistent_grid(k_qk_norm_rope_fast<IO, FTT, false>, block, smem);
+            k_qk_norm_rope_fast<IO, FTT, false><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(m, fr);
+        }
+        const cudaError_t e = launched();
+        const long long rest = T - m.T;
+        if (e != cudaSuccess || rest == 0) return e;
+        // tail tokens: advance every row pointer and the positions
+        const size_t qin = (size_t)n_q * a.q_stride, kin = (size_t)n_kv * D;
+        a.qfull = n_q ? static_cast<const IO*>(a.qfull) + m.T * qin : nullptr;
+        a.k = n_kv ? static_cast<const IO*>(a.k) + m.T * kin : nullptr;
+        a.q_out = n_q ? static_cast<IO*>(a.q_out) + m.T * (size_t)n_q * D : nullptr;
+        a.k_out = n_kv ? static_cast<IO*>(a.k_out) + m.T * kin : nullptr;
+        if (a.positions) a.positions += m.T;
+        else a.pos0 += (int)m.T;
+        a.T = rest;
+        T = rest;
+    }
     if (block > 384) block = 384 / tph * tph;   // the kernel is built for at most 384 threads, two CTAs per SM
     // tokens per CTA pass: 4 for long batches (64 to 128 bytes of loads in flight per thread), 1 when there are so
     // few tokens that spreading them over the SMs matters more

@@ -225,6 +225,100 @@ k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     }
 }
 
+// The common case with everything that can be static made static: the CTA is exactly (heads x tph) threads (one head
+// chunk, every thread live), T is a multiple of TT (the launcher gives the tail tokens to k_qk_norm_rope), PPT = 1,
+// normalisation on. FULL: n_rot == D, so every thread rotates. The gammas of q and k sit in shared memory next to the
+// tables (read with immediate offsets: no address arithmetic in the token loop).
+// Shared memory: [2 * D floats: q gamma, k gamma][2 passes x (cos, sin) x TT x n_rot / 2 floats].
+template <typename IO, int TT, bool FULL>
+__global__ void __launch_bounds__(384, 2)
+k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
+    constexpr int VE = Io<IO>::VE, NP = VE / 2;
+    extern __shared__ __align__(16) float smem_all[];
+    const int D = a.D, NV = D / VE, tph = NV / 2;
+    const int R = a.n_rot / VE, P = R / 2, half = a.n_rot >> 1;
+    const int l = threadIdx.x % tph, h = threadIdx.x / tph;
+    const bool isq = h < a.n_q;
+    const double inv_n = 1.0 / (double)D;
+    float* gam_s = smem_all;
+    float* tab = smem_all + 2 * D;
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+        const float* g = i < D ? a.q_norm : a.k_norm;
+        gam_s[i] = g[i < D ? i : i - D];
+    }
+    const bool rot = FULL || l < P;
+    const int vlo = rot ? l : R + (l - P);
+    const int vhi = rot ? l + P : R + (l - P) + (NV - R) / 2;
+    const ulonglong2* glo = reinterpret_cast<const ulonglong2*>(gam_s + (isq ? 0 : D) + vlo * VE);
+    const ulonglong2* ghi = reinterpret_cast<const ulonglong2*>(gam_s + (isq ? 0 : D) + vhi * VE);
+    // this thread's place in a token row, in 16-byte vectors
+    const unsigned in_vec = (unsigned)((isq ? (size_t)a.n_q * a.q_stride : (size_t)a.n_kv * D) / VE);
+    const unsigned out_vec = (unsigned)((isq ? (size_t)a.n_q * D : (size_t)a.n_kv * D) / VE);
+    const unsigned in_head = (unsigned)((isq ? (size_t)h * a.q_stride : (size_t)(h - a.n_q) * D) / VE);
+    const unsigned out_head = (unsigned)((isq ? h : h - a.n_q) * NV);
+    const uint4* in_base = reinterpret_cast<const uint4*>(isq ? a.qfull : a.k) + in_head;
+    uint4* out_base = reinterpret_cast<uint4*>(isq ? a.q_out : a.k_out) + out_head;
+    __syncthreads();
+
+    int flip = 0;
+    const long long ntiles = a.T / TT;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, flip ^= 1) {
+        const long long t0 = tile * TT;
+        const uint4* src = in_base + (size_t)t0 * in_vec;
+        uint4* dst = out_base + (size_t)t0 * out_vec;
+        uint4 rlo[TT], rhi[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+            rlo[tt] = ld_stream(src + (tt * in_vec + (unsigned)vlo));
+            rhi[tt] = ld_stream(src + (tt * in_vec + (unsigned)vhi));
+        }
+        float* cos_t = tab + flip * (2 * TT * half);
+        float* sin_t = cos_t + TT * half;
+        tokens_cos_sin(cos_t, sin_t, a, fr, t0, TT);
+        __syncthreads();
+        const ulonglong2* ct = reinterpret_cast<const ulonglong2*>(cos_t + vlo * VE);
+        const ulonglong2* st = reinterpret_cast<const ulonglong2*>(sin_t + vlo * VE);
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+            f2 lo[NP], hi[NP];
+            Io2<IO>::unpack(rlo[tt], lo);
+            Io2<IO>::unpack(rhi[tt], hi);
+            double s0 = 0.0, s1 = 0.0;
+#pragma unroll
+            for (int k = 0; k < NP; ++k) sumsq2(lo[k], s0, s1);
+#pragma unroll
+            for (int k = 0; k < NP; ++k) sumsq2(hi[k], s0, s1);
+            const float inv = inv_rms(group_sum(s0 + s1, tph), inv_n, a.eps);
+            const f2 inv2 = pk2(inv, inv);
+#pragma unroll
+            for (int k = 0; k < NP; k += 2) {
+                const ulonglong2 gl = glo[k >> 1], gh = ghi[k >> 1];
+                lo[k] = mul2(mul2(lo[k], inv2), gl.x);
+                hi[k] = mul2(mul2(hi[k], inv2), gh.x);
+                lo[k + 1] = mul2(mul2(lo[k + 1], inv2), gl.y);
+                hi[k + 1] = mul2(mul2(hi[k + 1], inv2), gh.y);
+            }
+            float flo[VE], fhi[VE];
+            if (rot) {
+#pragma unroll
+                for (int k = 0; k < NP; k += 2) {
+                    const ulonglong2 c = ct[(tt * half) / 4 + (k >> 1)], sn = st[(tt * half) / 4 + (k >> 1)];
+                    rotate2(lo[k], hi[k], c.x, sn.x, flo + 2 * k, fhi + 2 * k);
+                    rotate2(lo[k + 1], hi[k + 1], c.y, sn.y, flo + 2 * k + 2, fhi + 2 * k + 2);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < NP; ++k) {
+                    upk2(lo[k], flo[2 * k], flo[2 * k + 1]);
+                    upk2(hi[k], fhi[2 * k], fhi[2 * k + 1]);
+                }
+            }
+            st_stream(dst + (tt * out_vec + (unsigned)vlo), Io<IO>::pack(flo));
+            st_stream(dst + (tt * out_vec + (unsigned)vhi), Io<IO>::pack(fhi));
+        }
+    }
+}
+
 // Any head size, rotary width and alignment: one CTA pass per token, heads one after the other, the normalised head
 // staged in shared memory so that a value can read its rotation partner (the reference kernel's own scheme).
 // D <= 1024.
