@@ -340,10 +340,32 @@ def run_reference(args, wl, rank, world):
             "config": {"workload": f"{args.config}: {wl['name']}", "rows_per_step": rows}, "cpu_baseline": base,
             "e2e": {"value": val, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_REAL_STDOUT = None
+
+
+def claim_stdout():
+    """Keeps stdout for the one JSON line: anything libraries print to file descriptor 1 (NCCL's version banner, for
+    one) goes to stderr instead."""
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, data)
 
 
 def main():
+    claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -493,7 +515,7 @@ def main():
             "kernels": kernels, "roofline": roof, "e2e": e2e, "cpu_baseline": cpu, "clocks": clk,
             "gpu_launches": launches, "gpu_launches_e2e": launches_e2e,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
