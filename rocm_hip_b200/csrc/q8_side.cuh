@@ -27,65 +27,76 @@ struct Q8Side {
     int xh_bf16;
 };
 
+// Shared scratch of one 256-thread group
+struct Q8Scratch {
+    float a[8], v[8];
+    int i[8];
+};
+
+// Side outputs of value v, element t (0..255) of 256-value block b of the flattened vector. Every thread of the
+// 256-thread group calls it the same number of times (it synchronises the group twice); a thread past the end of the
+// vector passes active = false.
+__device__ __forceinline__ void q8_block_value(float v, bool active, long long b, int t, Q8Scratch& sh, const Q8Side& o) {
+    const int lane = t & 31, w = t >> 5;
+    const long long i = b * 256 + t;
+    if (o.xh && active) o.xh[i] = o.xh_bf16 ? to_bf16_bits(v) : __half_as_ushort(__float2half_rn(v));
+    if (!o.qK) return;  // uniform
+    const float a = active ? fabsf(v) : 0.0f;
+
+    float am = a;
+    for (int off = 16; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+    const float id0 = am != 0.0f ? __fdiv_rn(127.0f, am) : 0.0f;
+    const int q0 = active ? (int)rintf(__fmul_rn(v, id0)) : 0;
+    int sum0 = q0;
+    for (int off = 16; off > 0; off >>= 1) sum0 += __shfl_xor_sync(0xffffffffu, sum0, off);
+    if (active) {
+        o.q0[i] = (int8_t)q0;
+        if (lane == 0) {
+            const float d = __fdiv_rn(am, 127.0f);
+            o.d0[b * 8 + w] = __half2float(__float2half_rn(d));
+            o.s0[b * 8 + w] = __float_as_int(__half2float(__float2half_rn(__fmul_rn(d, (float)sum0))));
+        }
+    }
+
+    // largest |x| of the block, lowest index on ties
+    float ba = a, bv = v;
+    int bi = t;
+    for (int off = 16; off > 0; off >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, ba, off), ov = __shfl_xor_sync(0xffffffffu, bv, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (oa > ba || (oa == ba && oi < bi)) { ba = oa; bi = oi; bv = ov; }
+    }
+    if (lane == 0) { sh.a[w] = ba; sh.i[w] = bi; sh.v[w] = bv; }
+    __syncthreads();
+    float fa = sh.a[0], fv = sh.v[0];
+    int fi = sh.i[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k)
+        if (sh.a[k] > fa || (sh.a[k] == fa && sh.i[k] < fi)) { fa = sh.a[k]; fi = sh.i[k]; fv = sh.v[k]; }
+    __syncthreads();  // the scratch is reused by the next call
+    int q = 0;
+    float iscale = 0.0f;
+    if (fa != 0.0f) {
+        iscale = __fdiv_rn(-127.0f, fv);
+        q = min(127, (int)rintf(__fmul_rn(iscale, v)));
+    }
+    int s16 = q;
+    for (int off = 8; off > 0; off >>= 1) s16 += __shfl_xor_sync(0xffffffffu, s16, off);
+    if (active) {
+        o.qK[i] = (int8_t)q;
+        if (t == 0) o.dK[b] = fa != 0.0f ? __fdiv_rn(1.0f, iscale) : 0.0f;
+        if ((lane & 15) == 0) o.bsK[b * 16 + w * 2 + (lane >> 4)] = s16;
+    }
+}
+
 __global__ void __launch_bounds__(256)
 k_q8_side(const float* x, long long K, Q8Side o) {
-    __shared__ float s_a[8], s_v[8];
-    __shared__ int s_i[8];
-    const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+    __shared__ Q8Scratch sh;
     const long long nblk = (K + 255) / 256;
     for (long long b = blockIdx.x; b < nblk; b += gridDim.x) {
-        const long long i = b * 256 + t;
+        const long long i = b * 256 + threadIdx.x;
         const bool active = i < K;
-        const float v = active ? x[i] : 0.0f;
-        if (o.xh && active)
-            o.xh[i] = o.xh_bf16 ? to_bf16_bits(v) : __half_as_ushort(__float2half_rn(v));
-        if (!o.qK) continue;  // uniform
-        const float a = active ? fabsf(v) : 0.0f;
-
-        float am = a;
-        for (int off = 16; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
-        const float id0 = am != 0.0f ? __fdiv_rn(127.0f, am) : 0.0f;
-        const int q0 = active ? (int)rintf(__fmul_rn(v, id0)) : 0;
-        int sum0 = q0;
-        for (int off = 16; off > 0; off >>= 1) sum0 += __shfl_xor_sync(0xffffffffu, sum0, off);
-        if (active) {
-            o.q0[i] = (int8_t)q0;
-            if (lane == 0) {
-                const float d = __fdiv_rn(am, 127.0f);
-                o.d0[b * 8 + w] = __half2float(__float2half_rn(d));
-                o.s0[b * 8 + w] = __float_as_int(__half2float(__float2half_rn(__fmul_rn(d, (float)sum0))));
-            }
-        }
-
-        // largest |x| of the block, lowest index on ties
-        float ba = a, bv = v;
-        int bi = t;
-        for (int off = 16; off > 0; off >>= 1) {
-            const float oa = __shfl_xor_sync(0xffffffffu, ba, off), ov = __shfl_xor_sync(0xffffffffu, bv, off);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-            if (oa > ba || (oa == ba && oi < bi)) { ba = oa; bi = oi; bv = ov; }
-        }
-        if (lane == 0) { s_a[w] = ba; s_i[w] = bi; s_v[w] = bv; }
-        __syncthreads();
-        float fa = s_a[0], fv = s_v[0];
-        int fi = s_i[0];
-#pragma unroll
-        for (int k = 1; k < 8; ++k)
-            if (s_a[k] > fa || (s_a[k] == fa && s_i[k] < fi)) { fa = s_a[k]; fi = s_i[k]; fv = s_v[k]; }
-        __syncthreads();
-        int q = 0;
-        float iscale = 0.0f;
-        if (fa != 0.0f) {
-            iscale = __fdiv_rn(-127.0f, fv);
-            q = min(127, (int)rintf(__fmul_rn(iscale, v)));
-        }
-        int s16 = q;
-        for (int off = 8; off > 0; off >>= 1) s16 += __shfl_xor_sync(0xffffffffu, s16, off);
-        if (active) {
-            o.qK[i] = (int8_t)q;
-            if (t == 0) o.dK[b] = fa != 0.0f ? __fdiv_rn(1.0f, iscale) : 0.0f;
-            if ((lane & 15) == 0) o.bsK[b * 16 + w * 2 + (lane >> 4)] = s16;
-        }
+        q8_block_value(active ? x[i] : 0.0f, active, b, threadIdx.x, sh, o);
     }
 }
 
