@@ -61,6 +61,20 @@ cudaError_t gpu_add_rmsnorm(const float* x_in, const float* add, float* x_out, c
  * (n % 32 == 0 and n <= q8->max_k, else cudaErrorInvalidValue). */
 cudaError_t gpu_swiglu(const float* g, const float* u, float* out, int n, const qmatvec_q8* q8, cudaStream_t stream);
 
+/* src/gpu_ops.h:66-77, src/gpu_ops.cpp:115-122. Groups the T * n_used (token, slot) entries of ids [T][n_used] by
+ * expert for expert-tiled consumers: tok_rows[i] = token, pair_rows[i] = token * n_used + slot of the i-th entry in
+ * expert order (tok_rows / pair_rows: T * n_used ints); each expert's run cut into tiles of up to `tile` entries,
+ * tile_e / tile_start / tile_n (gpu_moe_max_tiles entries each), *n_tiles of them. n_expert <= 1024. Unlike the
+ * reference, the order inside an expert's run is fixed too (ascending pair index). */
+#ifndef GPU_OPS_H
+static inline int gpu_moe_max_tiles(int T, int n_used, int n_expert, int tile) {
+    const int n = T * n_used, bound = n_expert + n / tile;
+    return n < bound ? n : bound;
+}
+#endif
+cudaError_t gpu_moe_group(const int* ids, int T, int n_used, int n_expert, int tile, int* tok_rows, int* pair_rows,
+                          int* n_tiles, int* tile_e, int* tile_start, int* tile_n, cudaStream_t stream);
+
 /* ------------------------------------------------------------------------------------------------ Part 2 */
 
 /* bf16 storage (uint16_t bit patterns), fp32 arithmetic, one round-to-nearest-even per stored value (the rule of

@@ -31,6 +31,7 @@ SIGNATURES = {
     "gpu_ops_free": (None, []),
     "gpu_add_rmsnorm": (_i, [_p, _p, _p, _p, _p, _i, _i, _f, C.POINTER(qmatvec_q8), _p]),
     "gpu_swiglu": (_i, [_p, _p, _p, _i, C.POINTER(qmatvec_q8), _p]),
+    "gpu_moe_group": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p]),
     "gpu_add_rmsnorm_bf16": (_i, [_p, _p, _p, _p, _p, _i, _ll, _f, _p]),
     "gpu_add_rmsnorm_f32": (_i, [_p, _p, _p, _p, _p, _i, _ll, _f, _p]),
     "gpu_swiglu_bf16": (_i, [_p, _p, _p, _ll, _p]),

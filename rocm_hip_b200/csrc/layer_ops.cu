@@ -14,6 +14,7 @@
 #include <type_traits>
 
 #include "embed.cuh"
+#include "moe_group.cuh"
 #include "q8_side.cuh"
 #include "qk_norm_rope.cuh"
 #include "rmsnorm.cuh"
@@ -263,7 +264,10 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     int ppt = 0;
     if (D % VE == 0 && n_rot % (2 * VE) == 0 && (n_q == 0 || (al16(qfull) && al16(q_out))) &&
         (n_kv == 0 || (al16(k) && al16(k_out))) && (!q_norm || al16(q_norm)) && (!k_norm || al16(k_norm))) {
-        for (int c = 1; c <= 2 && !ppt; ++c)
+#ifndef B200_QK_PPT0
+#define B200_QK_PPT0 1
+#endif
+        for (int c = B200_QK_PPT0; c <= 2 && !ppt; ++c)
             if (NV % (2 * c) == 0) {
                 const int tph = NV / (2 * c);
                 if (tph <= 32 && (tph & (tph - 1)) == 0) ppt = c;
@@ -285,7 +289,10 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     // The trimmed kernel: one head chunk of exactly block threads, long batches, normalisation on, n_rot / 2 a
     // multiple of 4 floats (16-byte table reads). It takes the whole tiles of 4 tokens; the 0..3 tokens left over go
     // through the general kernel below (a row's bits do not depend on which of the two processed it).
-    constexpr int FTT = 4;
+#ifndef B200_QK_TT
+#define B200_QK_TT 4
+#endif
+    constexpr int FTT = B200_QK_TT;
     if (ppt == 1 && qk_norm && (n_q + n_kv) * tph == block && block <= 384 && T >= 8LL * sm_count() && n_rot > 0 &&
         (n_rot / 2) % 4 == 0) {
         const long long tiles = T / FTT;
@@ -394,6 +401,17 @@ cudaError_t gpu_swiglu(const float* g, const float* u, float* out, int n, const 
     const cudaError_t e = launch_swiglu<float, false>(g, u, out, n, stream);
     if (e != cudaSuccess || !q8 || n <= 0) return e;
     return launch_q8_side(out, n, q8, stream);
+}
+
+cudaError_t gpu_moe_group(const int* ids, int T, int n_used, int n_expert, int tile, int* tok_rows, int* pair_rows,
+                          int* n_tiles, int* tile_e, int* tile_start, int* tile_n, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || n_used <= 0 || n_expert <= 0 || n_expert > MOE_MAX_EXPERTS || tile <= 0 ||
+        (long long)T * n_used > INT_MAX)
+        return cudaErrorInvalidValue;
+    k_moe_group<<<1, 1024, 0, stream>>>(ids, T, n_used, n_expert, tile, tok_rows, pair_rows, n_tiles, tile_e, tile_start,
+                                        tile_n);
+    return launched();
 }
 
 cudaError_t gpu_add_rmsnorm_f32(const float* x_in, const float* add, float* x_out, const float* w, float* y, int n,

@@ -50,6 +50,14 @@ struct QkArgs {
 // multiply-add even when both carry .rn (measured: 26 % of results differ in the last bit), which it never does to
 // the scalar forms.
 __device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, float* hi) {
+#ifdef B200_SCALAR_ROT
+    float p0, p1, q0, q1, c0, c1, s0, s1;
+    upk2(x0, p0, p1); upk2(x1, q0, q1); upk2(c, c0, c1); upk2(s, s0, s1);
+    lo[0] = __fsub_rn(__fmul_rn(p0, c0), __fmul_rn(q0, s0));
+    lo[1] = __fsub_rn(__fmul_rn(p1, c1), __fmul_rn(q1, s1));
+    hi[0] = __fadd_rn(__fmul_rn(p0, s0), __fmul_rn(q0, c0));
+    hi[1] = __fadd_rn(__fmul_rn(p1, s1), __fmul_rn(q1, c1));
+#else
     float a0, a1, b0, b1, c0, c1, d0, d1;
     upk2(mul2(x0, c), a0, a1);
     upk2(mul2(x1, s), b0, b1);
@@ -59,6 +67,7 @@ __device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, flo
     lo[1] = __fsub_rn(a1, b1);
     hi[0] = __fadd_rn(c0, d0);
     hi[1] = __fadd_rn(c1, d1);
+#endif
 }
 
 // cos / sin of the angles of `nt` consecutive tokens starting at t0, spread over all threads of the CTA:
@@ -231,7 +240,7 @@ k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
 // tables (read with immediate offsets: no address arithmetic in the token loop).
 // Shared memory: [2 * D floats: q gamma, k gamma][2 passes x (cos, sin) x TT x n_rot / 2 floats].
 template <typename IO, int TT, bool FULL>
-__global__ void __launch_bounds__(384, 2)
+__global__ void __launch_bounds__(384, TT <= 2 ? 3 : 2)
 k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
     extern __shared__ __align__(16) float smem_all[];

@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows",
 ]
 
@@ -120,6 +120,19 @@ def gpu_swiglu_rows(gate, up, out, rows, h, gate_stride, up_stride):
     lib = _lib.load()
     fn = lib.gpu_swiglu_rows if gate.dtype == torch.float32 else lib.gpu_swiglu_rows_bf16
     _check("gpu_swiglu_rows", fn(_ptr(gate), _ptr(up), _ptr(out), rows, h, gate_stride, up_stride, _stream()))
+
+
+def gpu_moe_max_tiles(T, n_used, n_expert, tile):
+    """Entries tile_e / tile_start / tile_n need (src/gpu_ops.h:68-71)."""
+    n = T * n_used
+    return min(n, n_expert + n // tile)
+
+
+def gpu_moe_group(ids, T, n_used, n_expert, tile, tok_rows, pair_rows, n_tiles, tile_e, tile_start, tile_n):
+    """Group the (token, slot) entries of ids [T][n_used] (int32) by expert; all arguments int32 CUDA tensors."""
+    _check("gpu_moe_group", _lib.load().gpu_moe_group(_ptr(ids), T, n_used, n_expert, tile, _ptr(tok_rows),
+                                                      _ptr(pair_rows), _ptr(n_tiles), _ptr(tile_e), _ptr(tile_start),
+                                                      _ptr(tile_n), _stream()))
 
 
 def gpu_qk_norm_rope(qfull, k, q_norm, k_norm, q_out, k_out, n_q, n_kv, head_dim, n_rot, rot_pairs, positions, pos0, T,

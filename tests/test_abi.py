@@ -17,6 +17,7 @@ REF = "/root/reference"
 def declared_functions():
     src = open(HEADER).read()
     src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    src = re.sub(r"static inline[^{]*\{.*?\n\}", "", src, flags=re.S)   # header-only helpers are not exports
     return sorted(set(re.findall(r"\b(gpu_[a-z0-9_]+|b200_[a-z0-9_]+)\s*\(", src)))
 
 
