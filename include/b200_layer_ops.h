@@ -114,6 +114,16 @@ cudaError_t gpu_qk_norm_rope_bf16(const uint16_t* qfull, const uint16_t* k, cons
                                   int rot_pairs, const int* positions, int pos0, long long T, float freq_base,
                                   float eps, int gated, int qk_norm, const float* freq_factors, cudaStream_t stream);
 
+/* The K / V write of the reference's attn_prep kernels for an unquantised (FP16) cache (src/attention.hip:279-300):
+ * row t of src [T][n_vals] (n_vals = n_kv * head_dim; K after gpu_qk_norm_rope, V as projected) is rounded to fp16 and
+ * stored at cache + kv_row(pos_t), kv_row(p) = (p >> kv_shift) * kv_bstride + (p & ((1 << kv_shift) - 1)) * kv_stride
+ * in fp16 units (src/attention.hip:38-42; a contiguous cache has kv_shift = 30), pos_t = positions[t] or pos0 + t.
+ * cache is the layer's K (or V) row 0 (uint16_t = fp16 bits). 0 <= kv_shift <= 30, kv_stride >= n_vals. */
+cudaError_t gpu_kv_store_f16(const float* src, uint16_t* cache, int n_vals, const int* positions, int pos0, long long T,
+                             int kv_stride, int kv_shift, long long kv_bstride, cudaStream_t stream);
+cudaError_t gpu_kv_store_f16_bf16(const uint16_t* src, uint16_t* cache, int n_vals, const int* positions, int pos0,
+                                  long long T, int kv_stride, int kv_shift, long long kv_bstride, cudaStream_t stream);
+
 /* Token-embedding gather + dequantisation: out row t = decode(table row tokens[t]) * scale, the loop of
  * src/qwen_model.cpp:980-986 (scale: embd_scale of :1409; pass 1 for none). type: 8 (Q8_0) or 2 (Q4_0), the ggml
  * ids of src/quant_types.h:19-27; row_bytes as qt_row_size(type, E) or larger (a row stride); E % 32 == 0.

@@ -14,6 +14,7 @@
 #include <type_traits>
 
 #include "embed.cuh"
+#include "kv_store.cuh"
 #include "moe_group.cuh"
 #include "q8_side.cuh"
 #include "qk_norm_rope.cuh"
@@ -363,6 +364,22 @@ cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int voca
     return launched();
 }
 
+template <typename IO>
+cudaError_t launch_kv_store(const IO* src, __half* cache, int n_vals, const int* positions, int pos0, long long T,
+                            int kv_stride, int kv_shift, long long kv_bstride, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (!src || !cache || n_vals <= 0 || T <= 0 || kv_shift < 0 || kv_shift > 30 || kv_stride < n_vals || kv_bstride < 0 ||
+        (!positions && pos0 < 0))
+        return cudaErrorInvalidValue;
+    const bool vec = n_vals % 8 == 0 && al16(src) && al16(cache) && kv_stride % 8 == 0 && kv_bstride % 8 == 0;
+    const long long work = T * (vec ? n_vals / 8 : n_vals), cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    if (vec) k_kv_store_f16<IO, true><<<(unsigned)grid, 256, 0, stream>>>(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride);
+    else k_kv_store_f16<IO, false><<<(unsigned)grid, 256, 0, stream>>>(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride);
+    return launched();
+}
+
 }  // namespace
 
 // ================================================================ C ABI
@@ -466,6 +483,18 @@ cudaError_t gpu_qk_norm_rope_bf16(const uint16_t* qfull, const uint16_t* k, cons
                                     reinterpret_cast<__nv_bfloat16*>(q_out), reinterpret_cast<__nv_bfloat16*>(k_out),
                                     n_q, n_kv, head_dim, n_rot, rot_pairs, positions, pos0, T, freq_base, eps, gated,
                                     qk_norm, freq_factors, stream);
+}
+
+cudaError_t gpu_kv_store_f16(const float* src, uint16_t* cache, int n_vals, const int* positions, int pos0, long long T,
+                             int kv_stride, int kv_shift, long long kv_bstride, cudaStream_t stream) {
+    return launch_kv_store<float>(src, reinterpret_cast<__half*>(cache), n_vals, positions, pos0, T, kv_stride, kv_shift,
+                                  kv_bstride, stream);
+}
+
+cudaError_t gpu_kv_store_f16_bf16(const uint16_t* src, uint16_t* cache, int n_vals, const int* positions, int pos0,
+                                  long long T, int kv_stride, int kv_shift, long long kv_bstride, cudaStream_t stream) {
+    return launch_kv_store<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(src), reinterpret_cast<__half*>(cache),
+                                          n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, stream);
 }
 
 cudaError_t gpu_embed_rows(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens, float* out,

@@ -1,0 +1,82 @@
+"""gpu_kv_store_f16: K / V rows into the block-major FP16 cache with the reference's row addressing
+(src/attention.hip:38-42, src/kv_cache.h:7-14), bit-exact against a numpy statement; and the q/k norm + RoPE -> K row
+chain of attn_prep (src/attention.hip:286-299) against the oracle rounded to fp16."""
+import numpy as np
+import pytest
+import torch
+
+from rocm_hip_b200 import synth
+from util import dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def rows_of(pos, kv_stride, kv_shift, kv_bstride):
+    pos = np.asarray(pos, dtype=np.int64)
+    return (pos >> kv_shift) * kv_bstride + (pos & ((1 << kv_shift) - 1)) * kv_stride
+
+
+@pytest.mark.parametrize("n_vals,kv_shift,bf16", [(1024, 30, False), (1024, 4, False), (512, 3, True), (200, 2, False),
+                                                    (36, 30, True)])
+def test_rows_land_where_the_cache_layout_says(ops, oracle, n_vals, kv_shift, bf16):
+    T, n_layers = 77, 3
+    B = 1 << min(kv_shift, 7)
+    kv_stride = n_vals
+    kv_bstride = 2 * n_layers * B * n_vals if kv_shift < 30 else 0   # a block holds K and V of every layer
+    n_ctx = 256
+    size = int(rows_of([n_ctx - 1], kv_stride, kv_shift, kv_bstride)[0]) + n_vals
+    src = synth.normal(0, "kv.src", 0, T * n_vals).reshape(T, n_vals) * 4
+    want_rows = oracle.f32_to_f16(src)
+    d_src = dev(src)
+    if bf16:
+        b = oracle.f32_to_bf16(src).reshape(T, n_vals)
+        want_rows = oracle.f32_to_f16(oracle.bf16_to_f32(b))
+        d_src = dev(b, torch.bfloat16)
+    for positions, pos0 in ((None, 100), (synth.randint(0, "kv.pos", 0, T, 0, n_ctx).astype(np.int32), 0)):
+        if positions is not None:
+            positions = np.unique(positions).astype(np.int32)      # distinct rows
+        P = positions if positions is not None else np.arange(pos0, pos0 + T)
+        n = len(P)
+        cache = torch.full((size + 64,), -3.0, device="cuda", dtype=torch.float16)
+        ops.gpu_kv_store_f16(d_src, cache, n_vals, dev(positions) if positions is not None else None, pos0, n, kv_stride,
+                             kv_shift, kv_bstride)
+        torch.cuda.synchronize()
+        got = host(cache)
+        want = np.full(size + 64, np.float16(-3.0).view(np.uint16), dtype=np.uint16)
+        for t, r in enumerate(rows_of(P, kv_stride, kv_shift, kv_bstride)):
+            want[r:r + n_vals] = want_rows[t]
+        assert np.array_equal(got, want)
+
+
+def test_attn_prep_chain(ops, oracle):
+    """q/k norm + RoPE, then the K row and the V row into the cache, as attn_prep does in one kernel."""
+    T, nq, nkv, D, pos0 = 50, 8, 2, 128, 300
+    q = synth.normal(0, "ap.q", 0, T * nq * D).reshape(T, nq * D)
+    k = synth.normal(0, "ap.k", 0, T * nkv * D).reshape(T, nkv * D)
+    v = synth.normal(0, "ap.v", 0, T * nkv * D).reshape(T, nkv * D)
+    qn, kn = synth.normal(0, "ap.qn", 0, D, 1.0, 0.1), synth.normal(0, "ap.kn", 0, D, 1.0, 0.1)
+    wq, wk = oracle.qk_norm_rope(q, k, qn, kn, nq, nkv, D, D, 0, None, pos0, 1e6, 1e-6)
+    dq, dk, dv = dev(q), dev(k), dev(v)
+    q_out, k_rot = torch.zeros_like(dq), torch.zeros_like(dk)
+    n_ctx, d_kv = 512, nkv * D
+    K = torch.zeros(n_ctx * d_kv, device="cuda", dtype=torch.float16)
+    V = torch.zeros_like(K)
+    ops.gpu_qk_norm_rope(dq, dk, dev(qn), dev(kn), q_out, k_rot, nq, nkv, D, D, 0, None, pos0, T, 1e6, 1e-6)
+    ops.gpu_kv_store_f16(k_rot, K, d_kv, None, pos0, T, d_kv, 30, 0)
+    ops.gpu_kv_store_f16(dv, V, d_kv, None, pos0, T, d_kv, 30, 0)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(q_out).view(np.uint32), wq.view(np.uint32))
+    assert np.array_equal(host(K).reshape(n_ctx, d_kv)[pos0:pos0 + T], oracle.f32_to_f16(wk).reshape(T, d_kv))
+    assert np.array_equal(host(V).reshape(n_ctx, d_kv)[pos0:pos0 + T], oracle.f32_to_f16(v).reshape(T, d_kv))
+    assert not host(K).reshape(n_ctx, d_kv)[:pos0].any() and not host(K).reshape(n_ctx, d_kv)[pos0 + T:].any()
+
+
+def test_argument_errors(ops):
+    s = torch.zeros(4, 64, device="cuda")
+    c = torch.zeros(4096, device="cuda", dtype=torch.float16)
+    for kw in (dict(kv_shift=31), dict(kv_stride=32), dict(T=0), dict(pos0=-1)):
+        a = dict(kv_shift=30, kv_stride=64, T=4, pos0=0)
+        a.update(kw)
+        with pytest.raises(ops.LayerOpError) as e:
+            ops.gpu_kv_store_f16(s, c, 64, None, a["pos0"], a["T"], a["kv_stride"], a["kv_shift"], 0)
+        assert e.value.code == 1
