@@ -265,10 +265,7 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     int ppt = 0;
     if (D % VE == 0 && n_rot % (2 * VE) == 0 && (n_q == 0 || (al16(qfull) && al16(q_out))) &&
         (n_kv == 0 || (al16(k) && al16(k_out))) && (!q_norm || al16(q_norm)) && (!k_norm || al16(k_norm))) {
-#ifndef B200_QK_PPT0
-#define B200_QK_PPT0 1
-#endif
-        for (int c = B200_QK_PPT0; c <= 2 && !ppt; ++c)
+        for (int c = 1; c <= 2 && !ppt; ++c)
             if (NV % (2 * c) == 0) {
                 const int tph = NV / (2 * c);
                 if (tph <= 32 && (tph & (tph - 1)) == 0) ppt = c;
@@ -290,10 +287,7 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     // The trimmed kernel: one head chunk of exactly block threads, long batches, normalisation on, n_rot / 2 a
     // multiple of 4 floats (16-byte table reads). It takes the whole tiles of 4 tokens; the 0..3 tokens left over go
     // through the general kernel below (a row's bits do not depend on which of the two processed it).
-#ifndef B200_QK_TT
-#define B200_QK_TT 4
-#endif
-    constexpr int FTT = B200_QK_TT;
+    constexpr int FTT = 4;
     if (ppt == 1 && qk_norm && (n_q + n_kv) * tph == block && block <= 384 && T >= 8LL * sm_count() && n_rot > 0 &&
         (n_rot / 2) % 4 == 0) {
         const long long tiles = T / FTT;

@@ -50,14 +50,6 @@ struct QkArgs {
 // multiply-add even when both carry .rn (measured: 26 % of results differ in the last bit), which it never does to
 // the scalar forms.
 __device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, float* hi) {
-#ifdef B200_SCALAR_ROT
-    float p0, p1, q0, q1, c0, c1, s0, s1;
-    upk2(x0, p0, p1); upk2(x1, q0, q1); upk2(c, c0, c1); upk2(s, s0, s1);
-    lo[0] = __fsub_rn(__fmul_rn(p0, c0), __fmul_rn(q0, s0));
-    lo[1] = __fsub_rn(__fmul_rn(p1, c1), __fmul_rn(q1, s1));
-    hi[0] = __fadd_rn(__fmul_rn(p0, s0), __fmul_rn(q0, c0));
-    hi[1] = __fadd_rn(__fmul_rn(p1, s1), __fmul_rn(q1, c1));
-#else
     float a0, a1, b0, b1, c0, c1, d0, d1;
     upk2(mul2(x0, c), a0, a1);
     upk2(mul2(x1, s), b0, b1);
@@ -67,7 +59,6 @@ __device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, flo
     lo[1] = __fsub_rn(a1, b1);
     hi[0] = __fadd_rn(c0, d0);
     hi[1] = __fadd_rn(c1, d1);
-#endif
 }
 
 // cos / sin of the angles of `nt` consecutive tokens starting at t0, spread over all threads of the CTA:
