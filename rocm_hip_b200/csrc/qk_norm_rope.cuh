@@ -64,8 +64,13 @@ __device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, flo
 // cos / sin of the angles of `nt` consecutive tokens starting at t0, spread over all threads of the CTA:
 // cos_t / sin_t [token][n_rot / 2]. Pairs at or beyond rot_pairs get (1, 0): x0 * 1 - x1 * 0 is x0 to the bit, so the
 // rotation loop needs no per-pair test.
+//
+// chunk_lanes > 0 selects the layout the trimmed kernel reads without shared-memory bank conflicts: a lane owns VE
+// consecutive pairs and fetches them as 16-byte chunks of 4, so chunk c of lane l is stored at ((c * chunk_lanes + l) * 4)
+// within the token's row: the 8 lanes of a quarter-warp then read 128 contiguous bytes (natural order puts them 32
+// bytes apart, two lanes per bank). chunk_lanes = number of rotating lanes per head; ve = pairs per lane.
 __device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const QkArgs& a, const RopeFreq& fr,
-                                               long long t0, int nt) {
+                                               long long t0, int nt, int chunk_lanes = 0, int ve = 4) {
     const int half = a.n_rot >> 1, total = nt * half;
     for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
         const int tt = idx / half, i = idx - tt * half;
@@ -79,8 +84,13 @@ __device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const
             c = (float)dc;
             s = (float)ds;
         }
-        cos_t[idx] = c;
-        sin_t[idx] = s;
+        int at = idx;
+        if (chunk_lanes > 0) {
+            const int l = i / ve, r = i - l * ve;
+            at = tt * half + (((r >> 2) * chunk_lanes + l) << 2) + (r & 3);
+        }
+        cos_t[at] = c;
+        sin_t[at] = s;
     }
 }
 
@@ -242,15 +252,25 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     const double inv_n = 1.0 / (double)D;
     float* gam_s = smem_all;
     float* tab = smem_all + 2 * D;
+    constexpr int C = VE / 4;        // 16-byte chunks of 4 floats per vector's worth of gammas / pairs
+    // gammas in shared memory as [q | k][low vector, high vector][chunk][lane][4]: the lanes of a head read
+    // consecutive 16-byte chunks (no bank conflicts), each lane exactly the gammas of the two vectors it owns
     for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
-        const float* g = i < D ? a.q_norm : a.k_norm;
-        gam_s[i] = g[i < D ? i : i - D];
+        const int which = i / D, r = i - which * D;
+        const int hv = r / (D / 2), r2 = r - hv * (D / 2);
+        const int c = r2 / (tph * 4), r3 = r2 - c * (tph * 4);
+        const int ll = r3 >> 2, j = r3 & 3;
+        const bool lrot = FULL || ll < P;
+        const int vec = hv == 0 ? (lrot ? ll : R + (ll - P)) : (lrot ? ll + P : R + (ll - P) + (NV - R) / 2);
+        gam_s[i] = (which == 0 ? a.q_norm : a.k_norm)[vec * VE + 4 * c + j];
     }
     const bool rot = FULL || l < P;
     const int vlo = rot ? l : R + (l - P);
     const int vhi = rot ? l + P : R + (l - P) + (NV - R) / 2;
-    const ulonglong2* glo = reinterpret_cast<const ulonglong2*>(gam_s + (isq ? 0 : D) + vlo * VE);
-    const ulonglong2* ghi = reinterpret_cast<const ulonglong2*>(gam_s + (isq ? 0 : D) + vhi * VE);
+    // chunk c of the low vector's gammas at glo[c * tph], of the high vector's at ghi[c * tph]
+    const ulonglong2* glo = reinterpret_cast<const ulonglong2*>(gam_s + (isq ? 0 : D)) + l;
+    const ulonglong2* ghi = glo + C * tph;
+    const int PL = FULL ? tph : P;   // rotating lanes per head
     // this thread's place in a token row, in 16-byte vectors
     const unsigned in_vec = (unsigned)((isq ? (size_t)a.n_q * a.q_stride : (size_t)a.n_kv * D) / VE);
     const unsigned out_vec = (unsigned)((isq ? (size_t)a.n_q * D : (size_t)a.n_kv * D) / VE);
@@ -274,10 +294,10 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
         }
         float* cos_t = tab + flip * (2 * TT * half);
         float* sin_t = cos_t + TT * half;
-        tokens_cos_sin(cos_t, sin_t, a, fr, t0, TT);
+        tokens_cos_sin(cos_t, sin_t, a, fr, t0, TT, PL, VE);
         __syncthreads();
-        const ulonglong2* ct = reinterpret_cast<const ulonglong2*>(cos_t + vlo * VE);
-        const ulonglong2* st = reinterpret_cast<const ulonglong2*>(sin_t + vlo * VE);
+        const ulonglong2* ct = reinterpret_cast<const ulonglong2*>(cos_t) + l;   // chunk c of token tt: [(tt * half) / 4 + c * PL]
+        const ulonglong2* st = reinterpret_cast<const ulonglong2*>(sin_t) + l;
 #pragma unroll
         for (int tt = 0; tt < TT; ++tt) {
             f2 lo[NP], hi[NP];
@@ -292,7 +312,7 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
             const f2 inv2 = pk2(inv, inv);
 #pragma unroll
             for (int k = 0; k < NP; k += 2) {
-                const ulonglong2 gl = glo[k >> 1], gh = ghi[k >> 1];
+                const ulonglong2 gl = glo[(k >> 1) * tph], gh = ghi[(k >> 1) * tph];
                 lo[k] = mul2(mul2(lo[k], inv2), gl.x);
                 hi[k] = mul2(mul2(hi[k], inv2), gh.x);
                 lo[k + 1] = mul2(mul2(lo[k + 1], inv2), gl.y);
@@ -302,7 +322,7 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
             if (rot) {
 #pragma unroll
                 for (int k = 0; k < NP; k += 2) {
-                    const ulonglong2 c = ct[(tt * half) / 4 + (k >> 1)], sn = st[(tt * half) / 4 + (k >> 1)];
+                    const ulonglong2 c = ct[(tt * half) / 4 + (k >> 1) * PL], sn = st[(tt * half) / 4 + (k >> 1) * PL];
                     rotate2(lo[k], hi[k], c.x, sn.x, flo + 2 * k, fhi + 2 * k);
                     rotate2(lo[k + 1], hi[k + 1], c.y, sn.y, flo + 2 * k + 2, fhi + 2 * k + 2);
                 }
