@@ -162,7 +162,7 @@ k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                 }
             }
             if (!tables_done) {  // uniform over the CTA
-                tokens_cos_sin(cos_t, sin_t, a, fr, t0, nt);
+                tokens_cos_sin(cos_t, sin_t, a, fr, t0, nt, P, VE);   // lane-contiguous chunks (no bank conflicts)
                 __syncthreads();
                 tables_done = true;
             }
@@ -211,11 +211,12 @@ k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                         float flo[VE], fhi[VE];
                         if (rot[p]) {
                             // pairs vlo * VE .. + VE - 1 of this token's tables
-                            const ulonglong2* ct = reinterpret_cast<const ulonglong2*>(cos_t + tt * half + vlo[p] * VE);
-                            const ulonglong2* st = reinterpret_cast<const ulonglong2*>(sin_t + tt * half + vlo[p] * VE);
+                            // chunk c of rotating slot vlo: [(c * P + vlo) * 4] within the token's row
+                            const ulonglong2* ct = reinterpret_cast<const ulonglong2*>(cos_t + tt * half) + vlo[p];
+                            const ulonglong2* st = reinterpret_cast<const ulonglong2*>(sin_t + tt * half) + vlo[p];
 #pragma unroll
                             for (int k = 0; k < NP; k += 2) {
-                                const ulonglong2 c = ct[k >> 1], sn = st[k >> 1];
+                                const ulonglong2 c = ct[(k >> 1) * P], sn = st[(k >> 1) * P];
                                 rotate2(lo[p][k], hi[p][k], c.x, sn.x, flo + 2 * k, fhi + 2 * k);
                                 rotate2(lo[p][k + 1], hi[p][k + 1], c.y, sn.y, flo + 2 * k + 2, fhi + 2 * k + 2);
                             }
