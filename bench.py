@@ -56,48 +56,61 @@ from rocm_hip_b200.sharding import shard  # noqa: E402  (contiguous row range of
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """Samples SM clock and throttle reasons with nvidia-smi every 10 ms. It is started ahead of the warm-up (the tool
+    takes a moment to come up); mark() brackets the timed region and only samples taken inside it are reported (the
+    nearest ones if the region was shorter than a sampling interval)."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc = index, None
+        self.index, self.proc, self.t0, self.t1 = index, None, None, None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "10"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.12)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        import datetime
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), [n for n, v in zip(names, f[5:9]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        inside = [r for r in rows if self.t0 is not None and self.t0 <= r[0] <= self.t1]
+        if not inside and rows and self.t0 is not None:   # region shorter than an interval: the two nearest samples
+            mid = 0.5 * (self.t0 + self.t1)
+            inside = sorted(rows, key=lambda r: abs(r[0] - mid))[:2]
+        if not inside:
+            inside = rows
+        sm = [r[1] for r in inside]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(r[2] for r in inside) if inside else None,
+                "reasons": sorted({n for r in inside for n in r[3]}), "samples": len(inside)}
 
 
 # ------------------------------------------------------------------------------------------------ device workload
@@ -432,17 +445,19 @@ def main():
           for _ in range(args.steps)]
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
+    clocks = ClockSampler(local)
+    clocks.start()
     for _ in range(max(args.warmup, 3)):
         sw.step()
     launches0 = ops.launch_count()
-    clocks = ClockSampler(local)
     barrier()
-    clocks.start()
+    clocks.mark_begin()
     start.record()
     for i in range(args.steps):
         sw.step(ev[i])
     end.record()
     barrier()
+    clocks.mark_end()
     clk = clocks.stop()
     launches = ops.launch_count() - launches0
     ms_total = start.elapsed_time(end)
