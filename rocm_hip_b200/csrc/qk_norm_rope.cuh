@@ -69,7 +69,9 @@ __device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, flo
 // consecutive pairs and fetches them as 16-byte chunks of 4, so chunk c of lane l is stored at ((c * chunk_lanes + l) * 4)
 // within the token's row: the 8 lanes of a quarter-warp then read 128 contiguous bytes (natural order puts them 32
 // bytes apart, two lanes per bank). chunk_lanes = number of rotating lanes per head; ve = pairs per lane.
-__device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const QkArgs& a, const RopeFreq& fr,
+// inv_freq: the angle multipliers in SHARED memory. (Indexing the kernel-parameter copy with a per-thread index makes
+// the 32 lanes' constant-bank reads serialise: measured 0.15 of this kernel's time.)
+__device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const QkArgs& a, const double* inv_freq,
                                                long long t0, int nt, int chunk_lanes = 0, int ve = 4) {
     const int half = a.n_rot >> 1, total = nt * half;
     for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
@@ -77,7 +79,7 @@ __device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const
         float c = 1.0f, s = 0.0f;
         if (i < a.rot_pairs) {
             const int pos = a.positions ? a.positions[t0 + tt] : a.pos0 + (int)(t0 + tt);
-            double theta = (double)pos * fr.inv_freq[i];
+            double theta = (double)pos * inv_freq[i];
             if (a.ff) theta /= (double)a.ff[i];
             double ds, dc;
             sincos(theta, &ds, &dc);
@@ -94,6 +96,13 @@ __device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const
     }
 }
 
+// Copies the n_rot / 2 angle multipliers from the kernel parameters into shared memory (thread i reads entry i of the
+// parameter block: done once per CTA) and synchronises the CTA.
+__device__ __forceinline__ void stage_inv_freq(double* dst, const RopeFreq& fr, int half) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) dst[i] = fr.inv_freq[i];
+    __syncthreads();
+}
+
 // PPT: pairs of vectors per thread. Threads per head tph = D / VE / (2 PPT), a power of two <= 32.
 // TT: tokens per CTA pass. All of a pass's loads are issued before its cos / sin are computed, so TT * 2 PPT 16-byte
 // loads per thread are in flight while the double-precision sincos runs; the tables of the pass are shared by all heads.
@@ -105,6 +114,8 @@ __global__ void __launch_bounds__(384, 2)
 k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
     extern __shared__ __align__(16) float tab_all[];
+    __shared__ double invf[B200_MAX_ROT_PAIRS];
+    stage_inv_freq(invf, fr, a.n_rot >> 1);
     const int D = a.D, NV = D / VE, tph = NV / (2 * PPT);
     const int R = a.n_rot / VE;      // vectors in the rotary part
     const int P = R / 2;             // pairs of vectors (low half, high half)
@@ -162,7 +173,7 @@ k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                 }
             }
             if (!tables_done) {  // uniform over the CTA
-                tokens_cos_sin(cos_t, sin_t, a, fr, t0, nt, P, VE);   // lane-contiguous chunks (no bank conflicts)
+                tokens_cos_sin(cos_t, sin_t, a, invf, t0, nt, P, VE);   // lane-contiguous chunks (no bank conflicts)
                 __syncthreads();
                 tables_done = true;
             }
@@ -246,6 +257,8 @@ __global__ void __launch_bounds__(384, TT <= 2 ? 3 : 2)
 k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
     extern __shared__ __align__(16) float smem_all[];
+    __shared__ double invf[B200_MAX_ROT_PAIRS];
+    stage_inv_freq(invf, fr, a.n_rot >> 1);
     const int D = a.D, NV = D / VE, tph = NV / 2;
     const int R = a.n_rot / VE, P = R / 2, half = a.n_rot >> 1;
     const int l = threadIdx.x % tph, h = threadIdx.x / tph;
@@ -283,6 +296,10 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
 
     int flip = 0;
     const long long ntiles = a.T / TT;
+    // The tables of a tile are computed at the END of the pass before it (the first tile's here), into the buffer the
+    // pass before that used: the double-precision sincos then runs while none of a pass's loaded vectors are live, so
+    // its registers do not compete with them (computing the tables between the loads and their use cost 15 %).
+    if ((long long)blockIdx.x < ntiles) tokens_cos_sin(tab, tab + TT * half, a, invf, (long long)blockIdx.x * TT, TT, PL, VE);
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, flip ^= 1) {
         const long long t0 = tile * TT;
         const uint4* src = in_base + (size_t)t0 * in_vec;
@@ -295,8 +312,7 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
         }
         float* cos_t = tab + flip * (2 * TT * half);
         float* sin_t = cos_t + TT * half;
-        tokens_cos_sin(cos_t, sin_t, a, fr, t0, TT, PL, VE);
-        __syncthreads();
+        __syncthreads();   // this tile's tables (written at the end of the previous pass) are complete
         const ulonglong2* ct = reinterpret_cast<const ulonglong2*>(cos_t) + l;   // chunk c of token tt: [(tt * half) / 4 + c * PL]
         const ulonglong2* st = reinterpret_cast<const ulonglong2*>(sin_t) + l;
 #pragma unroll
@@ -337,6 +353,10 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
             st_stream(dst + (tt * out_vec + (unsigned)vlo), Io<IO>::pack(flo));
             st_stream(dst + (tt * out_vec + (unsigned)vhi), Io<IO>::pack(fhi));
         }
+        if (tile + gridDim.x < ntiles) {   // the other buffer was last read one pass ago, before this pass's barrier
+            float* ncos = tab + (flip ^ 1) * (2 * TT * half);
+            tokens_cos_sin(ncos, ncos + TT * half, a, invf, (tile + gridDim.x) * TT, TT, PL, VE);
+        }
     }
 }
 
@@ -347,6 +367,8 @@ template <typename IO>
 __global__ void __launch_bounds__(128)
 k_qk_norm_rope_generic(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     __shared__ float cos_t[B200_MAX_ROT_PAIRS], sin_t[B200_MAX_ROT_PAIRS];
+    __shared__ double invf[B200_MAX_ROT_PAIRS];
+    stage_inv_freq(invf, fr, a.n_rot >> 1);
     __shared__ float v[1024];
     __shared__ double part[2][32];
     const int D = a.D, half = a.n_rot / 2, heads = a.n_q + a.n_kv;
@@ -354,7 +376,7 @@ k_qk_norm_rope_generic(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     int flip = 0;
     for (long long t = blockIdx.x; t < a.T; t += gridDim.x) {
         __syncthreads();  // the previous token's tables and head are no longer read
-        tokens_cos_sin(cos_t, sin_t, a, fr, t, 1);
+        tokens_cos_sin(cos_t, sin_t, a, invf, t, 1);
         for (int h = 0; h < heads; ++h) {
             const bool isq = h < a.n_q;
             const IO* src = isq ? static_cast<const IO*>(a.qfull) + ((size_t)t * a.n_q + h) * a.q_stride
