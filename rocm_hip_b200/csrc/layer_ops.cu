@@ -288,7 +288,8 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     // multiple of 4 floats (16-byte table reads). It takes the whole tiles of 4 tokens; the 0..3 tokens left over go
     // through the general kernel below (a row's bits do not depend on which of the two processed it).
     constexpr int FTT = 4;
-    if (ppt == 1 && qk_norm && (n_q + n_kv) * tph == block && block <= 384 && T >= 8LL * sm_count() && n_rot > 0 &&
+    // (no frequency factors and a base >= 1: every angle is then below 2^31, the range of the kernel's own sincos)
+    if (ppt == 1 && qk_norm && !ff && freq_base >= 1.0f && (n_q + n_kv) * tph == block && block <= 384 && T >= 8LL * sm_count() && n_rot > 0 &&
         (n_rot / 2) % 4 == 0) {
         const long long tiles = T / FTT;
         const size_t smem = (2 * (size_t)D + 2 * 2 * FTT * (size_t)(n_rot / 2)) * sizeof(float);

@@ -69,8 +69,41 @@ __device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, flo
 // consecutive pairs and fetches them as 16-byte chunks of 4, so chunk c of lane l is stored at ((c * chunk_lanes + l) * 4)
 // within the token's row: the 8 lanes of a quarter-warp then read 128 contiguous bytes (natural order puts them 32
 // bytes apart, two lanes per bank). chunk_lanes = number of rotating lanes per head; ve = pairs per lane.
+// sin and cos of a double-precision angle, 0 <= |x| < 2^32 * pi/2 (every int32 position times a multiplier <= 1), without
+// the library routine's large-argument path (whose local array and register needs weigh on the whole kernel):
+// k = rint(x * 2/pi); r = x - k * pi/2 with pi/2 split into three 21-bit pieces and a tail, so every k * piece product
+// is exact for |k| < 2^32 (Cody-Waite); then the classic degree-13 / degree-14 minimax polynomials on [-pi/4, pi/4]
+// (the coefficients of fdlibm's __kernel_sin / __kernel_cos), each below one ulp. Rounded to float the results are
+// those of the CPU reference's libm except when the exact value lies within ~2 double ulps of a float rounding tie.
+__device__ __forceinline__ void sincos_cw(double x, double* sn, double* cs) {
+    const double k = rint(x * 0.6366197723675814);
+    double r = fma(-k, 1.570796012878418, x);          // 0x1.921fb00000000p+0
+    r = fma(-k, 3.139164164167596e-07, r);             // 0x1.5110b00000000p-22
+    r = fma(-k, 6.22337468017542e-14, r);              // 0x1.1846a00000000p-44
+    r = fma(-k, -2.508278806334166e-20, r);            // tail of pi/2
+    const double z = r * r;
+    double ps = fma(z, 1.58969099521155010221e-10, -2.50507602534068634195e-08);
+    ps = fma(z, ps, 2.75573137070700676789e-06);
+    ps = fma(z, ps, -1.98412698298579493134e-04);
+    ps = fma(z, ps, 8.33333333332248946124e-03);
+    ps = fma(z, ps, -1.66666666666666324348e-01);
+    const double s = fma(z * r, ps, r);
+    double pc = fma(z, -1.13596475577881948265e-11, 2.08757232129817482790e-09);
+    pc = fma(z, pc, -2.75573143513906633035e-07);
+    pc = fma(z, pc, 2.48015872894767294178e-05);
+    pc = fma(z, pc, -1.38888888888741095749e-03);
+    pc = fma(z, pc, 4.16666666666666019037e-02);
+    const double c = 1.0 - fma(-(z * z), pc, 0.5 * z);
+    const int q = (int)((long long)k & 3);
+    *sn = (q & 1) ? c : s;
+    *cs = (q & 1) ? s : c;
+    if (q == 1 || q == 2) *cs = -*cs;
+    if (q >= 2) *sn = -*sn;
+}
+
 // inv_freq: the angle multipliers in SHARED memory. (Indexing the kernel-parameter copy with a per-thread index makes
 // the 32 lanes' constant-bank reads serialise: measured 0.15 of this kernel's time.)
+template <bool FAST_TRIG = false>
 __device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const QkArgs& a, const double* inv_freq,
                                                long long t0, int nt, int chunk_lanes = 0, int ve = 4) {
     const int half = a.n_rot >> 1, total = nt * half;
@@ -82,7 +115,8 @@ __device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const
             double theta = (double)pos * inv_freq[i];
             if (a.ff) theta /= (double)a.ff[i];
             double ds, dc;
-            sincos(theta, &ds, &dc);
+            if (FAST_TRIG) sincos_cw(theta, &ds, &dc);   // (the launcher guarantees |theta| < 2^31 here)
+            else sincos(theta, &ds, &dc);
             c = (float)dc;
             s = (float)ds;
         }
@@ -299,7 +333,7 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     // The tables of a tile are computed at the END of the pass before it (the first tile's here), into the buffer the
     // pass before that used: the double-precision sincos then runs while none of a pass's loaded vectors are live, so
     // its registers do not compete with them (computing the tables between the loads and their use cost 15 %).
-    if ((long long)blockIdx.x < ntiles) tokens_cos_sin(tab, tab + TT * half, a, invf, (long long)blockIdx.x * TT, TT, PL, VE);
+    if ((long long)blockIdx.x < ntiles) tokens_cos_sin<true>(tab, tab + TT * half, a, invf, (long long)blockIdx.x * TT, TT, PL, VE);
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, flip ^= 1) {
         const long long t0 = tile * TT;
         const uint4* src = in_base + (size_t)t0 * in_vec;
@@ -355,7 +389,7 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
         }
         if (tile + gridDim.x < ntiles) {   // the other buffer was last read one pass ago, before this pass's barrier
             float* ncos = tab + (flip ^ 1) * (2 * TT * half);
-            tokens_cos_sin(ncos, ncos + TT * half, a, invf, (tile + gridDim.x) * TT, TT, PL, VE);
+            tokens_cos_sin<true>(ncos, ncos + TT * half, a, invf, (tile + gridDim.x) * TT, TT, PL, VE);
         }
     }
 }
