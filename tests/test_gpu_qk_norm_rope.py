@@ -65,6 +65,26 @@ def test_c5_heads_and_far_positions(ops, oracle):
     assert run(ops, oracle, pos.size, 4, 2, 128, 128, 1e6, positions=pos) <= 1e-5
 
 
+@pytest.mark.parametrize("pos0", [0, 123456789, 2**30, 2**31 - 1501])
+def test_tile_kernel_trig_over_the_whole_position_range(ops, oracle, pos0):
+    """Long batches take the tile kernel, which evaluates sin / cos itself (Cody-Waite reduction with exact products
+    for every int32 position): 1e-5 must hold from position 0 to the last int32 position, fp32 and bf16, and the
+    results are in fact the CPU reference's bits (a handful of last-bit differences would still be legitimate)."""
+    T, nq, nkv, D = 1500, 4, 2, 128
+    q = synth.normal(9, "far.q", 0, T * nq * D).reshape(T, nq * D)
+    k = synth.normal(9, "far.k", 0, T * nkv * D).reshape(T, nkv * D)
+    qn, kn = synth.normal(9, "far.qn", 0, D, 1.0, 0.1), synth.normal(9, "far.kn", 0, D, 1.0, 0.1)
+    wq, wk = oracle.qk_norm_rope(q, k, qn, kn, nq, nkv, D, D, 0, None, pos0, 1e6, 1e-6)
+    qo, ko = torch.zeros(T, nq * D, device="cuda"), torch.zeros(T, nkv * D, device="cuda")
+    ops.gpu_qk_norm_rope(dev(q), dev(k), dev(qn), dev(kn), qo, ko, nq, nkv, D, D, 0, None, pos0, T, 1e6, 1e-6)
+    torch.cuda.synchronize()
+    assert max_rel_rows(host(qo).reshape(-1, D), wq.reshape(-1, D)) <= 1e-5
+    assert max_rel_rows(host(ko).reshape(-1, D), wk.reshape(-1, D)) <= 1e-5
+    differing = int((host(qo).view(np.uint32) != wq.view(np.uint32)).sum())
+    assert differing <= 8, differing
+    assert run(ops, oracle, T, nq, nkv, D, D, 1e6, pos0=pos0, bf16=True, seed=9) <= 1
+
+
 @pytest.mark.parametrize("D,n_rot", [(64, 64), (128, 64), (128, 128), (256, 256), (512, 512), (512, 128), (96, 32),
                                      (80, 80), (128, 20), (256, 0)])
 def test_head_shapes(ops, oracle, D, n_rot):
