@@ -192,6 +192,33 @@ cudaError_t b200_host_qk_norm_rope(b200_host_ctx* ctx, int elem, const void* qfu
 cudaError_t b200_host_embed_rows(b200_host_ctx* ctx, int elem, int type, const void* table_dev, size_t row_bytes,
                                  int vocab, const int32_t* tokens, void* out, int E, long long T, float scale);
 
+/* ------------------------------------------------------------------------------------------------ Part 4 */
+
+/* From a GGUF file to a device-resident table. The reference maps the file and lets kernels read weights in place
+ * from unified memory (src/gguf_mmap.h:15-17; QuantWeight::row, src/inference_internal.h:33-40); here the mapping is
+ * the source of one upload. A reader of the container layout only (GGUF version 2 / 3; no split files). Tensor byte
+ * sizes are known for F32 (0), F16 (1), Q4_0 (2), Q8_0 (8), BF16 (30); tensors of other types are listed with
+ * nbytes 0 and cannot be uploaded. b200_gguf_open returns NULL for a missing, truncated or malformed file. */
+typedef struct b200_gguf b200_gguf;
+b200_gguf* b200_gguf_open(const char* path);
+void b200_gguf_close(b200_gguf* g);
+long long b200_gguf_n_tensors(const b200_gguf* g);
+unsigned b200_gguf_version(const b200_gguf* g);
+size_t b200_gguf_alignment(const b200_gguf* g);      /* general.alignment, default 32 */
+size_t b200_gguf_data_offset(const b200_gguf* g);    /* file offset of the data section */
+int b200_gguf_find_tensor(const b200_gguf* g, const char* name);   /* index, or -1 */
+/* Any out pointer may be NULL. ne: 4 extents (1 beyond n_dims); row_bytes: bytes of ne[0] values (qt_row_size);
+ * host_data: the tensor's bytes inside the read-only mapping (valid until b200_gguf_close). Returns 0, or -1. */
+int b200_gguf_tensor_info(const b200_gguf* g, int idx, const char** name, int* type, int* n_dims, long long ne[4],
+                          size_t* row_bytes, size_t* nbytes, const void** host_data);
+int b200_gguf_kv_u32(const b200_gguf* g, const char* key, uint32_t* out);   /* 0, or -1 if absent / other type */
+int b200_gguf_kv_f32(const b200_gguf* g, const char* key, float* out);
+long long b200_gguf_kv_str(const b200_gguf* g, const char* key, char* buf, size_t cap);   /* length, or -1 */
+/* Allocates device memory for tensor idx (this is a loader: it does allocate), queues the copy on `stream`, and
+ * returns the device pointer; release it with b200_gguf_free_tensor. The mapping must stay open until the copy ran. */
+cudaError_t b200_gguf_upload_tensor(const b200_gguf* g, int idx, void** dev_ptr, cudaStream_t stream);
+void b200_gguf_free_tensor(void* dev_ptr);
+
 /* Number of kernel launches this library has issued since it was loaded (all launchers, all threads) */
 unsigned long long b200_launch_count(void);
 /* "sm_100a" and the like: the architecture the kernels were compiled for */

@@ -54,6 +54,20 @@ SIGNATURES = {
     "b200_host_swiglu": (_i, [_p, _i, _p, _p, _p, _ll, _i]),
     "b200_host_qk_norm_rope": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p]),
     "b200_host_embed_rows": (_i, [_p, _i, _i, _p, _sz, _i, _p, _p, _i, _ll, _f]),
+    "b200_gguf_open": (_p, [C.c_char_p]),
+    "b200_gguf_close": (None, [_p]),
+    "b200_gguf_n_tensors": (_ll, [_p]),
+    "b200_gguf_version": (C.c_uint, [_p]),
+    "b200_gguf_alignment": (_sz, [_p]),
+    "b200_gguf_data_offset": (_sz, [_p]),
+    "b200_gguf_find_tensor": (_i, [_p, C.c_char_p]),
+    "b200_gguf_tensor_info": (_i, [_p, _i, C.POINTER(C.c_char_p), C.POINTER(_i), C.POINTER(_i), C.POINTER(_ll * 4),
+                                   C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_p)]),
+    "b200_gguf_kv_u32": (_i, [_p, C.c_char_p, C.POINTER(C.c_uint32)]),
+    "b200_gguf_kv_f32": (_i, [_p, C.c_char_p, C.POINTER(_f)]),
+    "b200_gguf_kv_str": (_ll, [_p, C.c_char_p, C.c_char_p, _sz]),
+    "b200_gguf_upload_tensor": (_i, [_p, _i, C.POINTER(_p), _p]),
+    "b200_gguf_free_tensor": (None, [_p]),
     "b200_launch_count": (C.c_ulonglong, []),
     "b200_build_arch": (C.c_char_p, []),
 }
