@@ -32,8 +32,6 @@ __device__ __forceinline__ void st_stream(void* p, const uint4& v) {
                  : "memory");
 }
 
-__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
 // ---------------------------------------------------------------- storage types
 
 // bf16 <-> fp32. Widening is exact; narrowing is round-to-nearest-even, the same rule as the integer formula

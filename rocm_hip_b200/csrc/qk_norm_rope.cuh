@@ -7,12 +7,16 @@
 // double product pos * inv_freq[i] with inv_freq built on the host by the CPU reference's own expression, and
 // cos / sin are evaluated in double and rounded once: that is what holds 1e-5 at positions in the hundreds of thousands.
 //
-// One CTA pass handles one token: all of its n_q + n_kv heads. A head of D values is NV = D / VE 16-byte vectors,
-// owned by NV / (2 PPT) threads. Each thread owns PPT pairs of vectors; a rotating thread owns the vector of a
-// rotation pair's low half and the vector of its high half, so the rotation needs no exchange, the row is read
-// once and written once (2 D s bytes per head), and the sum of squares is a shuffle reduction inside the head's lanes.
-// The token's cos / sin (n_rot / 2 each) are computed once by the first threads, while the loads are in flight, and
-// shared by all heads through shared memory.
+// A CTA pass handles a tile of consecutive tokens (4 in long batches): all of their n_q + n_kv heads. A head of D
+// values is NV = D / VE 16-byte vectors, owned by NV / (2 PPT) threads. Each thread owns PPT pairs of vectors; a
+// rotating thread owns the vector of a rotation pair's low half and the vector of its high half, so the rotation
+// needs no exchange, the row is read once and written once (2 D s bytes per head), and the sum of squares is a
+// shuffle reduction inside the head's lanes. A tile's cos / sin (n_rot / 2 each per token) are computed once, in
+// double, into shared memory and shared by all heads.
+// Three kernels: k_qk_norm_rope_fast (long batches of the usual shapes: everything static, gammas and tables in
+// bank-conflict-free shared-memory layouts, the next tile's tables computed at the end of a pass, its own sincos);
+// k_qk_norm_rope (any vectorisable shape, any batch length, frequency factors); k_qk_norm_rope_generic (any head
+// size and alignment, scalar).
 
 #ifndef B200_QK_NORM_ROPE_CUH
 #define B200_QK_NORM_ROPE_CUH

@@ -11,11 +11,14 @@
 // Layout: rows [T][n] contiguous. A row is read exactly once with 16-byte loads, VPT vectors per thread, kept packed
 // in registers (so that many loads are in flight per thread at little register cost), reduced, scaled and written
 // with 16-byte stores: 2 n s bytes per row without add, 4 n s with (s = bytes per value), the algorithmic minimum.
-// The gammas are re-read per row through the read-only path and stay in L1. Two shapes:
-//   * rows of up to 32 * VPT vectors: a lane group of tpr <= 32 threads per row, several rows per CTA, shuffles only;
-//   * wider rows: one CTA of tpr threads per row (tpr a multiple of 32), one shared-memory exchange per row.
-// The launcher picks (tpr, VPT) from n and the storage type alone, never from T or the grid, so the summation
-// order of a row is fixed. CTAs walk rows with a grid stride.
+// Three kernels:
+//   * k_add_rmsnorm_fast: the model-norm shapes (one CTA per row, the row exactly tpr * VPT vectors, fp32 or bf16,
+//     gammas given): gammas in registers, packed fp32 math;
+//   * k_add_rmsnorm: every other vectorisable shape: a lane group of tpr <= 32 threads per row (several rows per
+//     CTA, shuffles only) or one CTA per row; gammas re-read per row through the read-only path;
+//   * k_add_rmsnorm_generic: any width and alignment, scalar accesses.
+// The launcher picks kernel, tpr and VPT from n and the storage type alone, never from T or the grid, so the
+// summation order of a row is fixed. CTAs walk rows with a grid stride.
 
 #ifndef B200_RMSNORM_CUH
 #define B200_RMSNORM_CUH

@@ -4,7 +4,7 @@
 //
 // A flat elementwise map over n = rows * width values (dense FFN rows or expert-grouped rows: the order of rows does
 // not matter to it), 3 s bytes per value. Each thread moves UNROLL 16-byte vectors of g and of u per step so that
-// enough loads are in flight to cover HBM latency; the grid is a whole number of waves of resident CTAs.
+// enough loads are in flight to cover HBM latency; CTAs walk tiles of 256 * UNROLL vectors with a grid stride.
 //
 // fp32 rows use the accurate expf and an IEEE division (within ~2 ulp of the CPU reference). 16-bit rows use
 // ex2.approx and rcp.approx: their ~1e-6 relative error is far inside half a bf16 ulp (2e-3), so the rounded result
