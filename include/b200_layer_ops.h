@@ -192,6 +192,27 @@ cudaError_t b200_host_qk_norm_rope(b200_host_ctx* ctx, int elem, const void* qfu
 cudaError_t b200_host_embed_rows(b200_host_ctx* ctx, int elem, int type, const void* table_dev, size_t row_bytes,
                                  int vocab, const int32_t* tokens, void* out, int E, long long T, float scale);
 
+/* The same over several GPUs of one box from one process: rows are cut into contiguous ranges, one per device, and
+ * one host thread per device runs the single-device call on its range; nothing is exchanged between devices and a
+ * row gets the bits one device would give it. n_devices <= 0: all visible devices. tables_dev: one device pointer
+ * per device of the group (the table replicated, in device order). */
+typedef struct b200_host_group b200_host_group;
+b200_host_group* b200_host_group_create(int n_devices, size_t slot_bytes, int n_slots);   /* NULL on failure */
+void b200_host_group_destroy(b200_host_group* grp);
+int b200_host_group_size(const b200_host_group* grp);
+cudaError_t b200_host_group_add_rmsnorm(b200_host_group* grp, int elem, const void* x_in, const void* add, void* x_out,
+                                        const float* w, void* y, int n, long long T, float eps);
+cudaError_t b200_host_group_swiglu(b200_host_group* grp, int elem, const void* g, const void* u, void* out, long long rows,
+                                   int width);
+cudaError_t b200_host_group_qk_norm_rope(b200_host_group* grp, int elem, const void* qfull, const void* k,
+                                         const float* q_norm, const float* k_norm, void* q_out, void* k_out, int n_q,
+                                         int n_kv, int head_dim, int n_rot, int rot_pairs, const int* positions, int pos0,
+                                         long long T, float freq_base, float eps, int gated, int qk_norm,
+                                         const float* freq_factors);
+cudaError_t b200_host_group_embed_rows(b200_host_group* grp, int elem, int type, const void* const* tables_dev,
+                                       size_t row_bytes, int vocab, const int32_t* tokens, void* out, int E, long long T,
+                                       float scale);
+
 /* ------------------------------------------------------------------------------------------------ Part 4 */
 
 /* From a GGUF file to a device-resident table. The reference maps the file and lets kernels read weights in place

@@ -241,3 +241,121 @@ cudaError_t b200_host_embed_rows(b200_host_ctx* ctx, int elem, int type, const v
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Row sharding over several GPUs from ONE process: a group owns one host-buffer context per device; an operation
+// cuts the rows into contiguous ranges (device g gets rows [T g / G, T (g + 1) / G)), and one host thread per device
+// runs the single-device call on its range. Rows are independent, so nothing is exchanged between devices and each
+// row gets the bits a single device would give it. Small read-only inputs (gammas, frequency factors) are copied to
+// every device by the per-device call; the embedding table must already be resident on every device.
+
+#include <thread>
+
+struct b200_host_group {
+    std::vector<b200_host_ctx*> ctx;
+};
+
+namespace {
+
+template <class F>
+cudaError_t for_each_device(b200_host_group* grp, long long T, F fn) {
+    const int G = (int)grp->ctx.size();
+    std::vector<cudaError_t> err((size_t)G, cudaSuccess);
+    std::vector<std::thread> th;
+    for (int g = 0; g < G; ++g) {
+        const long long lo = T * g / G, hi = T * (g + 1) / G;
+        if (hi <= lo) continue;
+        th.emplace_back([&, g, lo, hi] { err[(size_t)g] = fn(grp->ctx[(size_t)g], g, lo, hi - lo); });
+    }
+    for (auto& t : th) t.join();
+    for (cudaError_t e : err)
+        if (e != cudaSuccess) return e;
+    return cudaSuccess;
+}
+
+inline const char* at(const void* p, size_t bytes) { return p ? (const char*)p + bytes : nullptr; }
+inline char* at(void* p, size_t bytes) { return p ? (char*)p + bytes : nullptr; }
+
+}  // namespace
+
+extern "C" {
+
+b200_host_group* b200_host_group_create(int n_devices, size_t slot_bytes, int n_slots) {
+    int have = 0;
+    if (cudaGetDeviceCount(&have) != cudaSuccess || have < 1) return nullptr;
+    if (n_devices <= 0) n_devices = have;
+    if (n_devices > have) return nullptr;
+    int prev = 0;
+    (void)cudaGetDevice(&prev);
+    b200_host_group* grp = new (std::nothrow) b200_host_group;
+    if (!grp) return nullptr;
+    for (int d = 0; d < n_devices; ++d) {
+        b200_host_ctx* c = cudaSetDevice(d) == cudaSuccess ? b200_host_ctx_create(slot_bytes, n_slots) : nullptr;
+        if (!c) {
+            (void)cudaSetDevice(prev);
+            b200_host_group_destroy(grp);
+            return nullptr;
+        }
+        grp->ctx.push_back(c);
+    }
+    (void)cudaSetDevice(prev);
+    return grp;
+}
+
+void b200_host_group_destroy(b200_host_group* grp) {
+    if (!grp) return;
+    for (b200_host_ctx* c : grp->ctx) b200_host_ctx_destroy(c);
+    delete grp;
+}
+
+int b200_host_group_size(const b200_host_group* grp) { return grp ? (int)grp->ctx.size() : 0; }
+
+cudaError_t b200_host_group_add_rmsnorm(b200_host_group* grp, int elem, const void* x_in, const void* add, void* x_out,
+                                        const float* w, void* y, int n, long long T, float eps) {
+    if (!grp || T <= 0 || n <= 0 || (elem != 2 && elem != 4)) return cudaErrorInvalidValue;
+    const size_t bpr = (size_t)n * elem;
+    return for_each_device(grp, T, [=](b200_host_ctx* c, int, long long lo, long long rows) {
+        return b200_host_add_rmsnorm(c, elem, at(x_in, lo * bpr), at(add, lo * bpr), at(x_out, lo * bpr), w, at(y, lo * bpr), n,
+                                     rows, eps);
+    });
+}
+
+cudaError_t b200_host_group_swiglu(b200_host_group* grp, int elem, const void* g, const void* u, void* out, long long rows,
+                                   int width) {
+    if (!grp || rows <= 0 || width <= 0 || (elem != 2 && elem != 4)) return cudaErrorInvalidValue;
+    const size_t bpr = (size_t)width * elem;
+    return for_each_device(grp, rows, [=](b200_host_ctx* c, int, long long lo, long long r) {
+        return b200_host_swiglu(c, elem, at(g, lo * bpr), at(u, lo * bpr), at(out, lo * bpr), r, width);
+    });
+}
+
+cudaError_t b200_host_group_qk_norm_rope(b200_host_group* grp, int elem, const void* qfull, const void* k,
+                                         const float* q_norm, const float* k_norm, void* q_out, void* k_out, int n_q,
+                                         int n_kv, int head_dim, int n_rot, int rot_pairs, const int* positions, int pos0,
+                                         long long T, float freq_base, float eps, int gated, int qk_norm,
+                                         const float* freq_factors) {
+    if (!grp || T <= 0 || head_dim <= 0 || (elem != 2 && elem != 4)) return cudaErrorInvalidValue;
+    const size_t qi = (size_t)n_q * (gated ? 2 : 1) * head_dim * elem, qo = (size_t)n_q * head_dim * elem,
+                 kb = (size_t)n_kv * head_dim * elem;
+    return for_each_device(grp, T, [=](b200_host_ctx* c, int, long long lo, long long rows) {
+        return b200_host_qk_norm_rope(c, elem, at(qfull, lo * qi), at(k, lo * kb), q_norm, k_norm, at(q_out, lo * qo),
+                                      at(k_out, lo * kb), n_q, n_kv, head_dim, n_rot, rot_pairs,
+                                      positions ? positions + lo : nullptr, positions ? 0 : pos0 + (int)lo, rows, freq_base,
+                                      eps, gated, qk_norm, freq_factors);
+    });
+}
+
+cudaError_t b200_host_group_embed_rows(b200_host_group* grp, int elem, int type, const void* const* tables_dev,
+                                       size_t row_bytes, int vocab, const int32_t* tokens, void* out, int E, long long T,
+                                       float scale) {
+    if (!grp || !tables_dev || !tokens || T <= 0 || E <= 0 || (elem != 2 && elem != 4)) return cudaErrorInvalidValue;
+    for (long long t = 0; t < T; ++t)   // refuse before any device starts (src/qwen_model.cpp:981)
+        if (tokens[t] < 0 || tokens[t] >= vocab) return cudaErrorInvalidValue;
+    const size_t bpr = (size_t)E * elem;
+    return for_each_device(grp, T, [=](b200_host_ctx* c, int g, long long lo, long long rows) {
+        return b200_host_embed_rows(c, elem, type, tables_dev[g], row_bytes, vocab, tokens + lo, at(out, lo * bpr), E, rows,
+                                    scale);
+    });
+}
+
+}  // extern "C"

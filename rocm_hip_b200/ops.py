@@ -14,7 +14,7 @@ from . import _lib
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
     "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
-    "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows",
+    "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
 ]
 
 QT_Q4_0 = 2  # ggml type ids, src/quant_types.h:19-27 of the reference
@@ -232,3 +232,46 @@ class HostRows:
         h = self._h
         _check("b200_host_embed_rows", self._lib.b200_host_embed_rows(
             self._ctx, self._elem(out), qtype, _ptr(table_dev), row_bytes, vocab, h(tokens), h(out), E, T, scale))
+
+
+class HostGroup(HostRows):
+    """The same host-buffer calls over several GPUs of one box from one process (b200_host_group_*): rows are cut into
+    contiguous ranges, one per device, and one host thread per device streams its range. embed_rows takes one CUDA
+    table per device, in device order."""
+
+    def __init__(self, n_devices=0, slot_bytes=64 << 20, n_slots=4):
+        self._lib = _lib.load()
+        self._ctx = self._lib.b200_host_group_create(n_devices, slot_bytes, n_slots)
+        if not self._ctx:
+            raise LayerOpError("b200_host_group_create", -1)
+        self.size = self._lib.b200_host_group_size(self._ctx)
+
+    def close(self):
+        if self._ctx:
+            self._lib.b200_host_group_destroy(self._ctx)
+            self._ctx = None
+
+    def add_rmsnorm(self, x_in, add, x_out, w, y, n, T, eps):
+        h = self._h
+        _check("b200_host_group_add_rmsnorm", self._lib.b200_host_group_add_rmsnorm(
+            self._ctx, self._elem(x_in), h(x_in), h(add), h(x_out), h(w), h(y), n, T, eps))
+
+    def swiglu(self, g, u, out, rows, width):
+        h = self._h
+        _check("b200_host_group_swiglu",
+               self._lib.b200_host_group_swiglu(self._ctx, self._elem(g), h(g), h(u), h(out), rows, width))
+
+    def qk_norm_rope(self, qfull, k, q_norm, k_norm, q_out, k_out, n_q, n_kv, head_dim, n_rot, rot_pairs, positions,
+                     pos0, T, freq_base, eps, gated=0, qk_norm=1, freq_factors=None):
+        h = self._h
+        ref = qfull if qfull is not None else k
+        _check("b200_host_group_qk_norm_rope", self._lib.b200_host_group_qk_norm_rope(
+            self._ctx, self._elem(ref), h(qfull), h(k), h(q_norm), h(k_norm), h(q_out), h(k_out), n_q, n_kv, head_dim,
+            n_rot, rot_pairs, h(positions), pos0, T, freq_base, eps, gated, qk_norm, h(freq_factors)))
+
+    def embed_rows(self, qtype, tables_dev, row_bytes, vocab, tokens, out, E, T, scale=1.0):
+        h = self._h
+        assert len(tables_dev) == self.size
+        ptrs = (C.c_void_p * self.size)(*[t.data_ptr() for t in tables_dev])
+        _check("b200_host_group_embed_rows", self._lib.b200_host_group_embed_rows(
+            self._ctx, self._elem(out), qtype, ptrs, row_bytes, vocab, h(tokens), h(out), E, T, scale))
