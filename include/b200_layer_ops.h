@@ -124,6 +124,16 @@ cudaError_t gpu_kv_store_f16(const float* src, uint16_t* cache, int n_vals, cons
 cudaError_t gpu_kv_store_f16_bf16(const uint16_t* src, uint16_t* cache, int n_vals, const int* positions, int pos0,
                                   long long T, int kv_stride, int kv_shift, long long kv_bstride, cudaStream_t stream);
 
+/* The same write for a quantised cache (kv_quant 1: Q8_0, 2: Q4_0; kvq_store, src/attention.hip:159-178, row layout
+ * :44-50): a row holds d_row values and then one fp16 scale per 32; kv_stride (still in fp16 units) = d_row * 17 / 32
+ * (Q8_0) or d_row * 9 / 32 (Q4_0). Q8_0: d = amax / 127, q = rint(x / d). Q4_0: d = m / -8 (m the value of largest
+ * magnitude), nibble = min(15, (int)(x / d + 8.5)), byte 4 j + k holding values 8 j + k (low) and 8 j + k + 4 (high).
+ * n_vals % 32 == 0 and n_vals <= d_row (the reference's caches have d_row % 256 == 0, src/kv_cache.cpp:123). */
+cudaError_t gpu_kv_store_q(const float* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
+                           int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream);
+cudaError_t gpu_kv_store_q_bf16(const uint16_t* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
+                                int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream);
+
 /* Token-embedding gather + dequantisation: out row t = decode(table row tokens[t]) * scale, the loop of
  * src/qwen_model.cpp:980-986 (scale: embd_scale of :1409; pass 1 for none). type: 8 (Q8_0) or 2 (Q4_0), the ggml
  * ids of src/quant_types.h:19-27; row_bytes as qt_row_size(type, E) or larger (a row stride); E % 32 == 0.

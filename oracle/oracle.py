@@ -235,6 +235,31 @@ def quantize_q8(x, xh=None, int8=True):
     return o
 
 
+def kv_quant_rows(x, kq):
+    """Quantised KV cache rows of x [T][n_vals] fp32 (n_vals % 32 == 0), by the reference's kvq_store
+    (src/attention.hip:159-178; row layout :44-50), every float32 operation rounded on its own. Returns (values,
+    scales): kq 1 (Q8_0) int8 [T][n_vals], kq 2 (Q4_0) uint8 [T][n_vals / 2] with byte 4 j + k holding values 8 j + k
+    (low nibble) and 8 j + k + 4 (high); scales are fp16 bit patterns [T][n_vals / 32]."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    T, n = x.shape
+    b = x.reshape(T, n // 32, 32)
+    one = np.float32(1.0)
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        amax = np.abs(b).max(axis=2, keepdims=True)
+        if kq == 1:
+            d = amax / np.float32(127.0)
+            q = np.where(d != 0, b * (one / d), np.float32(0.0)).astype(np.float32)
+            vals = np.rint(q).astype(np.int32).astype(np.int8).reshape(T, n)
+        else:
+            m = np.where(np.abs(b) == amax, b, -np.inf).astype(np.float32).max(axis=2, keepdims=True)
+            d = (m / np.float32(-8.0)).astype(np.float32)
+            v = np.where(d != 0, (b * (one / d)).astype(np.float32) + np.float32(8.5), np.float32(8.0)).astype(np.float32)
+            nib = np.minimum(15, v.astype(np.int32)).astype(np.uint8).reshape(T, n // 8, 8)   # (int) truncates
+            vals = (nib[:, :, :4] | (nib[:, :, 4:] << 4)).astype(np.uint8).reshape(T, n // 2)
+        scales = f32_to_f16(d.reshape(T, n // 32)).reshape(T, n // 32)   # a huge scale overflows to inf, as __float2half
+    return vals, scales
+
+
 class Lcg:
     """The reference tests' generator (tests/layernorm_verify.cpp:29-33)."""
 

@@ -42,6 +42,8 @@ SIGNATURES = {
     "gpu_qk_norm_rope_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_kv_store_f16": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _p]),
     "gpu_kv_store_f16_bf16": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _p]),
+    "gpu_kv_store_q": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _i, _p]),
+    "gpu_kv_store_q_bf16": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _i, _p]),
     "gpu_embed_rows": (_i, [_i, _p, _sz, _i, _p, _p, _i, _ll, _f, _p, _p]),
     "gpu_embed_rows_bf16": (_i, [_i, _p, _sz, _i, _p, _p, _i, _ll, _f, _p, _p]),
     "gpu_embed_rows_host_ids": (_i, [_i, _p, _sz, _i, _p, _p, _p, _i, _ll, _f, _p, _p]),

@@ -155,6 +155,15 @@ struct Io2<__nv_bfloat16> {
     }
 };
 
+// Four fp32 values (two packed pairs) rounded to bf16 or fp16 and stored as one 8-byte vector
+__device__ __forceinline__ void st_half4(uint16_t* p, f2 v01, f2 v23, int bf16) {
+    float a, b, c, d;
+    upk2(v01, a, b);
+    upk2(v23, c, d);
+    const uint2 r = bf16 ? make_uint2(pack_bf16(a, b), pack_bf16(c, d)) : make_uint2(pack_f16(a, b), pack_f16(c, d));
+    asm volatile("st.global.L1::no_allocate.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(r.x), "r"(r.y) : "memory");
+}
+
 // sum += a^2 + b^2 of a packed pair, in double
 __device__ __forceinline__ void sumsq2(f2 v, double& s0, double& s1) {
     float a, b;

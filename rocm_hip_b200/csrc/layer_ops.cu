@@ -119,9 +119,12 @@ cudaError_t launch_norm_vec(const NormPlan& p, const IO* x_in, const IO* add, IO
     return launched();
 }
 
+// xh (fp32 rows): the 16-bit side copy of y, written by the producer itself when the row shape takes the trimmed
+// kernel; *xh_done says whether it was (else the caller runs the side kernel).
 template <typename IO, typename WT>
 cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int n, long long T,
-                               float eps, cudaStream_t stream) {
+                               float eps, cudaStream_t stream, uint16_t* xh = nullptr, int xh_bf16 = 0,
+                               bool* xh_done = nullptr) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (T <= 0 || n <= 0 || !x_in || !y || (add && (!x_out || x_out == x_in))) return cudaErrorInvalidValue;
     constexpr int VE = Io<IO>::VE;
@@ -138,6 +141,23 @@ cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const W
         k_add_rmsnorm_fast<IO, V, A, M><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps); \
     } while (0)
 #define NORM_FAST(V, A) do { if (p.tpr <= 160) NORM_FAST2(V, A, 160); else NORM_FAST2(V, A, 512); } while (0)
+            if constexpr (std::is_same<IO, float>::value) {
+                if (xh && (reinterpret_cast<uintptr_t>(xh) & 7) == 0) {
+#define NORM_XH2(V, A, M)                                                                             \
+    do {                                                                                              \
+        long long grid = persistent_grid(k_add_rmsnorm_fast<IO, V, A, M, true>, p.tpr, 0);            \
+        if (grid > T) grid = T;                                                                       \
+        k_add_rmsnorm_fast<IO, V, A, M, true><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, xh, xh_bf16); \
+    } while (0)
+#define NORM_XH(V, A) do { if (p.tpr <= 160) NORM_XH2(V, A, 160); else NORM_XH2(V, A, 512); } while (0)
+                    if (p.vpt == 4) { if (add) NORM_XH(4, true); else NORM_XH(4, false); }
+                    else { if (add) NORM_XH(2, true); else NORM_XH(2, false); }
+#undef NORM_XH2
+#undef NORM_XH
+                    if (xh_done) *xh_done = true;
+                    return launched();
+                }
+            }
             if (p.vpt == 4) { if (add) NORM_FAST(4, true); else NORM_FAST(4, false); }
             else { if (add) NORM_FAST(2, true); else NORM_FAST(2, false); }
 #undef NORM_FAST2
@@ -168,7 +188,8 @@ cudaError_t launch_q8_side(const float* x, long long K, const qmatvec_q8* q8, cu
 // ---------------------------------------------------------------- SwiGLU
 
 template <typename IO, bool FAST>
-cudaError_t launch_swiglu(const IO* g, const IO* u, IO* out, long long n, cudaStream_t stream) {
+cudaError_t launch_swiglu(const IO* g, const IO* u, IO* out, long long n, cudaStream_t stream, uint16_t* xh = nullptr,
+                          int xh_bf16 = 0, bool* xh_done = nullptr) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (n < 0 || (n > 0 && (!g || !u || !out))) return cudaErrorInvalidValue;
     if (n == 0) return cudaSuccess;
@@ -179,6 +200,13 @@ cudaError_t launch_swiglu(const IO* g, const IO* u, IO* out, long long n, cudaSt
         const long long cap = resident_ctas(256) * 8;
         if (grid > cap) grid = cap;
         if (grid < 1) grid = 1;
+        if constexpr (std::is_same<IO, float>::value) {
+            if (xh && n % VE == 0 && (reinterpret_cast<uintptr_t>(xh) & 7) == 0) {
+                k_swiglu<IO, FAST, UNROLL, true><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n, xh, xh_bf16);
+                if (xh_done) *xh_done = true;
+                return launched();
+            }
+        }
         k_swiglu<IO, FAST, UNROLL><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n);
     } else {
         const long long cap = resident_ctas(256) * 8;
@@ -375,6 +403,30 @@ cudaError_t launch_kv_store(const IO* src, __half* cache, int n_vals, const int*
     return launched();
 }
 
+template <typename IO>
+cudaError_t launch_kv_store_q(const IO* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
+                              int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (!src || !cache || n_vals <= 0 || n_vals % 32 != 0 || T <= 0 || kv_shift < 0 || kv_shift > 30 || kv_stride <= 0 ||
+        kv_bstride < 0 || (!positions && pos0 < 0) || (kv_quant != 1 && kv_quant != 2))
+        return cudaErrorInvalidValue;
+    // the row must hold n_vals values and their scales: d_row = kv_stride * 32 / 17 (or / 9), as src/attention.hip:50
+    const long long d_row = (long long)kv_stride * 32 / (kv_quant == 2 ? 9 : 17);
+    const long long need = kv_quant == 2 ? d_row / 2 + n_vals / 32 * 2 : d_row + n_vals / 32 * 2;
+    if (n_vals > d_row || need > (long long)kv_stride * 2 || (kv_quant == 2 ? d_row / 2 : d_row) % 2 != 0)
+        return cudaErrorInvalidValue;
+    constexpr int U = 4;
+    const long long nblk = T * (n_vals / 32), cap = resident_ctas(256) * 4;
+    long long grid = (nblk + 8 * U - 1) / (8 * U);
+    if (grid > cap) grid = cap;
+    __half* c = reinterpret_cast<__half*>(cache);
+    if (kv_quant == 1)
+        k_kv_store_q<IO, 1, U><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride);
+    else
+        k_kv_store_q<IO, 2, U><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride);
+    return launched();
+}
+
 }  // namespace
 
 // ================================================================ C ABI
@@ -402,17 +454,27 @@ cudaError_t gpu_add_rmsnorm(const float* x_in, const float* add, float* x_out, c
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (T <= 0 || (q8 && (n % 256 != 0 || (long long)n * T > q8->max_k)) || (add && x_out == x_in))
         return cudaErrorInvalidValue;
-    const cudaError_t e = launch_add_rmsnorm<float, float>(x_in, add, x_out, w, y, n, T, eps, stream);
+    // the 16-bit copy is written by the norm kernel itself where the row shape allows; what is left (the int8
+    // formats, or the copy for the other shapes) is one more pass over y
+    bool xh_done = false;
+    const cudaError_t e = launch_add_rmsnorm<float, float>(x_in, add, x_out, w, y, n, T, eps, stream,
+                                                           q8 ? (uint16_t*)q8->xh : nullptr, q8 ? q8->xh_bf16 : 0, &xh_done);
     if (e != cudaSuccess || !q8) return e;
-    return launch_q8_side(y, (long long)n * T, q8, stream);
+    qmatvec_q8 rest = *q8;
+    if (xh_done) rest.xh = nullptr;
+    return launch_q8_side(y, (long long)n * T, &rest, stream);
 }
 
 cudaError_t gpu_swiglu(const float* g, const float* u, float* out, int n, const qmatvec_q8* q8, cudaStream_t stream) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (q8 && (n % 32 != 0 || n > q8->max_k)) return cudaErrorInvalidValue;
-    const cudaError_t e = launch_swiglu<float, false>(g, u, out, n, stream);
+    bool xh_done = false;
+    const cudaError_t e = launch_swiglu<float, false>(g, u, out, n, stream, q8 ? (uint16_t*)q8->xh : nullptr,
+                                                      q8 ? q8->xh_bf16 : 0, &xh_done);
     if (e != cudaSuccess || !q8 || n <= 0) return e;
-    return launch_q8_side(out, n, q8, stream);
+    qmatvec_q8 rest = *q8;
+    if (xh_done) rest.xh = nullptr;
+    return launch_q8_side(out, n, &rest, stream);
 }
 
 cudaError_t gpu_moe_group(const int* ids, int T, int n_used, int n_expert, int tile, int* tok_rows, int* pair_rows,
@@ -490,6 +552,17 @@ cudaError_t gpu_kv_store_f16_bf16(const uint16_t* src, uint16_t* cache, int n_va
                                   long long T, int kv_stride, int kv_shift, long long kv_bstride, cudaStream_t stream) {
     return launch_kv_store<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(src), reinterpret_cast<__half*>(cache),
                                           n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, stream);
+}
+
+cudaError_t gpu_kv_store_q(const float* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
+                           int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream) {
+    return launch_kv_store_q<float>(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, kv_quant, stream);
+}
+
+cudaError_t gpu_kv_store_q_bf16(const uint16_t* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
+                                int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream) {
+    return launch_kv_store_q<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(src), cache, n_vals, positions, pos0, T,
+                                            kv_stride, kv_shift, kv_bstride, kv_quant, stream);
 }
 
 cudaError_t gpu_embed_rows(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens, float* out,

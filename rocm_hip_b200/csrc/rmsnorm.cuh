@@ -104,9 +104,14 @@ k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int 
 // each lane rounded as the scalar instruction would. Same summation order as k_add_rmsnorm is NOT promised: a row
 // width always maps to the same kernel, so a row's bits are still a function of the row alone.
 // MAXT: largest CTA the instance is launched with; small CTAs are held to 96 registers so that four fit an SM.
-template <typename IO, int VPT, bool HAS_ADD, int MAXT>
+// XH (fp32 rows only): y is also written rounded to bf16 (xh_bf16) or fp16 into xh, the 16-bit side copy the
+// reference's producers write for their matmul consumers (src/q8_device.h:37-43,58): 2 more bytes per value written
+// instead of a second kernel that reads y again.
+template <typename IO, int VPT, bool HAS_ADD, int MAXT, bool XH = false>
 __global__ void __launch_bounds__(MAXT, MAXT <= 160 ? 4 : 1)
-k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO* y, int n, long long T, float eps) {
+k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO* y, int n, long long T, float eps,
+                   uint16_t* xh = nullptr, int xh_bf16 = 0) {
+    static_assert(!XH || sizeof(IO) == 4, "the 16-bit side copy belongs to fp32 rows");
     constexpr int NP = Io2<IO>::NP;
     // fp32 rows: every square goes into a double sum, which makes 1/rms, and with it y, the CPU reference's to the bit.
     // 16-bit rows: a thread's own 16 or 32 squares (each exact in fp32) are summed in two packed fp32 chains and only
@@ -199,6 +204,7 @@ k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO*
 #pragma unroll
             for (int k = 0; k < NP; ++k) v[k] = mul2(mul2(v[k], inv2), gam[j][k]);
             st_stream(py + off + j * tpr, Io2<IO>::pack(v));
+            if (XH) st_half4(xh + (off + j * tpr + l) * 4, v[0], v[NP > 1 ? 1 : 0], xh_bf16);
         }
     }
 }

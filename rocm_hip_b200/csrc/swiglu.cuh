@@ -55,10 +55,12 @@ __device__ __forceinline__ f2 silu_mul2(f2 g, f2 u) {
 
 // Each CTA walks tiles of 256 * UNROLL vectors; inside a tile a thread's vectors are at tile + k * 256 + tid, so the
 // per-access index arithmetic is 32-bit and only the tile base is 64-bit. All UNROLL loads of g and of u are issued
-// before the first use.
-template <typename IO, bool FAST, int UNROLL>
+// before the first use. XH (fp32 rows, n a multiple of 4): out is also written rounded to bf16 (xh_bf16) or fp16 into
+// xh, the 16-bit side copy of the reference's producers (src/q8_device.h:37-43,58).
+template <typename IO, bool FAST, int UNROLL, bool XH = false>
 __global__ void __launch_bounds__(256)
-k_swiglu(const IO* g, const IO* u, IO* out, long long n) {
+k_swiglu(const IO* g, const IO* u, IO* out, long long n, uint16_t* xh = nullptr, int xh_bf16 = 0) {
+    static_assert(!XH || sizeof(IO) == 4, "the 16-bit side copy belongs to fp32 rows");
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
     const long long nvec = n / VE;
     constexpr int TILE = 256 * UNROLL;
@@ -84,6 +86,7 @@ k_swiglu(const IO* g, const IO* u, IO* out, long long n) {
 #pragma unroll
                 for (int e = 0; e < NP; ++e) a[e] = silu_mul2<FAST>(a[e], b[e]);
                 st_stream(po + k * 256, Io2<IO>::pack(a));
+                if (XH) st_half4(xh + (v0 + threadIdx.x + k * 256) * 4, a[0], a[NP > 1 ? 1 : 0], xh_bf16);
             }
         } else {
 #pragma unroll
@@ -95,6 +98,7 @@ k_swiglu(const IO* g, const IO* u, IO* out, long long n) {
 #pragma unroll
                     for (int e = 0; e < NP; ++e) a[e] = silu_mul2<FAST>(a[e], b[e]);
                     st_stream(po + k * 256, Io2<IO>::pack(a));
+                    if (XH) st_half4(xh + (v0 + threadIdx.x + k * 256) * 4, a[0], a[NP > 1 ? 1 : 0], xh_bf16);
                 }
             }
         }

@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
 ]
 
@@ -128,6 +128,15 @@ def gpu_kv_store_f16(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift
     fn = lib.gpu_kv_store_f16 if src.dtype == torch.float32 else lib.gpu_kv_store_f16_bf16
     _check("gpu_kv_store_f16", fn(_ptr(src), _ptr(cache), n_vals, _ptr(positions), pos0, T, kv_stride, kv_shift,
                                   kv_bstride, _stream()))
+
+
+def gpu_kv_store_q(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, kv_quant):
+    """Rows of src (fp32 or bf16) quantised to Q8_0 (kv_quant 1) or Q4_0 (2) into the block-major KV cache `cache`
+    (a CUDA tensor of any 16-bit or byte dtype; kv_stride / kv_bstride in 2-byte units)."""
+    lib = _lib.load()
+    fn = lib.gpu_kv_store_q if src.dtype == torch.float32 else lib.gpu_kv_store_q_bf16
+    _check("gpu_kv_store_q", fn(_ptr(src), _ptr(cache), n_vals, _ptr(positions), pos0, T, kv_stride, kv_shift,
+                                kv_bstride, kv_quant, _stream()))
 
 
 def gpu_moe_max_tiles(T, n_used, n_expert, tile):

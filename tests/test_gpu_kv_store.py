@@ -80,3 +80,57 @@ def test_argument_errors(ops):
         with pytest.raises(ops.LayerOpError) as e:
             ops.gpu_kv_store_f16(s, c, 64, None, a["pos0"], a["T"], a["kv_stride"], a["kv_shift"], 0)
         assert e.value.code == 1
+
+
+def _quant_case(oracle, T, n_vals, bf16):
+    src = synth.normal(0, "kvq.src", 0, T * n_vals).reshape(T, n_vals) * 3
+    src[1, :32] = 0.0                                   # d == 0: zeros (Q8_0), nibble 8 (Q4_0)
+    src[2, 32:64] = np.linspace(-2, 2, 32, dtype=np.float32)   # +- tie of the largest magnitude: the positive one wins
+    src[3, 0] = 1e30                                    # one huge value: everything else quantises to the middle
+    src[4, 64:96] = -np.abs(src[4, 64:96])              # all negative: d > 0 for Q4_0
+    if bf16:
+        b = oracle.f32_to_bf16(src).reshape(T, n_vals)
+        return oracle.bf16_to_f32(b).reshape(T, n_vals), dev(b, torch.bfloat16)
+    return src, dev(src)
+
+
+@pytest.mark.parametrize("kq", [1, 2])
+@pytest.mark.parametrize("n_vals,kv_shift,bf16", [(1024, 30, False), (1024, 4, False), (512, 3, True), (256, 30, True)])
+def test_quantised_rows_bit_exact(ops, oracle, kq, n_vals, kv_shift, bf16):
+    """Q8_0 / Q4_0 cache rows: values, nibble packing, scales and their place in the row, byte for byte; bytes outside
+    the written rows keep their fill."""
+    T, n_layers, n_ctx = 61, 2, 256
+    B = 1 << min(kv_shift, 7)
+    kv_stride = n_vals * (17 if kq == 1 else 9) // 32            # in 2-byte units
+    kv_bstride = 2 * n_layers * B * kv_stride if kv_shift < 30 else 0
+    size = int(rows_of([n_ctx - 1], kv_stride, kv_shift, kv_bstride)[0]) + kv_stride
+    vals, d_src = _quant_case(oracle, T, n_vals, bf16)
+    want_q, want_d = oracle.kv_quant_rows(vals, kq)
+    vbytes = n_vals if kq == 1 else n_vals // 2
+    for positions, pos0 in ((None, 100), (np.unique(synth.randint(0, "kvq.pos", 0, T, 0, n_ctx)).astype(np.int32), 0)):
+        P = positions if positions is not None else np.arange(pos0, pos0 + T)
+        n = len(P)
+        cache = torch.full((size + 64,), 0x5A5A, device="cuda", dtype=torch.int16)
+        ops.gpu_kv_store_q(d_src, cache, n_vals, dev(positions) if positions is not None else None, pos0, n, kv_stride,
+                           kv_shift, kv_bstride, kq)
+        torch.cuda.synchronize()
+        got = cache.cpu().numpy().view(np.uint8)
+        want = np.full((size + 64) * 2, 0x5A, dtype=np.uint8)
+        for t, r in enumerate(rows_of(P, kv_stride, kv_shift, kv_bstride)):
+            want[2 * r:2 * r + vbytes] = want_q[t].view(np.uint8)
+            want[2 * r + vbytes:2 * r + vbytes + n_vals // 16] = want_d[t].view(np.uint8)
+        assert np.array_equal(got, want)
+
+
+def test_quantised_argument_errors(ops):
+    s = torch.zeros(4, 256, device="cuda")
+    c = torch.zeros(4096, device="cuda", dtype=torch.int16)
+    ok = dict(n_vals=256, kv_stride=136, kq=1)
+    for kw in (dict(kq=0), dict(kq=3), dict(n_vals=48), dict(kv_stride=135), dict(kv_stride=72), dict(kq=2, kv_stride=71)):
+        a = dict(ok)
+        a.update(kw)
+        with pytest.raises(ops.LayerOpError) as e:
+            ops.gpu_kv_store_q(s, c, a["n_vals"], None, 0, 4, a["kv_stride"], 30, 0, a["kq"])
+        assert e.value.code == 1
+    ops.gpu_kv_store_q(s, c, 256, None, 0, 4, 72, 30, 0, 2)     # the Q4_0 row of 256 values is 72 halves
+    torch.cuda.synchronize()

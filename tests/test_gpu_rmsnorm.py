@@ -166,6 +166,36 @@ def test_q8_side_outputs(ops, oracle):
     assert e.value.code == 1
 
 
+@pytest.mark.parametrize("n,T", [(4096, 33), (1024, 300), (2560, 17)])
+def test_16_bit_side_copy_comes_from_the_norm_kernel_itself(ops, oracle, n, T):
+    """A qmatvec_q8 that asks only for the 16-bit copy (src/q8_device.h:58): xh = y rounded to bf16 / fp16, written by
+    the one norm launch when the row shape takes the trimmed kernel; with the int8 formats also wanted, or without
+    gammas, one more launch; the bits are the same either way."""
+    x = synth.normal(3, "xh.x", 0, T * n).reshape(T, n)
+    a = synth.normal(3, "xh.a", 0, T * n).reshape(T, n)
+    w = synth.normal(3, "xh.w", 0, n, 1.0, 0.1)
+    dx, da, dw = dev(x), dev(a), dev(w)
+    for kind in ("bf16", "f16"):
+        conv = oracle.f32_to_bf16 if kind == "bf16" else oracle.f32_to_f16
+        for add in (None, da):
+            q8 = ops.Q8Buffers(T * n, "cuda", xh=kind, int8=False)
+            y, xo, y_plain = torch.empty_like(dx), torch.empty_like(dx), torch.empty_like(dx)
+            before = ops.launch_count()
+            ops.gpu_add_rmsnorm(dx, add, xo, dw, y, n, T, 1e-6, q8=q8)
+            assert ops.launch_count() - before == 1
+            ops.gpu_add_rmsnorm(dx, add, xo, dw, y_plain, n, T, 1e-6)
+            torch.cuda.synchronize()
+            assert np.array_equal(host(y).view(np.uint32), host(y_plain).view(np.uint32))
+            assert np.array_equal(host(q8.xh).view(np.uint16), conv(host(y)).reshape(-1))
+        q8 = ops.Q8Buffers(T * n, "cuda", xh=kind, int8=False)
+        y = torch.empty_like(dx)
+        before = ops.launch_count()
+        ops.gpu_add_rmsnorm(dx, None, dx, None, y, n, T, 1e-6, q8=q8)       # no gammas: the general kernel + side kernel
+        torch.cuda.synchronize()
+        assert ops.launch_count() - before == 2
+        assert np.array_equal(host(q8.xh).view(np.uint16), conv(host(y)).reshape(-1))
+
+
 def test_argument_errors(ops):
     """src/gpu_ops.cpp:68-70: not initialised -> cudaErrorInvalidDeviceFunction (98); T <= 0 or add with
     x_out == x_in -> cudaErrorInvalidValue (1). Nothing is launched in either case."""

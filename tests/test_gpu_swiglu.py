@@ -143,3 +143,22 @@ def test_q8_side_outputs(ops, oracle):
     with pytest.raises(ops.LayerOpError) as e:
         ops.gpu_swiglu(dev(g), dev(u), out, n - 1, q8=q8)      # n % 32 != 0 with q8 (src/gpu_ops.cpp:82)
     assert e.value.code == 1
+
+
+@pytest.mark.parametrize("n", [256 * 1000 + 64, 4 * 1024 * 33, 1056])
+def test_16_bit_side_copy_comes_from_the_swiglu_kernel_itself(ops, oracle, n):
+    """Only the 16-bit copy wanted (src/q8_device.h:58): one launch writes out and out rounded to bf16 / fp16."""
+    g, u = synth.normal(7, "sx.g", 0, n), synth.normal(7, "sx.u", 0, n)
+    dg, du = dev(g), dev(u)
+    for kind in ("bf16", "f16"):
+        conv = oracle.f32_to_bf16 if kind == "bf16" else oracle.f32_to_f16
+        q8 = ops.Q8Buffers((n + 255) // 256 * 256, "cuda", xh=kind, int8=False)
+        out, plain = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+        before = ops.launch_count()
+        ops.gpu_swiglu(dg, du, out, n, q8=q8)
+        assert ops.launch_count() - before == 1
+        ops.gpu_swiglu(dg, du, plain, n)
+        torch.cuda.synchronize()
+        assert np.array_equal(host(out).view(np.uint32), host(plain).view(np.uint32))
+        assert np.array_equal(host(q8.xh).view(np.uint16)[:n], conv(host(out)).reshape(-1))
+        assert not host(q8.xh)[n:].any()

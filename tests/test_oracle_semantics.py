@@ -138,3 +138,40 @@ def test_quantize_q8_rules(oracle):
     assert o["qK"][512] == -127 and o["qK"][513] == 127      # iscale = -127 / (+2.5)
     dK = np.repeat(o["dK"], 256)
     assert np.abs(o["qK"] * dK - x).max() <= np.abs(x).max() / 127 * 0.51 + 1e-3
+
+
+def test_kv_quant_rows_follow_ggml_q8_0_and_q4_0(oracle):
+    """The quantised KV rows (src/attention.hip:159-178) are ggml's q8_0 / q4_0 blocks: dequantised they are within
+    half a step (Q8_0) or one step (Q4_0: the grid is offset, its top end is clipped) of the input, an all-zero block
+    stays zero, and the Q4_0 scale takes the sign that puts the largest magnitude on nibble 0."""
+    import numpy as np
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((4, 256)) * 2).astype(np.float32)
+    x[0, :32] = 0
+    x[1, 32:64] = np.linspace(-2, 2, 32, dtype=np.float32)
+    v, d = oracle.kv_quant_rows(x, 1)
+    df = oracle.f16_to_f32(d).reshape(4, 8)
+    du = np.abs(x.reshape(4, 8, 32)).max(axis=2) / np.float32(127)
+    assert np.all(np.abs(v.reshape(4, 8, 32) * du[:, :, None] - x.reshape(4, 8, 32)) <= du[:, :, None] * 0.5 * (1 + 1e-5))
+    assert not v[0, :32].any() and d[0, 0] == 0 and np.abs(v).max() == 127
+    v4, d4 = oracle.kv_quant_rows(x, 2)
+    nib = np.zeros((4, 32, 8), np.int32)
+    b = v4.reshape(4, 32, 4)
+    nib[:, :, :4], nib[:, :, 4:] = b & 15, b >> 4
+    nib = nib.reshape(4, 8, 32)
+    assert np.all(nib[0, 0] == 8) and d4[0, 0] == 0x8000        # 0 / -8 = -0, as the kernel's own division
+    xb = x.reshape(4, 8, 32)
+    for r in range(4):
+        for blk in range(8):
+            if (r, blk) in ((0, 0), (1, 1)):
+                continue
+            i = np.argmax(np.abs(xb[r, blk]))
+            assert nib[r, blk, i] == 0                        # the largest magnitude sits at the bottom of the grid
+    m = xb[1, 1][np.abs(xb[1, 1]) == np.abs(xb[1, 1]).max()]
+    assert nib[1, 1, 31] == 0 and nib[1, 1, 0] == 15          # -2 would need 16: clipped
+    assert len(m) == 2 and oracle.f16_to_f32(d4[1:2, 1:2])[0] == np.float32(2.0) / np.float32(-8.0)   # +2 wins the tie
+    d4u = np.take_along_axis(xb, np.abs(xb).argmax(axis=2)[:, :, None], axis=2) / np.float32(-8)
+    d4u[1, 1, 0] = np.float32(2.0) / np.float32(-8)
+    err = np.abs((nib - 8) * d4u - xb)
+    err[1, 1, 0] = 0
+    assert np.all(err <= np.abs(d4u) * (1 + 1e-5))
