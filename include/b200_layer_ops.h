@@ -75,6 +75,24 @@ static inline int gpu_moe_max_tiles(int T, int n_used, int n_expert, int tile) {
 cudaError_t gpu_moe_group(const int* ids, int T, int n_used, int n_expert, int tile, int* tok_rows, int* pair_rows,
                           int* n_tiles, int* tile_e, int* tile_start, int* tile_n, cudaStream_t stream);
 
+/* The sibling chains of the reference's Gemma-4 layers, same signatures and argument rules (src/gpu_ops.h:48-68,
+ * src/gpu_ops.cpp:186-234; kernels src/gpu_ops.hip:521-606,659-677). Rows [T][n] fp32, n % 256 == 0, n <= 4096.
+ *   gpu_add_normed:       out = (base + RMSNorm(a) * w) * (*scale, or 1 if NULL); out may be base, not a.
+ *   gpu_gemma_attn_post:  x_out = x + RMSNorm(a) * w_a; y1 = RMSNorm(x_out) * w1 (side outputs into q8 if set);
+ *                         y2 = RMSNorm(x_out) * w2 if w2. x_out is neither x nor a.
+ *   gpu_geglu:            out [rows][h] = GELU_tanh(g) * u, g / u row r at gate + r * gate_stride / up + r * up_stride
+ *                         (strides >= h; the experts' fused [gate | up] rows: up = gate + h, strides 2 h).
+ *   gpu_softcap:          x = cap * tanh(x / cap) in place, cap > 0.
+ * cudaErrorInvalidValue for the reference's refusals and for NULL or not 16-byte aligned row pointers. */
+cudaError_t gpu_add_normed(const float* base, const float* a, const float* w, const float* scale, float* out, int n, int T,
+                           float eps, cudaStream_t stream);
+cudaError_t gpu_gemma_attn_post(const float* x, const float* a, const float* w_a, float* x_out, const float* w1, float* y1,
+                                const qmatvec_q8* q8, const float* w2, float* y2, int n, int T, float eps,
+                                cudaStream_t stream);
+cudaError_t gpu_geglu(const float* gate, const float* up, float* out, int rows, int h, int gate_stride, int up_stride,
+                      const qmatvec_q8* q8, cudaStream_t stream);
+cudaError_t gpu_softcap(float* x, int n, float cap, cudaStream_t stream);
+
 /* ------------------------------------------------------------------------------------------------ Part 2 */
 
 /* bf16 storage (uint16_t bit patterns), fp32 arithmetic, one round-to-nearest-even per stored value (the rule of

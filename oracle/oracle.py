@@ -260,6 +260,47 @@ def kv_quant_rows(x, kq):
     return vals, scales
 
 
+def _row_inv_rms(v, eps):
+    """(float)(1 / sqrt(sum v^2 / n + eps)) per row with the sum in double, the CPU reference's accumulation
+    (src/qwen_ops.cpp:8-11) that this build's kernels keep for every RMSNorm."""
+    v = np.asarray(v, dtype=np.float32)
+    ss = (v.astype(np.float64) ** 2).sum(axis=1, keepdims=True)
+    return (1.0 / np.sqrt(ss / v.shape[1] + np.float64(np.float32(eps)))).astype(np.float32)
+
+
+def add_normed(base, a, w, scale, eps):
+    """out = (base + RMSNorm(a) * w) * scale, fp32 operations one by one in the order of the reference's add_normed
+    kernel (src/gpu_ops.hip:521-549): ((a * inv) * w + base) * s."""
+    base, a, w = (np.asarray(t, dtype=np.float32) for t in (base, a, w))
+    s = np.float32(1.0 if scale is None else scale)
+    return ((base + (a * _row_inv_rms(a, eps)) * w) * s).astype(np.float32)
+
+
+def gemma_attn_post(x, a, w_a, w1, w2, eps):
+    """x_out = x + RMSNorm(a) * w_a; y1 = RMSNorm(x_out) * w1; y2 = RMSNorm(x_out) * w2 or None
+    (src/gpu_ops.hip:577-606), fp32 operations one by one."""
+    x, a, w_a, w1 = (np.asarray(t, dtype=np.float32) for t in (x, a, w_a, w1))
+    x_out = (x + (a * _row_inv_rms(a, eps)) * w_a).astype(np.float32)
+    vn = (x_out * _row_inv_rms(x_out, eps)).astype(np.float32)
+    return x_out, (vn * w1).astype(np.float32), None if w2 is None else (vn * np.asarray(w2, np.float32)).astype(np.float32)
+
+
+def geglu(gate, up):
+    """GELU_tanh(g) * u (src/gpu_ops.hip:665-667): 0.5 x (1 + tanh(0.7978845608 x (1 + 0.044715 x x))) * u, fp32
+    products left to right, tanh correctly rounded."""
+    x, u = np.asarray(gate, dtype=np.float32), np.asarray(up, dtype=np.float32)
+    c1, c2, one, half = np.float32(0.7978845608028654), np.float32(0.044715), np.float32(1.0), np.float32(0.5)
+    inner = ((c1 * x) * (one + (c2 * x) * x)).astype(np.float32)
+    t = np.tanh(inner.astype(np.float64)).astype(np.float32)
+    return (((half * x) * (one + t)) * u).astype(np.float32)
+
+
+def softcap(x, cap):
+    """cap * tanh(x / cap) (src/gpu_ops.hip:673-677)."""
+    x, cap = np.asarray(x, dtype=np.float32), np.float32(cap)
+    return (cap * np.tanh((x / cap).astype(np.float64)).astype(np.float32)).astype(np.float32)
+
+
 class Lcg:
     """The reference tests' generator (tests/layernorm_verify.cpp:29-33)."""
 

@@ -16,6 +16,7 @@
 #include "embed.cuh"
 #include "kv_store.cuh"
 #include "moe_group.cuh"
+#include "norm_chains.cuh"
 #include "q8_side.cuh"
 #include "qk_norm_rope.cuh"
 #include "rmsnorm.cuh"
@@ -427,6 +428,50 @@ cudaError_t launch_kv_store_q(const IO* src, void* cache, int n_vals, const int*
     return launched();
 }
 
+// ---------------------------------------------------------------- Gemma-4 norm chains, GEGLU, soft cap
+
+// Rows of n fp32 values, n % 256 == 0 and n <= 4096 (src/gpu_ops.cpp:189,198): exactly tpr * vpt vectors
+bool plan_chain(int n, int* tpr, int* vpt) {
+    if (n <= 0 || n % 256 != 0 || n > 256 * 16) return false;
+    const int nvec = n / 4;
+    *vpt = nvec % 128 == 0 ? 4 : 2;
+    *tpr = nvec / *vpt;
+    return true;
+}
+
+cudaError_t launch_add_normed(const float* base, const float* a, const float* w, const float* scale, float* out, int n,
+                              long long T, float eps, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    int tpr, vpt;
+    if (T <= 0 || !plan_chain(n, &tpr, &vpt) || a == out || !base || !a || !w || !out || !al16(base) || !al16(a) ||
+        !al16(w) || !al16(out))
+        return cudaErrorInvalidValue;
+    if (vpt == 4) {
+        long long grid = persistent_grid(k_add_normed<4>, tpr, 0);
+        k_add_normed<4><<<(unsigned)(grid < T ? grid : T), tpr, 0, stream>>>(base, a, w, scale, out, n, T, eps);
+    } else {
+        long long grid = persistent_grid(k_add_normed<2>, tpr, 0);
+        k_add_normed<2><<<(unsigned)(grid < T ? grid : T), tpr, 0, stream>>>(base, a, w, scale, out, n, T, eps);
+    }
+    return launched();
+}
+
+cudaError_t launch_attn_post(const float* x, const float* a, const float* w_a, float* x_out, const float* w1, float* y1,
+                             const float* w2, float* y2, int n, long long T, float eps, cudaStream_t stream) {
+    int tpr, vpt;
+    if (!plan_chain(n, &tpr, &vpt) || !x || !a || !w_a || !x_out || !w1 || !y1 || (w2 && !y2) || !al16(x) || !al16(a) ||
+        !al16(w_a) || !al16(x_out) || !al16(w1) || !al16(y1) || (w2 && (!al16(w2) || !al16(y2))))
+        return cudaErrorInvalidValue;
+    if (vpt == 4) {
+        long long grid = persistent_grid(k_gemma_attn_post<4>, tpr, 0);
+        k_gemma_attn_post<4><<<(unsigned)(grid < T ? grid : T), tpr, 0, stream>>>(x, a, w_a, x_out, w1, y1, w2, y2, n, T, eps);
+    } else {
+        long long grid = persistent_grid(k_gemma_attn_post<2>, tpr, 0);
+        k_gemma_attn_post<2><<<(unsigned)(grid < T ? grid : T), tpr, 0, stream>>>(x, a, w_a, x_out, w1, y1, w2, y2, n, T, eps);
+    }
+    return launched();
+}
+
 }  // namespace
 
 // ================================================================ C ABI
@@ -475,6 +520,51 @@ cudaError_t gpu_swiglu(const float* g, const float* u, float* out, int n, const 
     qmatvec_q8 rest = *q8;
     if (xh_done) rest.xh = nullptr;
     return launch_q8_side(out, n, &rest, stream);
+}
+
+cudaError_t gpu_add_normed(const float* base, const float* a, const float* w, const float* scale, float* out, int n, int T,
+                           float eps, cudaStream_t stream) {
+    return launch_add_normed(base, a, w, scale, out, n, T, eps, stream);
+}
+
+cudaError_t gpu_gemma_attn_post(const float* x, const float* a, const float* w_a, float* x_out, const float* w1, float* y1,
+                                const qmatvec_q8* q8, const float* w2, float* y2, int n, int T, float eps,
+                                cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || (q8 && (long long)n * T > q8->max_k) || x_out == x || x_out == a) return cudaErrorInvalidValue;
+    const cudaError_t e = launch_attn_post(x, a, w_a, x_out, w1, y1, w2, y2, n, T, eps, stream);
+    if (e != cudaSuccess || !q8) return e;
+    return launch_q8_side(y1, (long long)n * T, q8, stream);
+}
+
+cudaError_t gpu_geglu(const float* gate, const float* up, float* out, int rows, int h, int gate_stride, int up_stride,
+                      const qmatvec_q8* q8, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    const long long n = (long long)rows * h;
+    if (rows <= 0 || h <= 0 || gate_stride < h || up_stride < h || n > INT_MAX || !gate || !up || !out ||
+        (q8 && (n % 32 != 0 || n > q8->max_k)))
+        return cudaErrorInvalidValue;
+    const bool vec = h % 4 == 0 && gate_stride % 4 == 0 && up_stride % 4 == 0 && al16(gate) && al16(up) && al16(out);
+    const long long work = vec ? n / 4 : n, cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    if (vec) k_geglu<true><<<(unsigned)grid, 256, 0, stream>>>(gate, up, out, rows, h, gate_stride, up_stride);
+    else k_geglu<false><<<(unsigned)grid, 256, 0, stream>>>(gate, up, out, rows, h, gate_stride, up_stride);
+    const cudaError_t e = launched();
+    if (e != cudaSuccess || !q8) return e;
+    return launch_q8_side(out, n, q8, stream);
+}
+
+cudaError_t gpu_softcap(float* x, int n, float cap, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (n <= 0 || !(cap > 0.0f) || !x) return cudaErrorInvalidValue;
+    const bool vec = al16(x);
+    const long long work = vec ? (n + 3) / 4 : n, cap_ctas = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap_ctas) grid = cap_ctas;
+    if (vec) k_softcap<true><<<(unsigned)grid, 256, 0, stream>>>(x, n, cap);
+    else k_softcap<false><<<(unsigned)grid, 256, 0, stream>>>(x, n, cap);
+    return launched();
 }
 
 cudaError_t gpu_moe_group(const int* ids, int T, int n_used, int n_expert, int tile, int* tok_rows, int* pair_rows,

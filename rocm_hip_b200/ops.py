@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
 ]
 
@@ -120,6 +120,31 @@ def gpu_swiglu_rows(gate, up, out, rows, h, gate_stride, up_stride):
     lib = _lib.load()
     fn = lib.gpu_swiglu_rows if gate.dtype == torch.float32 else lib.gpu_swiglu_rows_bf16
     _check("gpu_swiglu_rows", fn(_ptr(gate), _ptr(up), _ptr(out), rows, h, gate_stride, up_stride, _stream()))
+
+
+def gpu_add_normed(base, a, w, scale, out, n, T, eps):
+    """out = (base + RMSNorm(a) * w) * (scale[0] if scale is not None else 1) (src/gpu_ops.h:52)."""
+    _check("gpu_add_normed", _lib.load().gpu_add_normed(_ptr(base), _ptr(a), _ptr(w), _ptr(scale), _ptr(out), n, T, eps,
+                                                        _stream()))
+
+
+def gpu_gemma_attn_post(x, a, w_a, x_out, w1, y1, w2, y2, n, T, eps, q8=None):
+    """x_out = x + RMSNorm(a) * w_a; y1 = RMSNorm(x_out) * w1; y2 = RMSNorm(x_out) * w2 if w2 (src/gpu_ops.h:59)."""
+    q = C.byref(q8.struct()) if q8 is not None else None
+    _check("gpu_gemma_attn_post", _lib.load().gpu_gemma_attn_post(
+        _ptr(x), _ptr(a), _ptr(w_a), _ptr(x_out), _ptr(w1), _ptr(y1), q, _ptr(w2), _ptr(y2), n, T, eps, _stream()))
+
+
+def gpu_geglu(gate, up, out, rows, h, gate_stride, up_stride, q8=None):
+    """out [rows][h] = GELU_tanh(gate) * up on strided rows (src/gpu_ops.h:66)."""
+    q = C.byref(q8.struct()) if q8 is not None else None
+    _check("gpu_geglu", _lib.load().gpu_geglu(_ptr(gate), _ptr(up), _ptr(out), rows, h, gate_stride, up_stride, q,
+                                              _stream()))
+
+
+def gpu_softcap(x, n, cap):
+    """x = cap * tanh(x / cap) in place (src/gpu_ops.h:68)."""
+    _check("gpu_softcap", _lib.load().gpu_softcap(_ptr(x), n, cap, _stream()))
 
 
 def gpu_kv_store_f16(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride):

@@ -175,3 +175,27 @@ def test_kv_quant_rows_follow_ggml_q8_0_and_q4_0(oracle):
     err = np.abs((nib - 8) * d4u - xb)
     err[1, 1, 0] = 0
     assert np.all(err <= np.abs(d4u) * (1 + 1e-5))
+
+
+def test_gemma_chain_statements_against_plain_double_precision(oracle):
+    """add_normed, gemma_attn_post, geglu and softcap of the oracle (src/gpu_ops.hip:521-606, 659-677) against the
+    same formulas evaluated in double precision."""
+    import numpy as np
+    rng = np.random.default_rng(11)
+    T, n = 5, 768
+    x, a = rng.standard_normal((T, n)).astype(np.float32), (rng.standard_normal((T, n)) * 3).astype(np.float32)
+    w, w1, w2 = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32), rng.standard_normal(n).astype(np.float32), \
+        rng.standard_normal(n).astype(np.float32)
+    D = lambda t: np.asarray(t, dtype=np.float64)
+    rms = lambda v: D(v) / np.sqrt((D(v) ** 2).mean(axis=1, keepdims=True) + 1e-6)
+    assert np.abs(oracle.add_normed(x, a, w, 0.625, 1e-6) - (D(x) + rms(a) * w) * 0.625).max() < 2e-6
+    assert np.array_equal(oracle.add_normed(x, a, w, None, 1e-6), oracle.add_normed(x, a, w, 1.0, 1e-6))
+    xo, y1, y2 = oracle.gemma_attn_post(x, a, w, w1, w2, 1e-6)
+    ref_xo = D(x) + rms(a) * w
+    assert np.abs(xo - ref_xo).max() < 2e-6
+    assert np.abs(y1 - rms(ref_xo) * w1).max() < 4e-6 and np.abs(y2 - rms(ref_xo) * w2).max() < 4e-6
+    assert oracle.gemma_attn_post(x, a, w, w1, None, 1e-6)[2] is None
+    g = D(x) * 2
+    ref = 0.5 * g * (1 + np.tanh(0.7978845608028654 * g * (1 + 0.044715 * g * g))) * D(a)
+    assert np.abs(oracle.geglu(x * 2, a) - ref).max() < 4e-6
+    assert np.abs(oracle.softcap(a * 20, 30.0) - 30 * np.tanh(D(a) * 20 / 30)).max() < 4e-6
