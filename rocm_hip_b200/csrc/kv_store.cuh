@@ -51,42 +51,79 @@ k_kv_store_f16(const IO* src, __half* cache, int n_vals, const int* positions, i
 //               n = min(15, (int)(x * (1 / d) + 8.5)) (8 when d == 0); byte 4 j + k (k < 4) of the row holds value
 //               8 j + k in its low and value 8 j + k + 4 in its high nibble; scales start at byte d_row / 2.
 // The scale is stored rounded to fp16; the values are quantised with the unrounded d. Every operation rounds on its
-// own. A warp owns a 32-value block, lane = value; a warp takes U blocks per step so U loads are in flight per lane.
+// own. A thread owns 8 consecutive values (32 or 16 bytes read, 8 or 4 bytes written: for Q4_0 its eight values are
+// exactly one 32-bit word of the row), four neighbouring lanes own a block and share its maximum with two shuffles.
+// U octets per thread and step are loaded before the first is used.
 template <typename IO, int KQ, int U>
 __global__ void __launch_bounds__(256)
 k_kv_store_q(const IO* src, __half* cache, int n_vals, const int* positions, int pos0, long long T, int kv_stride,
              int kv_shift, long long kv_bstride) {
-    const int lane = threadIdx.x & 31;
-    const int bpr = n_vals / 32;                      // blocks per row
-    const long long nblk = T * bpr;
+    const int opr = n_vals / 8;                       // octets per row
+    const long long total = T * opr;
     const int d_row = kv_stride * 32 / (KQ == 2 ? 9 : 17);
-    const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long b0 = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * U; b0 < nblk; b0 += warps * U) {
-        float x[U];
-#pragma unroll
-        for (int j = 0; j < U; ++j) x[j] = b0 + j < nblk ? Io<IO>::load1(src + (b0 + j) * 32 + lane) : 0.0f;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    // every lane of a warp runs the same number of steps (the shuffles need all four lanes of a block; a block
+    // never straddles the end because n_vals is a multiple of 32)
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 - threadIdx.x % 32 < total; i0 += stride * U) {
+        float x[U][8];
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            if (b0 + j >= nblk) break;                // warp-uniform
-            const long long t = (b0 + j) / bpr;
-            const int blk = (int)(b0 + j - t * bpr);
+            const long long i = i0 + j * stride;
+            if (i < total) {
+                if (sizeof(IO) == 4) {
+                    Io<float>::unpack(ld_stream(reinterpret_cast<const float*>(src) + i * 8), x[j]);
+                    Io<float>::unpack(ld_stream(reinterpret_cast<const float*>(src) + i * 8 + 4), x[j] + 4);
+                } else {
+                    Io<__nv_bfloat16>::unpack(ld_stream(reinterpret_cast<const __nv_bfloat16*>(src) + i * 8), x[j]);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[j][e] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const long long i = i0 + j * stride;
+            const bool live = i < total;
+            float amax = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(x[j][e]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            float m = -INFINITY;
+            if (KQ == 2) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(x[j][e]) == amax ? x[j][e] : -INFINITY);
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            }
+            if (!live) continue;
+            const long long t = i / opr;
+            const int o = (int)(i - t * opr);            // octet of the row; block o / 4
             const int pos = positions ? positions[t] : pos0 + (int)t;
             uint8_t* row = reinterpret_cast<uint8_t*>(cache + kv_row(pos, kv_stride, kv_shift, kv_bstride));
-            float amax = fabsf(x[j]);
-            for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
             if (KQ == 1) {
                 const float d = __fdiv_rn(amax, 127.0f);
-                const float q = d != 0.0f ? __fmul_rn(x[j], __fdiv_rn(1.0f, d)) : 0.0f;
-                reinterpret_cast<int8_t*>(row)[blk * 32 + lane] = (int8_t)(int)rintf(q);
-                if (lane == 0) reinterpret_cast<__half*>(row + d_row)[blk] = __float2half_rn(d);
+                const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                uint32_t w[2] = {0u, 0u};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int q = d != 0.0f ? (int)rintf(__fmul_rn(x[j][e], id)) : 0;
+                    w[e >> 2] |= (uint32_t)(q & 0xff) << (8 * (e & 3));
+                }
+                *reinterpret_cast<uint2*>(row + o * 8) = make_uint2(w[0], w[1]);
+                if ((o & 3) == 0) reinterpret_cast<__half*>(row + d_row)[o >> 2] = __float2half_rn(d);
             } else {
-                float m = fabsf(x[j]) == amax ? x[j] : -INFINITY;
-                for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
                 const float d = __fdiv_rn(m, -8.0f);
-                const int n = min(15, (int)(d != 0.0f ? __fadd_rn(__fmul_rn(x[j], __fdiv_rn(1.0f, d)), 8.5f) : 8.0f));
-                const int hi = __shfl_down_sync(0xffffffffu, n, 4);
-                if ((lane & 4) == 0) row[blk * 16 + (lane >> 3) * 4 + (lane & 3)] = (uint8_t)(n | (hi << 4));
-                if (lane == 0) reinterpret_cast<__half*>(row + d_row / 2)[blk] = __float2half_rn(d);
+                const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                uint32_t w = 0u;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int n = min(15, (int)(d != 0.0f ? __fadd_rn(__fmul_rn(x[j][e], id), 8.5f) : 8.0f));
+                    w |= (uint32_t)n << (8 * (e & 3) + 4 * (e >> 2));     // value e: byte e % 4, high nibble for e >= 4
+                }
+                *reinterpret_cast<uint32_t*>(row + o * 4) = w;
+                if ((o & 3) == 0) reinterpret_cast<__half*>(row + d_row / 2)[o >> 2] = __float2half_rn(d);
             }
         }
     }

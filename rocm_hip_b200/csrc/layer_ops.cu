@@ -181,8 +181,12 @@ cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const W
 cudaError_t launch_q8_side(const float* x, long long K, const qmatvec_q8* q8, cudaStream_t stream) {
     if (!q8->qK && !q8->xh) return cudaSuccess;  // nothing wanted (src/q8_device.h:35)
     Q8Side o = {q8->q0, q8->d0, q8->qK, q8->dK, q8->bsK, q8->s0, q8->xh, q8->xh_bf16};
-    const long long nblk = (K + 255) / 256, cap = resident_ctas(256) * 4;
-    k_q8_side<<<(unsigned)(nblk < cap ? nblk : cap), 256, 0, stream>>>(x, K, o);
+    const long long nblk = (K + 255) / 256, cap = resident_ctas(256) * 8;
+    long long grid = (nblk + 7) / 8;   // a warp per block, 8 warps per CTA
+    if (grid > cap) grid = cap;
+    const bool vec = al16(x) && (!o.xh || al16(o.xh)) && (!o.qK || ((reinterpret_cast<uintptr_t>(o.q0) | reinterpret_cast<uintptr_t>(o.qK)) & 7) == 0);
+    if (vec) k_q8_side<true><<<(unsigned)grid, 256, 0, stream>>>(x, K, o);
+    else k_q8_side<false><<<(unsigned)grid, 256, 0, stream>>>(x, K, o);
     return launched();
 }
 
@@ -416,9 +420,15 @@ cudaError_t launch_kv_store_q(const IO* src, void* cache, int n_vals, const int*
     const long long need = kv_quant == 2 ? d_row / 2 + n_vals / 32 * 2 : d_row + n_vals / 32 * 2;
     if (n_vals > d_row || need > (long long)kv_stride * 2 || (kv_quant == 2 ? d_row / 2 : d_row) % 2 != 0)
         return cudaErrorInvalidValue;
-    constexpr int U = 4;
-    const long long nblk = T * (n_vals / 32), cap = resident_ctas(256) * 4;
-    long long grid = (nblk + 8 * U - 1) / (8 * U);
+    // a thread writes its 8 values as one 8-byte (Q8_0) or 4-byte (Q4_0) word: rows must start on such a boundary
+    // (the reference's rows, d_row % 256 == 0, are multiples of 272 and 144 bytes)
+    const int unit = kv_quant == 1 ? 4 : 2;   // in fp16 units
+    if (!al16(src) || kv_stride % unit != 0 || kv_bstride % unit != 0 ||
+        (reinterpret_cast<uintptr_t>(cache) & (size_t)(2 * unit - 1)) != 0)
+        return cudaErrorInvalidValue;
+    constexpr int U = 2;
+    const long long octets = T * (n_vals / 8), cap = resident_ctas(256) * 8;
+    long long grid = (octets + 256 * U - 1) / (256 * U);
     if (grid > cap) grid = cap;
     __half* c = reinterpret_cast<__half*>(cache);
     if (kv_quant == 1)

@@ -6,8 +6,9 @@
 //   Q8_K : per 256 values, max = the signed value of largest |x| (lowest index on ties), iscale = -127 / max,
 //          q = min(127, rint(iscale * x)), d = 1 / iscale, plus the sum of every 16 q
 // The int8 outputs are written only when qK is set (then q0, d0, s0, dK, bsK are all expected), xh only when set.
-// One CTA of 256 threads per 256-value block of the flattened vector; a last partial block (n a multiple of 32 only)
-// gets its Q8_0 part and an incomplete Q8_K part, as in the reference.
+// A last partial 256-value block (n a multiple of 32 only) gets its Q8_0 part and an incomplete Q8_K part, as in the
+// reference. Two forms: q8_block_value, one value per thread of a 256-thread group (the reference's shape, for a
+// kernel that has the value in a register), and k_q8_side, a warp per block over a vector in memory.
 
 #ifndef B200_Q8_SIDE_CUH
 #define B200_Q8_SIDE_CUH
@@ -89,14 +90,104 @@ __device__ __forceinline__ void q8_block_value(float v, bool active, long long b
     }
 }
 
+// The same outputs for a finished vector in memory, at memory speed: one warp per 256-value block, a lane owns 8
+// consecutive values (two 16-byte loads; its int8 results are one 8-byte store per format, its 16-bit copy one 16-byte
+// store), a Q8_0 block is four neighbouring lanes, a Q8_K block the warp, so every reduction is a shuffle. Same rules
+// and the same bits as q8_block_value (which keeps the reference's one-value-per-thread shape for kernels that call
+// it on a value in flight). With qK set K is a multiple of 32, so a lane's 8 values are all inside or all outside.
+// VEC: x, q0, qK 16- / 8-byte aligned and xh 16-byte aligned.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 k_q8_side(const float* x, long long K, Q8Side o) {
-    __shared__ Q8Scratch sh;
+    const int lane = threadIdx.x & 31;
     const long long nblk = (K + 255) / 256;
-    for (long long b = blockIdx.x; b < nblk; b += gridDim.x) {
-        const long long i = b * 256 + threadIdx.x;
-        const bool active = i < K;
-        q8_block_value(active ? x[i] : 0.0f, active, b, threadIdx.x, sh, o);
+    const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long b = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); b < nblk; b += warps) {
+        const long long i = b * 256 + lane * 8;
+        const int act = (int)(K - i >= 8 ? 8 : (K - i > 0 ? K - i : 0));      // live values of this lane
+        float v[8];
+        if (VEC && act == 8) {
+            Io<float>::unpack(ld_stream(x + i), v);
+            Io<float>::unpack(ld_stream(x + i + 4), v + 4);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = e < act ? x[i + e] : 0.0f;
+        }
+        if (o.xh) {
+            if (VEC && act == 8) {
+                const uint4 r = o.xh_bf16 ? Io<__nv_bfloat16>::pack(v) : Io<__half>::pack(v);
+                st_stream(o.xh + i, r);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (e < act) o.xh[i + e] = o.xh_bf16 ? to_bf16_bits(v[e]) : __half_as_ushort(__float2half_rn(v[e]));
+            }
+        }
+        if (!o.qK) continue;  // uniform
+        const bool active = act == 8;
+
+        // Q8_0: 32 values = lanes 4 g .. 4 g + 3
+        float am = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(v[e]));
+        float ba = 0.0f, bv = 0.0f;      // this lane's largest |x| and its signed value, lowest index on ties
+        int bi = lane * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (fabsf(v[e]) > ba || e == 0) { ba = fabsf(v[e]); bv = v[e]; bi = lane * 8 + e; }
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+        const float id0 = am != 0.0f ? __fdiv_rn(127.0f, am) : 0.0f;
+        int q[8], sum0 = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { q[e] = (int)rintf(__fmul_rn(v[e], id0)); sum0 += q[e]; }
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+        if (active) {
+            uint32_t w0 = 0u, w1 = 0u;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { w0 |= (uint32_t)(q[e] & 0xff) << (8 * e); w1 |= (uint32_t)(q[e + 4] & 0xff) << (8 * e); }
+            if (VEC) *reinterpret_cast<uint2*>(o.q0 + i) = make_uint2(w0, w1);
+            else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o.q0[i + e] = (int8_t)q[e];
+            }
+            if ((lane & 3) == 0) {
+                const float d = __fdiv_rn(am, 127.0f);
+                o.d0[b * 8 + (lane >> 2)] = __half2float(__float2half_rn(d));
+                o.s0[b * 8 + (lane >> 2)] = __float_as_int(__half2float(__float2half_rn(__fmul_rn(d, (float)sum0))));
+            }
+        }
+
+        // Q8_K: the warp's 256 values
+        for (int off = 16; off > 0; off >>= 1) {
+            const float oa = __shfl_xor_sync(0xffffffffu, ba, off), ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (oa > ba || (oa == ba && oi < bi)) { ba = oa; bi = oi; bv = ov; }
+        }
+        float iscale = 0.0f;
+        int s8 = 0;
+        if (ba != 0.0f) {
+            iscale = __fdiv_rn(-127.0f, bv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { q[e] = min(127, (int)rintf(__fmul_rn(iscale, v[e]))); s8 += q[e]; }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) q[e] = 0;
+        }
+        const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
+        if (active) {
+            uint32_t w0 = 0u, w1 = 0u;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { w0 |= (uint32_t)(q[e] & 0xff) << (8 * e); w1 |= (uint32_t)(q[e + 4] & 0xff) << (8 * e); }
+            if (VEC) *reinterpret_cast<uint2*>(o.qK + i) = make_uint2(w0, w1);
+            else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o.qK[i + e] = (int8_t)q[e];
+            }
+            if (lane == 0) o.dK[b] = ba != 0.0f ? __fdiv_rn(1.0f, iscale) : 0.0f;
+            if ((lane & 1) == 0) o.bsK[b * 16 + (lane >> 1)] = s16;
+        }
     }
 }
 
