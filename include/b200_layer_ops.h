@@ -83,12 +83,27 @@ cudaError_t gpu_moe_group(const int* ids, int T, int n_used, int n_expert, int t
  *   gpu_geglu:            out [rows][h] = GELU_tanh(g) * u, g / u row r at gate + r * gate_stride / up + r * up_stride
  *                         (strides >= h; the experts' fused [gate | up] rows: up = gate + h, strides 2 h).
  *   gpu_softcap:          x = cap * tanh(x / cap) in place, cap > 0.
+ *   gpu_moe_combine[_scaled]: out [T][n] = sum_j wts[t][j] * down[t][j] (+ sg[t] * shared[t]; + shared[t] if sg is
+ *                         NULL; wts NULL: weight 1), down [T][n_used][n], in slot order; _scaled: each expert's
+ *                         output times exp_scale[ids[t][j]] first (src/gpu_ops.h:40-46). Any n.
+ *   gpu_gemma_ffn_post:   c = the combine above (no shared expert); h = RMSNorm(mlp) * w1 + RMSNorm(c) * w2;
+ *                         x_out = (x + RMSNorm(h) * w_post) * (*scale, or 1); y = RMSNorm(x_out) * w_next (side
+ *                         outputs into q8 if set). x_out is not x.
  * cudaErrorInvalidValue for the reference's refusals and for NULL or not 16-byte aligned row pointers. */
 cudaError_t gpu_add_normed(const float* base, const float* a, const float* w, const float* scale, float* out, int n, int T,
                            float eps, cudaStream_t stream);
 cudaError_t gpu_gemma_attn_post(const float* x, const float* a, const float* w_a, float* x_out, const float* w1, float* y1,
                                 const qmatvec_q8* q8, const float* w2, float* y2, int n, int T, float eps,
                                 cudaStream_t stream);
+cudaError_t gpu_gemma_ffn_post(const float* x, const float* mlp, const float* down, const float* wts, const int* ids,
+                               const float* exp_scale, int n_used, const float* w1, const float* w2, const float* w_post,
+                               const float* scale, float* x_out, const float* w_next, float* y, const qmatvec_q8* q8, int n,
+                               int T, float eps, cudaStream_t stream);
+cudaError_t gpu_moe_combine(const float* down, const float* wts, const float* shared, const float* sg, float* out,
+                            int n_used, int n, int T, cudaStream_t stream);
+cudaError_t gpu_moe_combine_scaled(const float* down, const float* wts, const float* shared, const float* sg,
+                                   const int* ids, const float* exp_scale, float* out, int n_used, int n, int T,
+                                   cudaStream_t stream);
 cudaError_t gpu_geglu(const float* gate, const float* up, float* out, int rows, int h, int gate_stride, int up_stride,
                       const qmatvec_q8* q8, cudaStream_t stream);
 cudaError_t gpu_softcap(float* x, int n, float cap, cudaStream_t stream);

@@ -285,6 +285,44 @@ def gemma_attn_post(x, a, w_a, w1, w2, eps):
     return x_out, (vn * w1).astype(np.float32), None if w2 is None else (vn * np.asarray(w2, np.float32)).astype(np.float32)
 
 
+def moe_combine(down, wts, shared=None, sg=None, ids=None, exp_scale=None):
+    """out [T][n] = sum_j wts[t][j] * down[t][j] in slot order (+ shared * sg, or + shared), fp32 operations one by one
+    (src/gpu_ops.hip:245-264): with exp_scale each term is (d * exp_scale[ids[t][j]]) * w; wts None: weight 1."""
+    down = np.asarray(down, dtype=np.float32)
+    T, n_used, n = down.shape
+    acc = None
+    for j in range(n_used):
+        v = down[:, j, :]
+        if wts is not None:
+            w = np.asarray(wts, np.float32)[:, j:j + 1]
+            if exp_scale is not None:
+                es = np.asarray(exp_scale, np.float32)[np.asarray(ids)[:, j]][:, None]
+                v = ((v * es).astype(np.float32) * w).astype(np.float32)
+            else:
+                v = (w * v).astype(np.float32)
+        acc = v if acc is None else (acc + v).astype(np.float32)
+    if shared is not None:
+        sh = np.asarray(shared, np.float32)
+        if sg is not None and wts is not None:
+            sh = (sh * np.asarray(sg, np.float32)[:, None]).astype(np.float32)
+        acc = (acc + sh).astype(np.float32)
+    return acc
+
+
+def gemma_ffn_post(x, mlp, down, wts, ids, exp_scale, w1, w2, w_post, scale, w_next, eps):
+    """(x_out, y) of the reference's gemma_ffn_post kernel (src/gpu_ops.hip:608-655), fp32 operations one by one:
+    c = moe_combine; h = RMSNorm(mlp) * w1 + RMSNorm(c) * w2; x_out = (x + RMSNorm(h) * w_post) * scale;
+    y = RMSNorm(x_out) * w_next."""
+    f = lambda t: np.asarray(t, dtype=np.float32)
+    x, mlp, w1, w2, w_post, w_next = map(f, (x, mlp, w1, w2, w_post, w_next))
+    c = moe_combine(down, wts, ids=ids, exp_scale=exp_scale)
+    h = ((mlp * _row_inv_rms(mlp, eps)) * w1).astype(np.float32)
+    h = (h + (c * _row_inv_rms(c, eps)) * w2).astype(np.float32)
+    s = np.float32(1.0 if scale is None else scale)
+    x_out = ((x + (h * _row_inv_rms(h, eps)) * w_post) * s).astype(np.float32)
+    return x_out, ((x_out * _row_inv_rms(x_out, eps)) * w_next).astype(np.float32)
+
+
 def geglu(gate, up):
     """GELU_tanh(g) * u (src/gpu_ops.hip:665-667): 0.5 x (1 + tanh(0.7978845608 x (1 + 0.044715 x x))) * u, fp32
     products left to right, tanh correctly rounded."""

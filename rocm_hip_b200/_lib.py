@@ -42,6 +42,9 @@ SIGNATURES = {
     "gpu_qk_norm_rope_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_add_normed": (_i, [_p, _p, _p, _p, _p, _i, _i, _f, _p]),
     "gpu_gemma_attn_post": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p]),
+    "gpu_gemma_ffn_post": (_i, [_p] * 6 + [_i] + [_p] * 8 + [_i, _i, _f, _p]),
+    "gpu_moe_combine": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "gpu_moe_combine_scaled": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "gpu_geglu": (_i, [_p, _p, _p, _i, _i, _i, _i, _p, _p]),
     "gpu_softcap": (_i, [_p, _i, _f, _p]),
     "gpu_kv_store_f16": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _p]),

@@ -547,6 +547,48 @@ cudaError_t gpu_gemma_attn_post(const float* x, const float* a, const float* w_a
     return launch_q8_side(y1, (long long)n * T, q8, stream);
 }
 
+cudaError_t gpu_gemma_ffn_post(const float* x, const float* mlp, const float* down, const float* wts, const int* ids,
+                               const float* exp_scale, int n_used, const float* w1, const float* w2, const float* w_post,
+                               const float* scale, float* x_out, const float* w_next, float* y, const qmatvec_q8* q8, int n,
+                               int T, float eps, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    int tpr, vpt;
+    if (T <= 0 || n_used <= 0 || !plan_chain(n, &tpr, &vpt) || (q8 && (long long)n * T > q8->max_k) || x_out == x ||
+        !x || !mlp || !down || !wts || (exp_scale && !ids) || !w1 || !w2 || !w_post || !x_out || !w_next || !y ||
+        !al16(x) || !al16(mlp) || !al16(down) || !al16(w1) || !al16(w2) || !al16(w_post) || !al16(x_out) ||
+        !al16(w_next) || !al16(y))
+        return cudaErrorInvalidValue;
+    if (vpt == 4) {
+        long long grid = persistent_grid(k_gemma_ffn_post<4>, tpr, 0);
+        k_gemma_ffn_post<4><<<(unsigned)(grid < T ? grid : T), tpr, 0, stream>>>(x, mlp, down, wts, ids, exp_scale, n_used, w1, w2, w_post, scale, x_out, w_next, y, n, T, eps);
+    } else {
+        long long grid = persistent_grid(k_gemma_ffn_post<2>, tpr, 0);
+        k_gemma_ffn_post<2><<<(unsigned)(grid < T ? grid : T), tpr, 0, stream>>>(x, mlp, down, wts, ids, exp_scale, n_used, w1, w2, w_post, scale, x_out, w_next, y, n, T, eps);
+    }
+    const cudaError_t e = launched();
+    if (e != cudaSuccess || !q8) return e;
+    return launch_q8_side(y, (long long)n * T, q8, stream);
+}
+
+cudaError_t gpu_moe_combine_scaled(const float* down, const float* wts, const float* shared, const float* sg,
+                                   const int* ids, const float* exp_scale, float* out, int n_used, int n, int T,
+                                   cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if ((exp_scale && !ids) || T <= 0 || n <= 0 || n_used <= 0 || !down || !out) return cudaErrorInvalidValue;
+    const bool vec = n % 4 == 0 && al16(down) && al16(out) && (!shared || al16(shared));
+    const long long work = (long long)T * (vec ? n / 4 : n), cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    if (vec) k_moe_combine<true><<<(unsigned)grid, 256, 0, stream>>>(down, wts, shared, sg, out, n_used, n, T, ids, exp_scale);
+    else k_moe_combine<false><<<(unsigned)grid, 256, 0, stream>>>(down, wts, shared, sg, out, n_used, n, T, ids, exp_scale);
+    return launched();
+}
+
+cudaError_t gpu_moe_combine(const float* down, const float* wts, const float* shared, const float* sg, float* out,
+                            int n_used, int n, int T, cudaStream_t stream) {
+    return gpu_moe_combine_scaled(down, wts, shared, sg, nullptr, nullptr, out, n_used, n, T, stream);
+}
+
 cudaError_t gpu_geglu(const float* gate, const float* up, float* out, int rows, int h, int gate_stride, int up_stride,
                       const qmatvec_q8* q8, cudaStream_t stream) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;

@@ -4,6 +4,8 @@
 //   gemma_attn_post  x_out = x + RMSNorm(a) * w_a;  y1 = RMSNorm(x_out) * w1;  y2 = RMSNorm(x_out) * w2 (if w2)
 //   geglu            out = GELU_tanh(g) * u on rows whose gate / up halves sit at a stride
 //   softcap          x = cap * tanh(x / cap), in place
+//   moe_combine      out = sum_j wts_j * down_j (+ sg * shared), the experts' outputs back into token rows (:245-264)
+//   gemma_ffn_post   the FFN epilogue: combine, two norms added, residual, scale, the next layer's norm (:608-655)
 // Every product and sum is rounded on its own, in the order the reference writes them: RMSNorm(v) * w is
 // (v * inv) * w, then the add, then the scale. inv = (float)(1 / sqrt(ss / n + eps)) with ss summed in double, as in
 // rmsnorm.cuh, so the chains give the bits of the separate norm kernels followed by fp32 adds.
@@ -130,6 +132,158 @@ k_gemma_attn_post(const float* x, const float* a, const float* w_a, float* x_out
             }
         }
         // (the second reduction's barrier separates this row's reads of part[0] from the next row's writes)
+    }
+}
+
+// ---------------------------------------------------------------- MoE combine and the FFN epilogue
+
+// One slot's term of the experts' weighted sum for a packed pair (src/gpu_ops.hip:259-261): (d * exp_scale[e]) * w
+// with per-expert scales, else w * d; the sum runs in slot order, each product and each add rounded on its own.
+__device__ __forceinline__ f2 combine_term(f2 d, float w, float es, bool scaled) {
+    return scaled ? mul2(mul2(d, pk2(es, es)), pk2(w, w)) : mul2(pk2(w, w), d);
+}
+
+// out [T][n] = sum_j wts[t][j] * down[t][j][:] (+ shared[t] * sg[t], or + shared[t] when sg is NULL); wts NULL: weight 1
+// (src/gpu_ops.hip:245-264). down is [T][n_used][n]. One thread per 16-byte vector of out (VEC: n % 4 == 0 and
+// aligned bases) or per value; up to 8 slots' loads are in flight per thread.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+k_moe_combine(const float* down, const float* wts, const float* shared, const float* sg, float* out, int n_used, int n,
+              long long T, const int* ids, const float* exp_scale) {
+    const int per_row = VEC ? n / 4 : n;
+    const long long total = T * per_row;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / per_row;
+        const int c = (int)(i - t * per_row);
+        const float* w = wts ? wts + t * n_used : nullptr;
+        const int* e = exp_scale ? ids + t * n_used : nullptr;
+        if (VEC) {
+            const uint4* d = reinterpret_cast<const uint4*>(down + (size_t)t * n_used * n) + c;
+            f2 acc[2];
+            for (int j0 = 0; j0 < n_used; j0 += 8) {
+                uint4 r[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (j0 + u < n_used) r[u] = ld_stream(d + (size_t)(j0 + u) * per_row);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int j = j0 + u;
+                    if (j < n_used) {
+                        f2 v[2];
+                        Io2<float>::unpack(r[u], v);
+                        if (w) {
+                            const float wj = __ldg(w + j), es = e ? __ldg(exp_scale + __ldg(e + j)) : 1.0f;
+                            v[0] = combine_term(v[0], wj, es, e != nullptr);
+                            v[1] = combine_term(v[1], wj, es, e != nullptr);
+                        }
+                        if (j == 0) { acc[0] = v[0]; acc[1] = v[1]; }
+                        else { acc[0] = add_rounded(acc[0], v[0]); acc[1] = add_rounded(acc[1], v[1]); }
+                    }
+                }
+            }
+            if (shared) {
+                f2 sv[2];
+                Io2<float>::unpack(ld_stream(reinterpret_cast<const uint4*>(shared) + i), sv);
+                if (sg && w) {
+                    const float g = __ldg(sg + t);
+                    sv[0] = mul2(sv[0], pk2(g, g));
+                    sv[1] = mul2(sv[1], pk2(g, g));
+                }
+                acc[0] = add_rounded(acc[0], sv[0]);
+                acc[1] = add_rounded(acc[1], sv[1]);
+            }
+            st_stream(reinterpret_cast<uint4*>(out) + i, Io2<float>::pack(acc));
+        } else {
+            const float* d = down + (size_t)t * n_used * n + c;
+            float acc = 0.0f;
+            for (int j = 0; j < n_used; ++j) {
+                float v = d[(size_t)j * n];
+                if (w) v = e ? __fmul_rn(__fmul_rn(v, exp_scale[e[j]]), w[j]) : __fmul_rn(w[j], v);
+                acc = j == 0 ? v : __fadd_rn(acc, v);
+            }
+            if (shared) acc = __fadd_rn(acc, (sg && w) ? __fmul_rn(shared[i], sg[t]) : shared[i]);
+            out[i] = acc;
+        }
+    }
+}
+
+// Gemma-4's norm chain after the FFN, one CTA per row (src/gpu_ops.hip:608-655):
+//   c = the experts' outputs combined (as k_moe_combine: exp_scale, wts);  h = RMSNorm(mlp) * w1 + RMSNorm(c) * w2;
+//   x_out = (x + RMSNorm(h) * w_post) * (*scale, or 1);  y = RMSNorm(x_out) * w_next
+template <int VPT>
+__global__ void __launch_bounds__(512)
+k_gemma_ffn_post(const float* x, const float* mlp, const float* down, const float* wts, const int* ids,
+                 const float* exp_scale, int n_used, const float* w1, const float* w2, const float* w_post,
+                 const float* scale, float* x_out, const float* w_next, float* y, int n, long long T, float eps) {
+    __shared__ double part[4][32];
+    const int tpr = blockDim.x, l = threadIdx.x;
+    const size_t row_vecs = (size_t)tpr * VPT;
+    const double inv_n = 1.0 / (double)n;
+    const float sc = scale ? __ldg(scale) : 1.0f;
+    for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+        const size_t off = (size_t)row * row_vecs + l;
+        f2 h[VPT][2], c[VPT][2];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) Io2<float>::unpack(ld_stream(reinterpret_cast<const uint4*>(mlp) + off + j * tpr), h[j]);
+        const float* wt = wts + row * n_used;
+        const int* e = ids + row * n_used;
+        const uint4* d = reinterpret_cast<const uint4*>(down) + (size_t)row * n_used * row_vecs + l;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            for (int u0 = 0; u0 < n_used; u0 += 4) {
+                uint4 r[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (u0 + k < n_used) r[k] = ld_stream(d + (size_t)(u0 + k) * row_vecs + j * tpr);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int u = u0 + k;
+                    if (u < n_used) {
+                        f2 v[2];
+                        Io2<float>::unpack(r[k], v);
+                        const float wu = __ldg(wt + u), es = exp_scale ? __ldg(exp_scale + __ldg(e + u)) : 1.0f;
+                        v[0] = combine_term(v[0], wu, es, exp_scale != nullptr);
+                        v[1] = combine_term(v[1], wu, es, exp_scale != nullptr);
+                        if (u == 0) { c[j][0] = v[0]; c[j][1] = v[1]; }
+                        else { c[j][0] = add_rounded(c[j][0], v[0]); c[j][1] = add_rounded(c[j][1], v[1]); }
+                    }
+                }
+            }
+        }
+        const float im = inv_rms(cta_sum(row_sumsq<VPT>(h), part[0]), inv_n, eps);
+        const float ic = inv_rms(cta_sum(row_sumsq<VPT>(c), part[1]), inv_n, eps);
+        const f2 im2 = pk2(im, im), ic2 = pk2(ic, ic);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            f2 g1[2], g2[2];
+            gamma_pair(w1, (size_t)l + (size_t)j * tpr, g1);
+            gamma_pair(w2, (size_t)l + (size_t)j * tpr, g2);
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                h[j][k] = add_rounded(mul2(mul2(h[j][k], im2), g1[k]), mul2(mul2(c[j][k], ic2), g2[k]));
+        }
+        const float ih = inv_rms(cta_sum(row_sumsq<VPT>(h), part[2]), inv_n, eps);
+        const f2 ih2 = pk2(ih, ih), sc2 = pk2(sc, sc);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            f2 g[2], b[2];
+            gamma_pair(w_post, (size_t)l + (size_t)j * tpr, g);
+            Io2<float>::unpack(ld_stream(reinterpret_cast<const uint4*>(x) + off + j * tpr), b);
+#pragma unroll
+            for (int k = 0; k < 2; ++k) h[j][k] = mul2(add_rounded(b[k], mul2(mul2(h[j][k], ih2), g[k])), sc2);
+            st_stream(reinterpret_cast<uint4*>(x_out) + off + j * tpr, Io2<float>::pack(h[j]));
+        }
+        const float inv = inv_rms(cta_sum(row_sumsq<VPT>(h), part[3]), inv_n, eps);
+        const f2 inv2 = pk2(inv, inv);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            f2 g[2], o[2];
+            gamma_pair(w_next, (size_t)l + (size_t)j * tpr, g);
+#pragma unroll
+            for (int k = 0; k < 2; ++k) o[k] = mul2(mul2(h[j][k], inv2), g[k]);
+            st_stream(reinterpret_cast<uint4*>(y) + off + j * tpr, Io2<float>::pack(o));
+        }
+        // (four buffers: a row's reductions are separated from the next row's by the barriers in between)
     }
 }
 

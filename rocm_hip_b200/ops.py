@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
 ]
 
@@ -133,6 +133,28 @@ def gpu_gemma_attn_post(x, a, w_a, x_out, w1, y1, w2, y2, n, T, eps, q8=None):
     q = C.byref(q8.struct()) if q8 is not None else None
     _check("gpu_gemma_attn_post", _lib.load().gpu_gemma_attn_post(
         _ptr(x), _ptr(a), _ptr(w_a), _ptr(x_out), _ptr(w1), _ptr(y1), q, _ptr(w2), _ptr(y2), n, T, eps, _stream()))
+
+
+def gpu_gemma_ffn_post(x, mlp, down, wts, ids, exp_scale, n_used, w1, w2, w_post, scale, x_out, w_next, y, n, T, eps,
+                       q8=None):
+    """The FFN epilogue of a Gemma-4 layer (src/gpu_ops.h:62): experts combined, two norms added, residual, scale,
+    the next norm."""
+    q = C.byref(q8.struct()) if q8 is not None else None
+    _check("gpu_gemma_ffn_post", _lib.load().gpu_gemma_ffn_post(
+        _ptr(x), _ptr(mlp), _ptr(down), _ptr(wts), _ptr(ids), _ptr(exp_scale), n_used, _ptr(w1), _ptr(w2), _ptr(w_post),
+        _ptr(scale), _ptr(x_out), _ptr(w_next), _ptr(y), q, n, T, eps, _stream()))
+
+
+def gpu_moe_combine(down, wts, shared, sg, out, n_used, n, T, ids=None, exp_scale=None):
+    """out [T][n] = sum_j wts[t][j] * down[t][j] (+ sg[t] * shared[t]); with exp_scale, each expert's output scaled by
+    exp_scale[ids[t][j]] first (src/gpu_ops.h:40-46)."""
+    lib = _lib.load()
+    if ids is None and exp_scale is None:
+        code = lib.gpu_moe_combine(_ptr(down), _ptr(wts), _ptr(shared), _ptr(sg), _ptr(out), n_used, n, T, _stream())
+    else:
+        code = lib.gpu_moe_combine_scaled(_ptr(down), _ptr(wts), _ptr(shared), _ptr(sg), _ptr(ids), _ptr(exp_scale),
+                                          _ptr(out), n_used, n, T, _stream())
+    _check("gpu_moe_combine", code)
 
 
 def gpu_geglu(gate, up, out, rows, h, gate_stride, up_stride, q8=None):

@@ -142,3 +142,73 @@ def test_chain_argument_errors(ops):
     small = ops.Q8Buffers(256, "cuda")
     with pytest.raises(ops.LayerOpError):
         ops.gpu_gemma_attn_post(x, a, w, t(512), w, t(512), None, None, 512, 4, 1e-6, q8=small)
+
+
+def _moe_case(T, n_used, n, n_expert, seed):
+    down = synth.normal(seed, "mc.d", 0, T * n_used * n).reshape(T, n_used, n)
+    wts = np.abs(synth.normal(seed, "mc.w", 0, T * n_used)).reshape(T, n_used).astype(np.float32)
+    wts /= wts.sum(axis=1, keepdims=True)
+    ids = synth.randint(seed, "mc.i", 0, T * n_used, 0, n_expert).astype(np.int32).reshape(T, n_used)
+    es = synth.normal(seed, "mc.e", 0, n_expert, 1.0, 0.2)
+    return down, wts.astype(np.float32), ids, es
+
+
+@pytest.mark.parametrize("T,n_used,n", [(19, 8, 2048), (7, 10, 1000), (5, 3, 37), (3, 1, 256), (4, 17, 512)])
+def test_moe_combine(ops, oracle, T, n_used, n):
+    """Every variant of src/gpu_ops.hip:245-264 bit for bit: weighted, per-expert scales, gated / ungated shared
+    expert, weight 1."""
+    down, wts, ids, es = _moe_case(T, n_used, n, 64, 5)
+    shared = synth.normal(5, "mc.s", 0, T * n).reshape(T, n)
+    sg = synth.normal(5, "mc.g", 0, T, 0.5, 0.1)
+    dd, dw, di, de, dsh, dsg = dev(down), dev(wts), dev(ids), dev(es), dev(shared), dev(sg)
+    cases = [dict(wts=wts), dict(wts=wts, shared=shared, sg=sg), dict(wts=wts, shared=shared),
+             dict(wts=wts, ids=ids, exp_scale=es), dict(wts=wts, ids=ids, exp_scale=es, shared=shared, sg=sg),
+             dict(wts=None), dict(wts=None, shared=shared, sg=sg)]
+    for kw in cases:
+        out = torch.full((T, n), -1.0, device="cuda")
+        ops.gpu_moe_combine(dd, dw if kw.get("wts") is not None else None, dsh if "shared" in kw else None,
+                            dsg if "sg" in kw else None, out, n_used, n, T, di if "ids" in kw else None,
+                            de if "exp_scale" in kw else None)
+        torch.cuda.synchronize()
+        want = oracle.moe_combine(down, kw.get("wts"), kw.get("shared"), kw.get("sg"), kw.get("ids"), kw.get("exp_scale"))
+        assert np.array_equal(host(out).view(np.uint32), want.view(np.uint32)), sorted(kw)
+    with pytest.raises(ops.LayerOpError) as e:      # exp_scale without ids (src/gpu_ops.cpp:108)
+        ops.gpu_moe_combine(dd, dw, None, None, torch.empty(T, n, device="cuda"), n_used, n, T, None, de)
+    assert e.value.code == 1
+
+
+@pytest.mark.parametrize("n", [256, 1536, 2816, 4096])
+@pytest.mark.parametrize("scaled", [False, True])
+def test_gemma_ffn_post(ops, oracle, n, scaled):
+    T, n_used = 23, 8
+    down, wts, ids, es = _moe_case(T, n_used, n, 128, 6)
+    x = synth.normal(6, "fp.x", 0, T * n).reshape(T, n)
+    mlp = synth.normal(6, "fp.m", 0, T * n).reshape(T, n) * 2
+    w1, w2, w_post, w_next = (synth.normal(6, "fp.w%d" % i, 0, n, 1.0, 0.1) for i in range(4))
+    scale = 0.8125 if scaled else None
+    ds = torch.tensor([scale], device="cuda") if scaled else None
+    x_out, y = torch.empty(T, n, device="cuda"), torch.empty(T, n, device="cuda")
+    q8 = ops.Q8Buffers(T * n, "cuda", xh="bf16")
+    ops.gpu_gemma_ffn_post(dev(x), dev(mlp), dev(down), dev(wts), dev(ids), dev(es) if scaled else None, n_used, dev(w1),
+                           dev(w2), dev(w_post), ds, x_out, dev(w_next), y, n, T, 1e-6, q8=q8)
+    torch.cuda.synchronize()
+    wx, wy = oracle.gemma_ffn_post(x, mlp, down, wts, ids, es if scaled else None, w1, w2, w_post, scale, w_next, 1e-6)
+    assert np.array_equal(host(x_out).view(np.uint32), wx.view(np.uint32))
+    assert np.array_equal(host(y).view(np.uint32), wy.view(np.uint32))
+    want = oracle.quantize_q8(host(y), xh="bf16")
+    for k in ("q0", "d0", "s0", "qK", "dK", "bsK"):
+        assert np.array_equal(host(getattr(q8, k)).view(want[k].dtype), want[k]), k
+    # the unfused branch of the reference (src/qwen_model.cpp:1364-1382): combine, add_normed x3, the plain norm
+    c, h, xo2, y2 = (torch.empty(T, n, device="cuda") for _ in range(4))
+    ops.gpu_moe_combine(dev(down), dev(wts), None, None, c, n_used, n, T, dev(ids) if scaled else None,
+                        dev(es) if scaled else None)
+    ops.gpu_add_rmsnorm(dev(mlp), None, None, dev(w1), h, n, T, 1e-6)
+    ops.gpu_add_normed(h, c, dev(w2), None, h, n, T, 1e-6)
+    ops.gpu_add_normed(dev(x), h, dev(w_post), ds, xo2, n, T, 1e-6)
+    ops.gpu_add_rmsnorm(xo2, None, None, dev(w_next), y2, n, T, 1e-6)
+    torch.cuda.synchronize()
+    assert max_rel_rows(host(xo2), host(x_out)) <= 1e-6 and max_rel_rows(host(y2), host(y)) <= 1e-6
+    with pytest.raises(ops.LayerOpError):
+        xx = dev(x)
+        ops.gpu_gemma_ffn_post(xx, dev(mlp), dev(down), dev(wts), dev(ids), None, n_used, dev(w1), dev(w2), dev(w_post),
+                               None, xx, dev(w_next), y, n, T, 1e-6)

@@ -199,3 +199,27 @@ def test_gemma_chain_statements_against_plain_double_precision(oracle):
     ref = 0.5 * g * (1 + np.tanh(0.7978845608028654 * g * (1 + 0.044715 * g * g))) * D(a)
     assert np.abs(oracle.geglu(x * 2, a) - ref).max() < 4e-6
     assert np.abs(oracle.softcap(a * 20, 30.0) - 30 * np.tanh(D(a) * 20 / 30)).max() < 4e-6
+
+
+def test_moe_combine_and_ffn_post_statements(oracle):
+    """moe_combine / gemma_ffn_post of the oracle (src/gpu_ops.hip:245-264, 608-655) against double precision."""
+    import numpy as np
+    rng = np.random.default_rng(13)
+    T, U, n, E = 4, 6, 512, 32
+    down = rng.standard_normal((T, U, n)).astype(np.float32)
+    wts = rng.random((T, U)).astype(np.float32)
+    ids = rng.integers(0, E, (T, U)).astype(np.int32)
+    es = (1 + 0.2 * rng.standard_normal(E)).astype(np.float32)
+    shared, sg = rng.standard_normal((T, n)).astype(np.float32), rng.random(T).astype(np.float32)
+    D = lambda t: np.asarray(t, dtype=np.float64)
+    ref = (D(down) * D(es)[ids][:, :, None] * D(wts)[:, :, None]).sum(axis=1) + D(shared) * D(sg)[:, None]
+    assert np.abs(oracle.moe_combine(down, wts, shared, sg, ids, es) - ref).max() < 4e-6
+    assert np.abs(oracle.moe_combine(down, None, shared, sg) - (D(down).sum(axis=1) + D(shared))).max() < 4e-6
+    rms = lambda v: D(v) / np.sqrt((D(v) ** 2).mean(axis=1, keepdims=True) + 1e-6)
+    x, mlp = rng.standard_normal((T, n)).astype(np.float32), rng.standard_normal((T, n)).astype(np.float32)
+    w = [(1 + 0.1 * rng.standard_normal(n)).astype(np.float32) for _ in range(4)]
+    xo, y = oracle.gemma_ffn_post(x, mlp, down, wts, ids, es, w[0], w[1], w[2], 0.75, w[3], 1e-6)
+    c = (D(down) * D(es)[ids][:, :, None] * D(wts)[:, :, None]).sum(axis=1)
+    h = rms(mlp) * w[0] + rms(c) * w[1]
+    rxo = (D(x) + rms(h) * w[2]) * 0.75
+    assert np.abs(xo - rxo).max() < 4e-6 and np.abs(y - rms(rxo) * w[3]).max() < 8e-6
