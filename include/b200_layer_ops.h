@@ -167,6 +167,20 @@ cudaError_t gpu_kv_store_q(const float* src, void* cache, int n_vals, const int*
 cudaError_t gpu_kv_store_q_bf16(const uint16_t* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
                                 int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream);
 
+/* The rotation the reference applies for a quantised cache (ATTN_KV_ROT; hadamard_rot, src/attention.hip:238-263,
+ * 285-293): an orthonormal Walsh-Hadamard transform in blocks of `block` values (64, 128, 256 or 512), its own inverse.
+ * q and K rows are rotated in blocks of hadamard_k(head_dim) (64 doubled while it divides head_dim), V in blocks of
+ * 64. gpu_hadamard_rot: rows of D values (D % block == 0), out may be x. gpu_kv_store_q_rot: gpu_kv_store_q with
+ * the values rotated in blocks of rot_block (n_vals % rot_block == 0; 0: none) before they are quantised. */
+cudaError_t gpu_hadamard_rot(const float* x, float* out, long long rows, int D, int block, cudaStream_t stream);
+cudaError_t gpu_hadamard_rot_bf16(const uint16_t* x, uint16_t* out, long long rows, int D, int block, cudaStream_t stream);
+cudaError_t gpu_kv_store_q_rot(const float* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
+                               int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, int rot_block,
+                               cudaStream_t stream);
+cudaError_t gpu_kv_store_q_rot_bf16(const uint16_t* src, void* cache, int n_vals, const int* positions, int pos0,
+                                    long long T, int kv_stride, int kv_shift, long long kv_bstride, int kv_quant,
+                                    int rot_block, cudaStream_t stream);
+
 /* Token-embedding gather + dequantisation: out row t = decode(table row tokens[t]) * scale, the loop of
  * src/qwen_model.cpp:980-986 (scale: embd_scale of :1409; pass 1 for none). type: 8 (Q8_0) or 2 (Q4_0), the ggml
  * ids of src/quant_types.h:19-27; row_bytes as qt_row_size(type, E) or larger (a row stride); E % 32 == 0.

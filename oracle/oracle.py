@@ -235,6 +235,30 @@ def quantize_q8(x, xh=None, int8=True):
     return o
 
 
+def hadamard_k(D):
+    """Block of the q / K rotation: 64, doubled while it divides D (src/attention.hip:243-247)."""
+    r = 64
+    while D % (2 * r) == 0:
+        r *= 2
+    return r
+
+
+def hadamard_rot(x, N):
+    """The reference's hadamard_rot (src/attention.hip:251-263) on the last axis in blocks of N: butterflies
+    s = 1, 2, ..., N / 2 in that order, value d becoming (d & s) ? v[d ^ s] - v[d] : v[d] + v[d ^ s] in fp32, then a
+    multiply by the float 1 / sqrtf(N)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    v = x.reshape(-1, N).copy()
+    d = np.arange(N)
+    s = 1
+    while s < N:
+        y = v[:, d ^ s]
+        v = np.where((d & s) != 0, y - v, v + y).astype(np.float32)
+        s <<= 1
+    r = np.float32(1.0) / np.sqrt(np.float32(N))
+    return (v * r).astype(np.float32).reshape(x.shape)
+
+
 def kv_quant_rows(x, kq):
     """Quantised KV cache rows of x [T][n_vals] fp32 (n_vals % 32 == 0), by the reference's kvq_store
     (src/attention.hip:159-178; row layout :44-50), every float32 operation rounded on its own. Returns (values,

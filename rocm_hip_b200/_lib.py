@@ -40,6 +40,10 @@ SIGNATURES = {
     "gpu_swiglu_rows_bf16": (_i, [_p, _p, _p, _ll, _i, _ll, _ll, _p]),
     "gpu_qk_norm_rope": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_qk_norm_rope_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
+    "gpu_hadamard_rot": (_i, [_p, _p, _ll, _i, _i, _p]),
+    "gpu_hadamard_rot_bf16": (_i, [_p, _p, _ll, _i, _i, _p]),
+    "gpu_kv_store_q_rot": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _i, _i, _p]),
+    "gpu_kv_store_q_rot_bf16": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _i, _i, _p]),
     "gpu_add_normed": (_i, [_p, _p, _p, _p, _p, _i, _i, _f, _p]),
     "gpu_gemma_attn_post": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p]),
     "gpu_gemma_ffn_post": (_i, [_p] * 6 + [_i] + [_p] * 8 + [_i, _i, _f, _p]),

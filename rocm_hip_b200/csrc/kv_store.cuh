@@ -44,6 +44,82 @@ k_kv_store_f16(const IO* src, __half* cache, int n_vals, const int* positions, i
     }
 }
 
+// Orthonormal Walsh-Hadamard transform of blocks of N values (N = 64, 128, 256 or 512), as the reference rotates q, K
+// and V for a quantised cache (hadamard_rot, src/attention.hip:238-263): stages s = 1, 2, ..., N / 2 in that order,
+// value d becoming (d & s) ? v[d ^ s] - v[d] : v[d] + v[d ^ s], then one multiply by 1 / sqrt(N). A lane holds values
+// 8 lane .. 8 lane + 7 of its warp's 256: stages below 8 stay inside the lane, stages up to 128 are one shuffle per
+// value, and the last stage of a 512-block pairs two neighbouring warps of the CTA through shared memory (xchg:
+// 8 * blockDim.x floats; the pair meets at its own named barrier, so other warps may have left the kernel). Same
+// operations in the same order as the reference's shared-memory butterflies, so the same bits.
+// Callers keep 256-value chunks on consecutive warps: thread t of the CTA holds octet (CTA base + t).
+__device__ __forceinline__ void wht8(float (&x)[8], int N, float* xchg) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int s = 1; s < 8; s <<= 1) {
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = (e & s) ? __fsub_rn(x[e ^ s], x[e]) : __fadd_rn(x[e], x[e ^ s]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = y[e];
+    }
+    const int in_warp = N < 256 ? N / 8 : 32;
+    for (int s = 1; s < in_warp; s <<= 1) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float y = __shfl_xor_sync(0xffffffffu, x[e], s);
+            x[e] = (lane & s) ? __fsub_rn(y, x[e]) : __fadd_rn(x[e], y);
+        }
+    }
+    if (N == 512) {   // uniform
+        const int warp = threadIdx.x >> 5, bar = 1 + (warp >> 1);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xchg[e * blockDim.x + threadIdx.x] = x[e];
+        asm volatile("bar.sync %0, 64;" ::"r"(bar) : "memory");
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float y = xchg[e * blockDim.x + (threadIdx.x ^ 32)];
+            x[e] = (warp & 1) ? __fsub_rn(y, x[e]) : __fadd_rn(x[e], y);
+        }
+        asm volatile("bar.sync %0, 64;" ::"r"(bar) : "memory");   // the buffer is written again on the next step
+    }
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn((float)N));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = __fmul_rn(x[e], r);
+}
+
+// out = the transform of x in blocks of N, rows of any length that is a multiple of N (total values a multiple of N)
+template <typename IO>
+__global__ void __launch_bounds__(256)
+k_hadamard_rot(const IO* x, IO* out, long long n_total, int N) {
+    __shared__ float xchg[8 * 256];
+    const long long total = n_total / 8;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i - threadIdx.x % 32 < total; i += stride) {
+        float v[8];
+        const bool live = i < total;
+        if (live) {
+            if (sizeof(IO) == 4) {
+                Io<float>::unpack(ld_stream(reinterpret_cast<const float*>(x) + i * 8), v);
+                Io<float>::unpack(ld_stream(reinterpret_cast<const float*>(x) + i * 8 + 4), v + 4);
+            } else {
+                Io<__nv_bfloat16>::unpack(ld_stream(reinterpret_cast<const __nv_bfloat16*>(x) + i * 8), v);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+        }
+        wht8(v, N, xchg);
+        if (live) {
+            if (sizeof(IO) == 4) {
+                st_stream(reinterpret_cast<float*>(out) + i * 8, Io<float>::pack(v));
+                st_stream(reinterpret_cast<float*>(out) + i * 8 + 4, Io<float>::pack(v + 4));
+            } else {
+                st_stream(reinterpret_cast<__nv_bfloat16*>(out) + i * 8, Io<__nv_bfloat16>::pack(v));
+            }
+        }
+    }
+}
+
 // Quantised cache rows (src/attention.hip:44-50, kvq_store :159-178): a row holds d_row values and then one fp16 scale
 // per 32 values; d_row = kv_stride * 32 / 17 (Q8_0) or kv_stride * 32 / 9 (Q4_0), kv_stride still in fp16 units.
 //   KQ 1, Q8_0: d = amax / 127; q = rint(x * (1 / d)) as int8 (0 when d == 0); scales start at byte d_row.
@@ -53,11 +129,13 @@ k_kv_store_f16(const IO* src, __half* cache, int n_vals, const int* positions, i
 // The scale is stored rounded to fp16; the values are quantised with the unrounded d. Every operation rounds on its
 // own. A thread owns 8 consecutive values (32 or 16 bytes read, 8 or 4 bytes written: for Q4_0 its eight values are
 // exactly one 32-bit word of the row), four neighbouring lanes own a block and share its maximum with two shuffles.
-// U octets per thread and step are loaded before the first is used.
+// U octets per thread and step are loaded before the first is used. rot = 64, 128, 256 or 512: the values are rotated in
+// blocks of rot (wht8) before they are quantised, attn_prep's ATTN_KV_ROT (src/attention.hip:290-293).
 template <typename IO, int KQ, int U>
 __global__ void __launch_bounds__(256)
 k_kv_store_q(const IO* src, __half* cache, int n_vals, const int* positions, int pos0, long long T, int kv_stride,
-             int kv_shift, long long kv_bstride) {
+             int kv_shift, long long kv_bstride, int rot) {
+    __shared__ float xchg[8 * 256];
     const int opr = n_vals / 8;                       // octets per row
     const long long total = T * opr;
     const int d_row = kv_stride * 32 / (KQ == 2 ? 9 : 17);
@@ -80,6 +158,10 @@ k_kv_store_q(const IO* src, __half* cache, int n_vals, const int* positions, int
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[j][e] = 0.0f;
             }
+        }
+        if (rot) {   // uniform: rotate in blocks of rot values first (n_vals % rot == 0, so a block is whole)
+#pragma unroll
+            for (int j = 0; j < U; ++j) wht8(x[j], rot, xchg);
         }
 #pragma unroll
         for (int j = 0; j < U; ++j) {

@@ -410,10 +410,12 @@ cudaError_t launch_kv_store(const IO* src, __half* cache, int n_vals, const int*
 
 template <typename IO>
 cudaError_t launch_kv_store_q(const IO* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
-                              int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream) {
+                              int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, int rot,
+                              cudaStream_t stream) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (!src || !cache || n_vals <= 0 || n_vals % 32 != 0 || T <= 0 || kv_shift < 0 || kv_shift > 30 || kv_stride <= 0 ||
-        kv_bstride < 0 || (!positions && pos0 < 0) || (kv_quant != 1 && kv_quant != 2))
+        kv_bstride < 0 || (!positions && pos0 < 0) || (kv_quant != 1 && kv_quant != 2) ||
+        (rot != 0 && ((rot != 64 && rot != 128 && rot != 256 && rot != 512) || n_vals % rot != 0)))
         return cudaErrorInvalidValue;
     // the row must hold n_vals values and their scales: d_row = kv_stride * 32 / 17 (or / 9), as src/attention.hip:50
     const long long d_row = (long long)kv_stride * 32 / (kv_quant == 2 ? 9 : 17);
@@ -432,9 +434,21 @@ cudaError_t launch_kv_store_q(const IO* src, void* cache, int n_vals, const int*
     if (grid > cap) grid = cap;
     __half* c = reinterpret_cast<__half*>(cache);
     if (kv_quant == 1)
-        k_kv_store_q<IO, 1, U><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride);
+        k_kv_store_q<IO, 1, U><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, rot);
     else
-        k_kv_store_q<IO, 2, U><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride);
+        k_kv_store_q<IO, 2, U><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, rot);
+    return launched();
+}
+
+template <typename IO>
+cudaError_t launch_hadamard(const IO* x, IO* out, long long rows, int D, int N, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (!x || !out || rows <= 0 || D <= 0 || (N != 64 && N != 128 && N != 256 && N != 512) || D % N != 0 || !al16(x) || !al16(out))
+        return cudaErrorInvalidValue;
+    const long long total = rows * D, cap = resident_ctas(256) * 8;
+    long long grid = (total / 8 + 255) / 256;
+    if (grid > cap) grid = cap;
+    k_hadamard_rot<IO><<<(unsigned)grid, 256, 0, stream>>>(x, out, total, N);
     return launched();
 }
 
@@ -698,13 +712,36 @@ cudaError_t gpu_kv_store_f16_bf16(const uint16_t* src, uint16_t* cache, int n_va
 
 cudaError_t gpu_kv_store_q(const float* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
                            int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream) {
-    return launch_kv_store_q<float>(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, kv_quant, stream);
+    return launch_kv_store_q<float>(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, kv_quant, 0, stream);
+}
+
+cudaError_t gpu_kv_store_q_rot(const float* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
+                               int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, int rot_block,
+                               cudaStream_t stream) {
+    return launch_kv_store_q<float>(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, kv_quant,
+                                    rot_block, stream);
+}
+
+cudaError_t gpu_kv_store_q_rot_bf16(const uint16_t* src, void* cache, int n_vals, const int* positions, int pos0,
+                                    long long T, int kv_stride, int kv_shift, long long kv_bstride, int kv_quant,
+                                    int rot_block, cudaStream_t stream) {
+    return launch_kv_store_q<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(src), cache, n_vals, positions, pos0, T,
+                                            kv_stride, kv_shift, kv_bstride, kv_quant, rot_block, stream);
+}
+
+cudaError_t gpu_hadamard_rot(const float* x, float* out, long long rows, int D, int block, cudaStream_t stream) {
+    return launch_hadamard<float>(x, out, rows, D, block, stream);
+}
+
+cudaError_t gpu_hadamard_rot_bf16(const uint16_t* x, uint16_t* out, long long rows, int D, int block, cudaStream_t stream) {
+    return launch_hadamard<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(out),
+                                          rows, D, block, stream);
 }
 
 cudaError_t gpu_kv_store_q_bf16(const uint16_t* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
                                 int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream) {
     return launch_kv_store_q<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(src), cache, n_vals, positions, pos0, T,
-                                            kv_stride, kv_shift, kv_bstride, kv_quant, stream);
+                                            kv_stride, kv_shift, kv_bstride, kv_quant, 0, stream);
 }
 
 cudaError_t gpu_embed_rows(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens, float* out,

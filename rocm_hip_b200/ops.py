@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
 ]
 
@@ -177,13 +177,27 @@ def gpu_kv_store_f16(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift
                                   kv_bstride, _stream()))
 
 
-def gpu_kv_store_q(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, kv_quant):
+def gpu_kv_store_q(src, cache, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, kv_quant, rot_block=0):
     """Rows of src (fp32 or bf16) quantised to Q8_0 (kv_quant 1) or Q4_0 (2) into the block-major KV cache `cache`
-    (a CUDA tensor of any 16-bit or byte dtype; kv_stride / kv_bstride in 2-byte units)."""
+    (a CUDA tensor of any 16-bit or byte dtype; kv_stride / kv_bstride in 2-byte units); rot_block 64 / 128 / 256:
+    rotated in blocks of that many values first."""
     lib = _lib.load()
-    fn = lib.gpu_kv_store_q if src.dtype == torch.float32 else lib.gpu_kv_store_q_bf16
-    _check("gpu_kv_store_q", fn(_ptr(src), _ptr(cache), n_vals, _ptr(positions), pos0, T, kv_stride, kv_shift,
-                                kv_bstride, kv_quant, _stream()))
+    if rot_block:
+        fn = lib.gpu_kv_store_q_rot if src.dtype == torch.float32 else lib.gpu_kv_store_q_rot_bf16
+        code = fn(_ptr(src), _ptr(cache), n_vals, _ptr(positions), pos0, T, kv_stride, kv_shift, kv_bstride, kv_quant,
+                  rot_block, _stream())
+    else:
+        fn = lib.gpu_kv_store_q if src.dtype == torch.float32 else lib.gpu_kv_store_q_bf16
+        code = fn(_ptr(src), _ptr(cache), n_vals, _ptr(positions), pos0, T, kv_stride, kv_shift, kv_bstride, kv_quant,
+                  _stream())
+    _check("gpu_kv_store_q", code)
+
+
+def gpu_hadamard_rot(x, out, rows, D, block):
+    """Orthonormal Walsh-Hadamard transform of rows of D values in blocks of `block` (src/attention.hip:238-263)."""
+    lib = _lib.load()
+    fn = lib.gpu_hadamard_rot if x.dtype == torch.float32 else lib.gpu_hadamard_rot_bf16
+    _check("gpu_hadamard_rot", fn(_ptr(x), _ptr(out), rows, D, block, _stream()))
 
 
 def gpu_moe_max_tiles(T, n_used, n_expert, tile):

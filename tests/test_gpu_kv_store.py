@@ -134,3 +134,53 @@ def test_quantised_argument_errors(ops):
         assert e.value.code == 1
     ops.gpu_kv_store_q(s, c, 256, None, 0, 4, 72, 30, 0, 2)     # the Q4_0 row of 256 values is 72 halves
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("D,N", [(64, 64), (128, 128), (256, 256), (512, 512), (192, 64), (1024, 512), (384, 128)])
+def test_hadamard_rotation_is_the_reference_butterfly(ops, oracle, D, N):
+    """hadamard_rot (src/attention.hip:251-263): the same butterflies in the same order, so the same bits; its own
+    inverse up to rounding; norms preserved; bf16 rows round once."""
+    rows = 333
+    x = synth.normal(0, "wht.x", 0, rows * D).reshape(rows, D) * 3
+    out = torch.empty(rows, D, device="cuda")
+    ops.gpu_hadamard_rot(dev(x), out, rows, D, N)
+    torch.cuda.synchronize()
+    want = oracle.hadamard_rot(x, N)
+    assert np.array_equal(host(out).view(np.uint32), want.view(np.uint32))
+    back = out.clone()
+    ops.gpu_hadamard_rot(back, back, rows, D, N)                       # in place
+    torch.cuda.synchronize()
+    assert np.abs(host(back) - x).max() <= 2e-5 * np.abs(x).max()
+    assert np.allclose(np.linalg.norm(host(out), axis=1), np.linalg.norm(x, axis=1), rtol=1e-5)
+    xb = oracle.f32_to_bf16(x).reshape(rows, D)
+    ob = torch.empty(rows, D, device="cuda", dtype=torch.bfloat16)
+    ops.gpu_hadamard_rot(dev(xb, torch.bfloat16), ob, rows, D, N)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(ob), oracle.f32_to_bf16(oracle.hadamard_rot(oracle.bf16_to_f32(xb).reshape(rows, D), N)).reshape(rows, D))
+    with pytest.raises(ops.LayerOpError):
+        ops.gpu_hadamard_rot(dev(x), out, rows, D, 32)
+
+
+@pytest.mark.parametrize("kq", [1, 2])
+@pytest.mark.parametrize("n_vals,rot", [(1024, 128), (1024, 64), (512, 256), (256, 64), (1024, 512), (512, 512)])
+def test_rotated_quantised_rows(ops, oracle, kq, n_vals, rot):
+    """attn_prep with ATTN_KV_ROT (src/attention.hip:290-295): rotate in blocks, then quantise -- one launch, the bits
+    of the rotation followed by the quantiser; and q . k is unchanged when both are rotated."""
+    T = 45
+    src, d_src = _quant_case(oracle, T, n_vals, False)
+    src[3, 0] = 7.0                                                    # (a finite outlier: 1e30 would overflow the sums)
+    d_src = dev(src)
+    kv_stride = n_vals * (17 if kq == 1 else 9) // 32
+    cache = torch.zeros(T * kv_stride, device="cuda", dtype=torch.int16)
+    ops.gpu_kv_store_q(d_src, cache, n_vals, None, 0, T, kv_stride, 30, 0, kq, rot_block=rot)
+    torch.cuda.synchronize()
+    want_q, want_d = oracle.kv_quant_rows(oracle.hadamard_rot(src, rot), kq)
+    got = cache.cpu().numpy().view(np.uint8).reshape(T, kv_stride * 2)
+    vbytes = n_vals if kq == 1 else n_vals // 2
+    assert np.array_equal(got[:, :vbytes], want_q.view(np.uint8).reshape(T, vbytes))
+    assert np.array_equal(got[:, vbytes:vbytes + n_vals // 16], want_d.view(np.uint8).reshape(T, n_vals // 16))
+    q = synth.normal(0, "wht.q", 0, T * n_vals).reshape(T, n_vals)
+    dots = (oracle.hadamard_rot(q, rot).astype(np.float64) * oracle.hadamard_rot(src, rot)).sum(axis=1)
+    assert np.allclose(dots, (q.astype(np.float64) * src).sum(axis=1), rtol=1e-4, atol=1e-3)
+    with pytest.raises(ops.LayerOpError):
+        ops.gpu_kv_store_q(d_src, cache, n_vals, None, 0, T, kv_stride, 30, 0, kq, rot_block=96)

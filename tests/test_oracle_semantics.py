@@ -223,3 +223,17 @@ def test_moe_combine_and_ffn_post_statements(oracle):
     h = rms(mlp) * w[0] + rms(c) * w[1]
     rxo = (D(x) + rms(h) * w[2]) * 0.75
     assert np.abs(xo - rxo).max() < 4e-6 and np.abs(y - rms(rxo) * w[3]).max() < 8e-6
+
+
+def test_hadamard_rotation_statement(oracle):
+    """The butterfly statement (src/attention.hip:251-263) is the orthonormal Sylvester-Hadamard matrix: symmetric,
+    its own inverse, entries +-1 / sqrt(N); block size rule of hadamard_k (:243-247)."""
+    import numpy as np
+    assert [oracle.hadamard_k(D) for D in (64, 128, 256, 192, 512, 96 * 2)] == [64, 128, 256, 64, 512, 64]
+    for N in (64, 128, 256, 512):
+        H = oracle.hadamard_rot(np.eye(N, dtype=np.float32), N).astype(np.float64)
+        assert np.allclose(H, H.T) and np.allclose(H @ H, np.eye(N), atol=1e-6)
+        assert np.allclose(np.abs(H), 1 / np.sqrt(N), rtol=1e-6)
+        i, j = np.meshgrid(np.arange(N), np.arange(N), indexing="ij")
+        sign = 1 - 2 * (np.array([bin(v).count("1") for v in (i & j).ravel()]).reshape(N, N) & 1)
+        assert np.array_equal(np.sign(H), sign)
