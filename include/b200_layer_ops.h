@@ -65,7 +65,9 @@ cudaError_t gpu_swiglu(const float* g, const float* u, float* out, int n, const 
  * expert for expert-tiled consumers: tok_rows[i] = token, pair_rows[i] = token * n_used + slot of the i-th entry in
  * expert order (tok_rows / pair_rows: T * n_used ints); each expert's run cut into tiles of up to `tile` entries,
  * tile_e / tile_start / tile_n (gpu_moe_max_tiles entries each), *n_tiles of them. n_expert <= 1024. Unlike the
- * reference, the order inside an expert's run is fixed too (ascending pair index). */
+ * reference, the order inside an expert's run is fixed too (ascending pair index). Batches of more than 8192 entries
+ * are grouped by three launches over the whole device and need n_segments * n_expert ints of work memory: this entry
+ * point takes it from a few slots inside the library, used in turn (see gpu_moe_group_scratch below). */
 #ifndef GPU_OPS_H
 static inline int gpu_moe_max_tiles(int T, int n_used, int n_expert, int tile) {
     const int n = T * n_used, bound = n_expert + n / tile;
@@ -166,6 +168,15 @@ cudaError_t gpu_kv_store_q(const float* src, void* cache, int n_vals, const int*
                            int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream);
 cudaError_t gpu_kv_store_q_bf16(const uint16_t* src, void* cache, int n_vals, const int* positions, int pos0, long long T,
                                 int kv_stride, int kv_shift, long long kv_bstride, int kv_quant, cudaStream_t stream);
+
+/* gpu_moe_group with the caller's work memory, for a host that keeps more than four long groupings in flight on one
+ * device at a time (different streams) or wants none of the library's: scratch holds at least
+ * gpu_moe_group_scratch_ints(T, n_used, n_expert) ints (0 for batches of up to 8192 entries; then scratch may be
+ * NULL). Same results as gpu_moe_group. */
+size_t gpu_moe_group_scratch_ints(int T, int n_used, int n_expert);
+cudaError_t gpu_moe_group_scratch(const int* ids, int T, int n_used, int n_expert, int tile, int* tok_rows, int* pair_rows,
+                                  int* n_tiles, int* tile_e, int* tile_start, int* tile_n, int* scratch,
+                                  size_t scratch_ints, cudaStream_t stream);
 
 /* The rotation the reference applies for a quantised cache (ATTN_KV_ROT; hadamard_rot, src/attention.hip:238-263,
  * 285-293): an orthonormal Walsh-Hadamard transform in blocks of `block` values (64, 128, 256 or 512), its own inverse.

@@ -40,6 +40,8 @@ SIGNATURES = {
     "gpu_swiglu_rows_bf16": (_i, [_p, _p, _p, _ll, _i, _ll, _ll, _p]),
     "gpu_qk_norm_rope": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_qk_norm_rope_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
+    "gpu_moe_group_scratch_ints": (_sz, [_i, _i, _i]),
+    "gpu_moe_group_scratch": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "gpu_hadamard_rot": (_i, [_p, _p, _ll, _i, _i, _p]),
     "gpu_hadamard_rot_bf16": (_i, [_p, _p, _ll, _i, _i, _p]),
     "gpu_kv_store_q_rot": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _i, _i, _p]),

@@ -131,11 +131,11 @@ k_hadamard_rot(const IO* x, IO* out, long long n_total, int N) {
 // exactly one 32-bit word of the row), four neighbouring lanes own a block and share its maximum with two shuffles.
 // U octets per thread and step are loaded before the first is used. rot = 64, 128, 256 or 512: the values are rotated in
 // blocks of rot (wht8) before they are quantised, attn_prep's ATTN_KV_ROT (src/attention.hip:290-293).
-template <typename IO, int KQ, int U>
+template <typename IO, int KQ, int U, bool ROT>
 __global__ void __launch_bounds__(256)
 k_kv_store_q(const IO* src, __half* cache, int n_vals, const int* positions, int pos0, long long T, int kv_stride,
              int kv_shift, long long kv_bstride, int rot) {
-    __shared__ float xchg[8 * 256];
+    __shared__ float xchg[ROT ? 8 * 256 : 1];
     const int opr = n_vals / 8;                       // octets per row
     const long long total = T * opr;
     const int d_row = kv_stride * 32 / (KQ == 2 ? 9 : 17);
@@ -159,7 +159,7 @@ k_kv_store_q(const IO* src, __half* cache, int n_vals, const int* positions, int
                 for (int e = 0; e < 8; ++e) x[j][e] = 0.0f;
             }
         }
-        if (rot) {   // uniform: rotate in blocks of rot values first (n_vals % rot == 0, so a block is whole)
+        if (ROT) {   // rotate in blocks of rot values first (n_vals % rot == 0, so a block is whole)
 #pragma unroll
             for (int j = 0; j < U; ++j) wht8(x[j], rot, xchg);
         }

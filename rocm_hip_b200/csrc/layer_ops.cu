@@ -433,10 +433,10 @@ cudaError_t launch_kv_store_q(const IO* src, void* cache, int n_vals, const int*
     long long grid = (octets + 256 * U - 1) / (256 * U);
     if (grid > cap) grid = cap;
     __half* c = reinterpret_cast<__half*>(cache);
-    if (kv_quant == 1)
-        k_kv_store_q<IO, 1, U><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, rot);
-    else
-        k_kv_store_q<IO, 2, U><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, rot);
+#define KVQ(KQ, R) k_kv_store_q<IO, KQ, U, R><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, rot)
+    if (kv_quant == 1) { if (rot) KVQ(1, true); else KVQ(1, false); }
+    else { if (rot) KVQ(2, true); else KVQ(2, false); }
+#undef KVQ
     return launched();
 }
 
@@ -449,6 +449,61 @@ cudaError_t launch_hadamard(const IO* x, IO* out, long long rows, int D, int N, 
     long long grid = (total / 8 + 255) / 256;
     if (grid > cap) grid = cap;
     k_hadamard_rot<IO><<<(unsigned)grid, 256, 0, stream>>>(x, out, total, N);
+    return launched();
+}
+
+// ---------------------------------------------------------------- MoE grouping
+
+// Up to this many entries one CTA groups the batch in shared memory (no scratch, one launch); beyond it the segment
+// kernels take over
+constexpr int MOE_SINGLE_CTA_MAX = 8192;
+constexpr int MOE_MAX_SEGS = 1024;
+constexpr int MOE_SCRATCH_SLOTS = 4;
+
+// Scratch of the reference-named launcher, which has no scratch argument: a few slots used in turn, so that calls
+// still queued on other streams do not meet each other's counters (a caller with more than MOE_SCRATCH_SLOTS long
+// groupings in flight on one device passes its own scratch: gpu_moe_group_scratch)
+__device__ int g_moe_scratch[MOE_SCRATCH_SLOTS][MOE_MAX_SEGS * MOE_MAX_EXPERTS];
+std::atomic<unsigned> g_moe_slot{0};
+
+// Segments of a batch of n entries: at most MOE_MAX_SEGS, each a multiple of 32 entries and at least 1024
+int moe_segments(int n, int* seg_len) {
+    long long len = ((long long)n + MOE_MAX_SEGS - 1) / MOE_MAX_SEGS;
+    len = (len + 31) / 32 * 32;
+    if (len < 1024) len = 1024;
+    if (seg_len) *seg_len = (int)len;
+    return (int)((n + len - 1) / len);
+}
+
+cudaError_t launch_moe_group(const int* ids, int T, int n_used, int n_expert, int tile, int* tok_rows, int* pair_rows,
+                             int* n_tiles, int* tile_e, int* tile_start, int* tile_n, int* scratch, size_t scratch_ints,
+                             cudaStream_t stream) {
+    const int n = T * n_used;
+    if (n <= MOE_SINGLE_CTA_MAX) {
+        k_moe_group<<<1, 1024, 0, stream>>>(ids, T, n_used, n_expert, tile, tok_rows, pair_rows, n_tiles, tile_e,
+                                            tile_start, tile_n);
+        return launched();
+    }
+    int seg_len = 0;
+    const int n_segs = moe_segments(n, &seg_len);
+    if (!scratch) {
+        void* base = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&base, g_moe_scratch);
+        if (e != cudaSuccess) return e;
+        const unsigned slot = g_moe_slot.fetch_add(1, std::memory_order_relaxed) % MOE_SCRATCH_SLOTS;
+        scratch = static_cast<int*>(base) + (size_t)slot * MOE_MAX_SEGS * MOE_MAX_EXPERTS;
+    }
+    (void)scratch_ints;
+    const int ctas = (n_segs + MOE_SEG_WARPS - 1) / MOE_SEG_WARPS;
+    k_moe_seg_count<<<ctas, 32 * MOE_SEG_WARPS, 0, stream>>>(ids, n, n_expert, seg_len, n_segs, scratch);
+    cudaError_t e = launched();
+    if (e != cudaSuccess) return e;
+    k_moe_seg_scan<<<1, 1024, 0, stream>>>(n_expert, next_pow2(n_expert), tile, n_segs, scratch, n_tiles, tile_e, tile_start,
+                                           tile_n);
+    e = launched();
+    if (e != cudaSuccess) return e;
+    k_moe_seg_scatter<<<ctas, 32 * MOE_SEG_WARPS, 0, stream>>>(ids, n, n_used, n_expert, seg_len, n_segs, scratch, tok_rows,
+                                                               pair_rows);
     return launched();
 }
 
@@ -639,9 +694,26 @@ cudaError_t gpu_moe_group(const int* ids, int T, int n_used, int n_expert, int t
     if (T <= 0 || n_used <= 0 || n_expert <= 0 || n_expert > MOE_MAX_EXPERTS || tile <= 0 ||
         (long long)T * n_used > INT_MAX)
         return cudaErrorInvalidValue;
-    k_moe_group<<<1, 1024, 0, stream>>>(ids, T, n_used, n_expert, tile, tok_rows, pair_rows, n_tiles, tile_e, tile_start,
-                                        tile_n);
-    return launched();
+    return launch_moe_group(ids, T, n_used, n_expert, tile, tok_rows, pair_rows, n_tiles, tile_e, tile_start, tile_n,
+                            nullptr, 0, stream);
+}
+
+size_t gpu_moe_group_scratch_ints(int T, int n_used, int n_expert) {
+    const long long n = (long long)T * n_used;
+    if (T <= 0 || n_used <= 0 || n_expert <= 0 || n > INT_MAX || n <= MOE_SINGLE_CTA_MAX) return 0;
+    return (size_t)moe_segments((int)n, nullptr) * (size_t)n_expert;
+}
+
+cudaError_t gpu_moe_group_scratch(const int* ids, int T, int n_used, int n_expert, int tile, int* tok_rows, int* pair_rows,
+                                  int* n_tiles, int* tile_e, int* tile_start, int* tile_n, int* scratch,
+                                  size_t scratch_ints, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || n_used <= 0 || n_expert <= 0 || n_expert > MOE_MAX_EXPERTS || tile <= 0 ||
+        (long long)T * n_used > INT_MAX || scratch_ints < gpu_moe_group_scratch_ints(T, n_used, n_expert) ||
+        (!scratch && gpu_moe_group_scratch_ints(T, n_used, n_expert) > 0))
+        return cudaErrorInvalidValue;
+    return launch_moe_group(ids, T, n_used, n_expert, tile, tok_rows, pair_rows, n_tiles, tile_e, tile_start, tile_n,
+                            scratch, scratch_ints, stream);
 }
 
 cudaError_t gpu_add_rmsnorm_f32(const float* x_in, const float* add, float* x_out, const float* w, float* y, int n,

@@ -9,11 +9,11 @@
 // expert, and every entry lands at (start of its expert's run) + (entries of that expert in earlier ranges) + (its
 // rank inside its own range).
 //
-// One CTA of 1024 threads, as in the reference; n_expert <= 1024. Work memory: shared memory only (no scratch).
+// k_moe_group: one CTA of 1024 threads, as in the reference; n_expert <= 1024. Work memory: shared memory only.
 // The per-range, per-expert bookkeeping would need ranges x experts counters, so ranges are processed in rounds of
 // 1024 entries (one entry per thread, in index order): a round ranks its entries with a warp match and a scan over
-// the 32 warps, then advances the experts' running offsets. Cost is O(n / 1024) rounds; the reference's batches hold
-// at most a few thousand tokens.
+// the 32 warps, then advances the experts' running offsets. Cost is O(n / 1024) rounds: right for the reference's
+// batches of a few thousand tokens; longer batches take the segment kernels at the end of this file.
 
 #ifndef B200_MOE_GROUP_CUH
 #define B200_MOE_GROUP_CUH
@@ -104,6 +104,136 @@ k_moe_group(const int* ids, int T, int n_used, int n_expert, int tile, int* tok_
         __syncthreads();
         if (leader) round_cnt[e] = 0;
         __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Long batches: the same result (bit for bit the arrays k_moe_group writes) from three launches that use the whole
+// device. The n entries are cut into segments of seg_len consecutive entries (a multiple of 32), one warp each:
+//   k_moe_seg_count    counts [seg][expert]: entries of each expert in each segment (shared-memory histogram per warp)
+//   k_moe_seg_scan     one CTA, thread e: run start of expert e (scan of the totals), the tiles, and counts [seg][e]
+//                      turned into the position of segment seg's first entry of expert e
+//   k_moe_seg_scatter  each warp walks its segment in index order, 32 entries per step, ranks the lanes of one expert
+//                      with a warp match and places them at the running position of that expert
+// Work memory: n_segs * n_expert ints of device scratch. A warp's shared-memory counters are touched by that warp
+// alone, so __syncwarp is the only synchronisation inside a segment.
+
+#define MOE_SEG_WARPS 8   // warps (segments) per CTA
+
+__device__ __forceinline__ void moe_zero_row(int* row, int n_expert, int lane) {
+    for (int e = lane; e < n_expert; e += 32) row[e] = 0;
+    __syncwarp();
+}
+
+__global__ void __launch_bounds__(32 * MOE_SEG_WARPS)
+k_moe_seg_count(const int* ids, int n, int n_expert, int seg_len, int n_segs, int* counts) {
+    __shared__ int hist[MOE_SEG_WARPS][MOE_MAX_EXPERTS];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int seg = blockIdx.x * MOE_SEG_WARPS + w;
+    if (seg >= n_segs) return;
+    int* h = hist[w];
+    moe_zero_row(h, n_expert, lane);
+    const int lo = seg * seg_len, hi = min(n, lo + seg_len);
+    for (int base = lo; base < hi; base += 32) {
+        const int i = base + lane;
+        const int e = i < hi ? ids[i] : -1;
+        const bool ok = e >= 0 && e < n_expert;
+        const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+        if (ok && (peers & ((1u << lane) - 1u)) == 0) h[e] += __popc(peers);   // one lane per expert present
+        __syncwarp();
+    }
+    for (int e = lane; e < n_expert; e += 32) counts[(size_t)seg * n_expert + e] = h[e];
+}
+
+// ep: n_expert rounded up to a power of two. The 1024 threads are 1024 / ep parts x ep experts: a part sums and
+// later rewrites a contiguous range of segments, so small expert counts still keep every thread busy.
+__global__ void __launch_bounds__(1024)
+k_moe_seg_scan(int n_expert, int ep, int tile, int n_segs, int* counts, int* n_tiles, int* tile_e, int* tile_start,
+               int* tile_n) {
+    __shared__ int wsum[2][32];
+    __shared__ int psum[1024];
+    __shared__ int estart[MOE_MAX_EXPERTS];
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int parts = 1024 / ep, e = tid & (ep - 1), part = tid / ep;
+    const int per = (n_segs + parts - 1) / parts, s0 = part * per, s1 = min(n_segs, s0 + per);
+    int mine = 0;
+    if (e < n_expert)
+        for (int s = s0; s < s1; ++s) mine += counts[(size_t)s * n_expert + e];
+    psum[tid] = mine;
+    __syncthreads();
+    int c = 0;   // thread tid < n_expert: the total of expert tid
+    if (tid < n_expert)
+        for (int p = 0; p < parts; ++p) c += psum[p * ep + tid];
+    const int nt = (c + tile - 1) / tile;
+    int a = c, b = nt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int ua = __shfl_up_sync(0xffffffffu, a, d), ub = __shfl_up_sync(0xffffffffu, b, d);
+        if (lane >= d) { a += ua; b += ub; }
+    }
+    if (lane == 31) { wsum[0][w] = a; wsum[1][w] = b; }
+    __syncthreads();
+    if (w == 0) {
+        int x = wsum[0][lane], y = wsum[1][lane];
+        const int x0 = x, y0 = y;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int ux = __shfl_up_sync(0xffffffffu, x, d), uy = __shfl_up_sync(0xffffffffu, y, d);
+            if (lane >= d) { x += ux; y += uy; }
+        }
+        wsum[0][lane] = x - x0;
+        wsum[1][lane] = y - y0;
+    }
+    __syncthreads();
+    const int eo = wsum[0][w] + a - c, to = wsum[1][w] + b - nt;
+    if (tid < n_expert) {
+        estart[tid] = eo;
+        for (int k = 0; k < nt; ++k) {
+            tile_e[to + k] = tid;
+            tile_start[to + k] = eo + k * tile;
+            tile_n[to + k] = min(tile, c - k * tile);
+        }
+        if (tid == n_expert - 1) *n_tiles = to + nt;
+    }
+    __syncthreads();
+    if (e < n_expert) {
+        int run = estart[e];
+        for (int p = 0; p < part; ++p) run += psum[p * ep + e];
+        for (int s = s0; s < s1; ++s) {
+            int* q = counts + (size_t)s * n_expert + e;
+            const int v = *q;
+            *q = run;
+            run += v;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(32 * MOE_SEG_WARPS)
+k_moe_seg_scatter(const int* ids, int n, int n_used, int n_expert, int seg_len, int n_segs, const int* offsets,
+                  int* tok_rows, int* pair_rows) {
+    __shared__ int next[MOE_SEG_WARPS][MOE_MAX_EXPERTS];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int seg = blockIdx.x * MOE_SEG_WARPS + w;
+    if (seg >= n_segs) return;
+    int* nx = next[w];
+    for (int e = lane; e < n_expert; e += 32) nx[e] = offsets[(size_t)seg * n_expert + e];
+    __syncwarp();
+    const int lo = seg * seg_len, hi = min(n, lo + seg_len);
+    for (int base = lo; base < hi; base += 32) {
+        const int i = base + lane;
+        const int e = i < hi ? ids[i] : -1;
+        const bool ok = e >= 0 && e < n_expert;
+        const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        int p = 0;
+        if (ok) p = nx[e] + rank;
+        __syncwarp();
+        if (ok && rank == 0) nx[e] += __popc(peers);
+        __syncwarp();
+        if (ok) {
+            tok_rows[p] = i / n_used;
+            pair_rows[p] = i;
+        }
     }
 }
 

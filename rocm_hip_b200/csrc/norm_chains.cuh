@@ -230,13 +230,13 @@ k_gemma_ffn_post(const float* x, const float* mlp, const float* down, const floa
         const uint4* d = reinterpret_cast<const uint4*>(down) + (size_t)row * n_used * row_vecs + l;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
-            for (int u0 = 0; u0 < n_used; u0 += 4) {
-                uint4 r[4];
+            for (int u0 = 0; u0 < n_used; u0 += 8) {   // eight slots' vectors in flight
+                uint4 r[8];
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
+                for (int k = 0; k < 8; ++k)
                     if (u0 + k < n_used) r[k] = ld_stream(d + (size_t)(u0 + k) * row_vecs + j * tpr);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
+                for (int k = 0; k < 8; ++k) {
                     const int u = u0 + k;
                     if (u < n_used) {
                         f2 v[2];

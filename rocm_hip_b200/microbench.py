@@ -1,0 +1,127 @@
+"""Per-launcher microbenchmark of the entry points around the hot path (the rows bench.py's sweep does not time):
+MoE grouping / combine, strided SwiGLU / GEGLU, the Gemma-4 norm chains, KV-cache row writes (FP16, Q8_0, Q4_0, with
+the Hadamard rotation), the 16-bit and int8 side outputs, the soft cap.
+
+    python -m rocm_hip_b200.microbench [--tokens 65536] [--width 4096] [--iters 10] [--only REGEX]
+
+One line per case: CUDA-event time per launch (after 3 warm-ups; every case streams more bytes than the 126 MB L2
+holds), the ALGORITHMIC bytes of the case (each input read once, each output written once, stated per case below),
+GB/s, and that as a fraction of the copy bandwidth in MEASURED_PEAKS.json (repo root) when the file is there.
+The timed calls are the library's launchers through ctypes; nothing here computes a result another way.
+"""
+import argparse
+import json
+import os
+import re
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+import rocm_hip_b200 as m  # noqa: E402
+
+
+def measured_copy_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"])
+    except (OSError, KeyError, ValueError):
+        return None
+
+
+def time_launch(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e-3   # seconds per launch
+
+
+def cases(T, n):
+    """Yields (name, callable, algorithmic bytes per launch). fp32 rows [T][n] unless the name says otherwise."""
+    R = lambda *s: torch.randn(*s, device="cuda")
+    V = T * n
+    x, a, o1, o2, o3 = R(T, n), R(T, n), R(T, n), R(T, n), R(T, n)
+    w, w1, w2, w3 = R(n), R(n), R(n), R(n)
+    sc = torch.tensor([0.7], device="cuda")
+    # norm chains: inputs + outputs, 4 bytes each per value
+    yield "add_normed", lambda: m.gpu_add_normed(x, a, w, sc, o1, n, T, 1e-6), 12 * V
+    yield "gemma_attn_post", lambda: m.gpu_gemma_attn_post(x, a, w, o1, w1, o2, None, None, n, T, 1e-6), 16 * V
+    yield "gemma_attn_post + router norm", lambda: m.gpu_gemma_attn_post(x, a, w, o1, w1, o2, w2, o3, n, T, 1e-6), 20 * V
+    # MoE: 8 experts per token; down [T/8][8][n] so that the case stays the size of the others
+    U, Tm, E = 8, max(T // 8, 1), 128
+    down = R(Tm, U, n)
+    wts = torch.rand(Tm, U, device="cuda")
+    ids = torch.randint(0, E, (Tm, U), device="cuda", dtype=torch.int32)
+    es = torch.rand(E, device="cuda") + 0.5
+    xm, mlp, om1, om2 = R(Tm, n), R(Tm, n), R(Tm, n), R(Tm, n)
+    yield "moe_combine (8 slots)", lambda: m.gpu_moe_combine(down, wts, None, None, om1, U, n, Tm), 4 * (U + 1) * Tm * n
+    yield "moe_combine_scaled + shared", lambda: m.gpu_moe_combine(down, wts, xm, torch.rand(Tm, device="cuda"), om1, U, n, Tm, ids, es), 4 * (U + 2) * Tm * n
+    yield "gemma_ffn_post (8 slots)", lambda: m.gpu_gemma_ffn_post(xm, mlp, down, wts, ids, es, U, w, w1, w2, sc, om1, w3, om2, n, Tm, 1e-6), 4 * (U + 4) * Tm * n
+    # moe_group: ids in, two row lists out (12 bytes per entry): latency-bound by design (one CTA)
+    Tg = min(T, 65536)
+    gi = torch.randint(0, E, (Tg, U), device="cuda", dtype=torch.int32)
+    tok, pair = (torch.empty(Tg * U, device="cuda", dtype=torch.int32) for _ in range(2))
+    mt = m.gpu_moe_max_tiles(Tg, U, E, 64)
+    nt = torch.zeros(1, device="cuda", dtype=torch.int32)
+    te, ts, tn = (torch.empty(mt, device="cuda", dtype=torch.int32) for _ in range(3))
+    yield "moe_group (%d x 8 entries)" % Tg, lambda: m.gpu_moe_group(gi, Tg, U, E, 64, tok, pair, nt, te, ts, tn), 12 * Tg * U
+    # gated activations on rows, 12 bytes per value
+    gu = R(T, 2 * n)
+    yield "swiglu flat", lambda: m.gpu_swiglu(x, a, o1, V), 12 * V
+    yield "swiglu rows [gate|up] fused", lambda: m.gpu_swiglu_rows(gu, gu[:, n:], o1, T, n, 2 * n, 2 * n), 12 * V
+    yield "geglu", lambda: m.gpu_geglu(x, a, o1, T, n, n, n), 12 * V
+    yield "geglu rows [gate|up] fused", lambda: m.gpu_geglu(gu, gu[:, n:], o1, T, n, 2 * n, 2 * n), 12 * V
+    yield "softcap (in place)", lambda: m.gpu_softcap(x, V, 30.0), 8 * V
+    # side outputs: the producer's own traffic + 2 bytes (xh), or + a pass of 4 read + ~2.5 written (int8 formats)
+    qx = m.Q8Buffers(V, "cuda", xh="bf16", int8=False)
+    qa = m.Q8Buffers(V, "cuda", xh="bf16")
+    yield "rmsnorm", lambda: m.gpu_add_rmsnorm(x, None, None, w, o1, n, T, 1e-6), 8 * V
+    yield "rmsnorm + bf16 copy (one launch)", lambda: m.gpu_add_rmsnorm(x, None, None, w, o1, n, T, 1e-6, q8=qx), 10 * V
+    yield "add+rmsnorm + bf16 copy (one launch)", lambda: m.gpu_add_rmsnorm(x, a, o2, w, o1, n, T, 1e-6, q8=qx), 18 * V
+    yield "swiglu + bf16 copy (one launch)", lambda: m.gpu_swiglu(x, a, o1, V, q8=qx), 14 * V
+    yield "rmsnorm + bf16 copy + Q8_0/Q8_K (two launches)", lambda: m.gpu_add_rmsnorm(x, None, None, w, o1, n, T, 1e-6, q8=qa), (10 + 4 + 2.53) * V
+    # KV rows: 1024 values per token row (8 heads x 128), 4 T rows
+    nv, Tk = 1024, 4 * T
+    src = R(Tk, nv)
+    sb = src.to(torch.bfloat16)
+    c16 = torch.zeros(Tk * nv, device="cuda", dtype=torch.float16)
+    yield "kv_store_f16", lambda: m.gpu_kv_store_f16(src, c16, nv, None, 0, Tk, nv, 30, 0), 6 * Tk * nv
+    yield "kv_store_f16 (bf16 rows)", lambda: m.gpu_kv_store_f16(sb, c16, nv, None, 0, Tk, nv, 30, 0), 4 * Tk * nv
+    for kq, name, st in ((1, "q8_0", nv * 17 // 32), (2, "q4_0", nv * 9 // 32)):
+        c = torch.zeros(Tk * st, device="cuda", dtype=torch.int16)
+        yield "kv_store_%s" % name, (lambda c=c, st=st, kq=kq: m.gpu_kv_store_q(src, c, nv, None, 0, Tk, st, 30, 0, kq)), Tk * (4 * nv + 2 * st)
+        yield "kv_store_%s rotated (128)" % name, (lambda c=c, st=st, kq=kq: m.gpu_kv_store_q(src, c, nv, None, 0, Tk, st, 30, 0, kq, rot_block=128)), Tk * (4 * nv + 2 * st)
+        yield "kv_store_%s (bf16 rows)" % name, (lambda c=c, st=st, kq=kq: m.gpu_kv_store_q(sb, c, nv, None, 0, Tk, st, 30, 0, kq)), Tk * (2 * nv + 2 * st)
+    yield "hadamard_rot (128)", lambda: m.gpu_hadamard_rot(src, src, Tk * 8, 128, 128), 8 * Tk * nv
+    yield "hadamard_rot (512)", lambda: m.gpu_hadamard_rot(src, src, Tk * 2, 512, 512), 8 * Tk * nv
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--tokens", type=int, default=65536)
+    ap.add_argument("--width", type=int, default=4096, help="row width n (a multiple of 256, at most 4096)")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--only", default=None, help="regular expression on the case name")
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    assert m.gpu_ops_init("gpu_ops.co") == 0
+    peak = measured_copy_peak()
+    print("%-50s %10s %10s %9s %s" % ("case", "us", "MB", "GB/s", "of measured copy peak" if peak else ""))
+    for name, fn, nbytes in cases(args.tokens, args.width):
+        if args.only and not re.search(args.only, name):
+            continue
+        sec = time_launch(fn, args.iters)
+        gbs = nbytes / sec / 1e9
+        print("%-50s %10.1f %10.1f %9.0f %s" % (name, sec * 1e6, nbytes / 1e6, gbs, "%.3f" % (gbs / peak) if peak else ""))
+
+
+if __name__ == "__main__":
+    main()

@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
 ]
 
@@ -206,11 +206,22 @@ def gpu_moe_max_tiles(T, n_used, n_expert, tile):
     return min(n, n_expert + n // tile)
 
 
-def gpu_moe_group(ids, T, n_used, n_expert, tile, tok_rows, pair_rows, n_tiles, tile_e, tile_start, tile_n):
-    """Group the (token, slot) entries of ids [T][n_used] (int32) by expert; all arguments int32 CUDA tensors."""
-    _check("gpu_moe_group", _lib.load().gpu_moe_group(_ptr(ids), T, n_used, n_expert, tile, _ptr(tok_rows),
-                                                      _ptr(pair_rows), _ptr(n_tiles), _ptr(tile_e), _ptr(tile_start),
-                                                      _ptr(tile_n), _stream()))
+def gpu_moe_group(ids, T, n_used, n_expert, tile, tok_rows, pair_rows, n_tiles, tile_e, tile_start, tile_n, scratch=None):
+    """Group the (token, slot) entries of ids [T][n_used] (int32) by expert; all arguments int32 CUDA tensors.
+    scratch: an int32 CUDA tensor of gpu_moe_group_scratch_ints(...) entries to use instead of the library's own."""
+    lib = _lib.load()
+    if scratch is None:
+        code = lib.gpu_moe_group(_ptr(ids), T, n_used, n_expert, tile, _ptr(tok_rows), _ptr(pair_rows), _ptr(n_tiles),
+                                 _ptr(tile_e), _ptr(tile_start), _ptr(tile_n), _stream())
+    else:
+        code = lib.gpu_moe_group_scratch(_ptr(ids), T, n_used, n_expert, tile, _ptr(tok_rows), _ptr(pair_rows),
+                                         _ptr(n_tiles), _ptr(tile_e), _ptr(tile_start), _ptr(tile_n), _ptr(scratch),
+                                         scratch.numel(), _stream())
+    _check("gpu_moe_group", code)
+
+
+def gpu_moe_group_scratch_ints(T, n_used, n_expert):
+    return int(_lib.load().gpu_moe_group_scratch_ints(T, n_used, n_expert))
 
 
 def gpu_qk_norm_rope(qfull, k, q_norm, k_norm, q_out, k_out, n_q, n_kv, head_dim, n_rot, rot_pairs, positions, pos0, T,

@@ -43,6 +43,48 @@ def test_grouping(ops, T, n_used, n_expert, tile):
         assert np.array_equal(host(pair), order) and np.array_equal(host(tok), order // n_used)
 
 
+@pytest.mark.parametrize("T,n_used,n_expert,tile", [(1025, 8, 256, 64), (20000, 8, 128, 64), (65536, 8, 256, 128),
+                                                      (4099, 3, 1000, 16), (300000, 4, 60, 256), (9000, 1, 7, 32)])
+def test_long_batches_take_the_segment_kernels(ops, T, n_used, n_expert, tile):
+    """More than 8192 entries: three launches over the whole device, the same arrays as the one-CTA kernel would write
+    (the numpy statement), deterministic, with the library's scratch slots and with the caller's."""
+    ids, _ = synth.moe_routing(T, "mg.long", T, n_expert, n_used)
+    ids = ids.copy()
+    ids.ravel()[5::997] = -1                      # entries to skip, as the one-CTA kernel skips them
+    ids.ravel()[7::1013] = n_expert
+    d_ids = dev(ids)
+    n = T * n_used
+    assert n > 8192
+    flat = ids.ravel()
+    keep = np.flatnonzero((flat >= 0) & (flat < n_expert))
+    order = keep[np.argsort(flat[keep], kind="stable")]
+    counts = np.bincount(flat[keep], minlength=n_expert)
+    starts = np.concatenate([[0], np.cumsum(counts)[:-1]])
+    wte = np.concatenate([np.full((c + tile - 1) // tile, e) for e, c in enumerate(counts)])
+    wts = np.concatenate([starts[e] + tile * np.arange((c + tile - 1) // tile) for e, c in enumerate(counts)])
+    wtn = np.concatenate([np.minimum(tile, c - tile * np.arange((c + tile - 1) // tile)) for e, c in enumerate(counts)])
+    mt = ops.gpu_moe_max_tiles(T, n_used, n_expert, tile)
+    z = lambda k: torch.full((k,), -7, dtype=torch.int32, device="cuda")
+    need = ops.gpu_moe_group_scratch_ints(T, n_used, n_expert)
+    assert 0 < need <= 1024 * n_expert
+    for scratch in (None, None, None, None, None, z(need)):     # the library's slots in turn, then the caller's
+        tok, pair, ntl, te, ts, tn = z(n), z(n), z(1), z(mt + 4), z(mt + 4), z(mt + 4)
+        before = ops.launch_count()
+        ops.gpu_moe_group(d_ids, T, n_used, n_expert, tile, tok, pair, ntl, te, ts, tn, scratch=scratch)
+        torch.cuda.synchronize()
+        assert ops.launch_count() - before == 3
+        k = int(ntl.item())
+        assert k == len(wte) <= mt
+        assert np.array_equal(host(te)[:k], wte) and np.array_equal(host(ts)[:k], wts) and np.array_equal(host(tn)[:k], wtn)
+        assert (host(te)[mt:] == -7).all()
+        m = len(order)
+        assert np.array_equal(host(pair)[:m], order) and np.array_equal(host(tok)[:m], order // n_used)
+        assert (host(pair)[m:] == -7).all()
+    with pytest.raises(ops.LayerOpError):
+        ops.gpu_moe_group(d_ids, T, n_used, n_expert, tile, tok, pair, ntl, te, ts, tn, scratch=z(need - 1))
+    assert ops.gpu_moe_group_scratch_ints(1024, 8, 256) == 0
+
+
 def test_argument_errors(ops):
     ids = torch.zeros(8, dtype=torch.int32, device="cuda")
     o = torch.zeros(64, dtype=torch.int32, device="cuda")
