@@ -223,20 +223,18 @@ k_gemma_ffn_post(const float* x, const float* mlp, const float* down, const floa
     for (long long row = blockIdx.x; row < T; row += gridDim.x) {
         const size_t off = (size_t)row * row_vecs + l;
         f2 h[VPT][2], c[VPT][2];
-#pragma unroll
-        for (int j = 0; j < VPT; ++j) Io2<float>::unpack(ld_stream(reinterpret_cast<const uint4*>(mlp) + off + j * tpr), h[j]);
         const float* wt = wts + row * n_used;
         const int* e = ids + row * n_used;
         const uint4* d = reinterpret_cast<const uint4*>(down) + (size_t)row * n_used * row_vecs + l;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
-            for (int u0 = 0; u0 < n_used; u0 += 8) {   // eight slots' vectors in flight
-                uint4 r[8];
+            for (int u0 = 0; u0 < n_used; u0 += 4) {   // four slots' vectors in flight per row vector
+                uint4 r[4];
 #pragma unroll
-                for (int k = 0; k < 8; ++k)
+                for (int k = 0; k < 4; ++k)
                     if (u0 + k < n_used) r[k] = ld_stream(d + (size_t)(u0 + k) * row_vecs + j * tpr);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
+                for (int k = 0; k < 4; ++k) {
                     const int u = u0 + k;
                     if (u < n_used) {
                         f2 v[2];
@@ -250,6 +248,9 @@ k_gemma_ffn_post(const float* x, const float* mlp, const float* down, const floa
                 }
             }
         }
+        // (the dense MLP's row is fetched after the experts' so that its registers are not held through the combine)
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) Io2<float>::unpack(ld_stream(reinterpret_cast<const uint4*>(mlp) + off + j * tpr), h[j]);
         const float im = inv_rms(cta_sum(row_sumsq<VPT>(h), part[0]), inv_n, eps);
         const float ic = inv_rms(cta_sum(row_sumsq<VPT>(c), part[1]), inv_n, eps);
         const f2 im2 = pk2(im, im), ic2 = pk2(ic, ic);
