@@ -190,7 +190,7 @@ k_kv_store_q(const IO* src, __half* cache, int n_vals, const int* positions, int
                 uint32_t w[2] = {0u, 0u};
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const int q = d != 0.0f ? (int)rintf(__fmul_rn(x[j][e], id)) : 0;
+                    const int q = d != 0.0f ? __float2int_rn(__fmul_rn(x[j][e], id)) : 0;
                     w[e >> 2] |= (uint32_t)(q & 0xff) << (8 * (e & 3));
                 }
                 *reinterpret_cast<uint2*>(row + o * 8) = make_uint2(w[0], w[1]);

@@ -93,7 +93,7 @@ __device__ __forceinline__ void store_quantised(__half* row_h, int e, float x, i
     if (kq == 1) {
         const int d_row = kv_stride * 32 / 17;
         const float d = __fdiv_rn(amax, 127.0f);
-        reinterpret_cast<int8_t*>(row)[e] = (int8_t)(int)rintf(d != 0.0f ? __fmul_rn(x, __fdiv_rn(1.0f, d)) : 0.0f);
+        reinterpret_cast<int8_t*>(row)[e] = (int8_t)__float2int_rn(d != 0.0f ? __fmul_rn(x, __fdiv_rn(1.0f, d)) : 0.0f);
         if (lane == 0) reinterpret_cast<__half*>(row + d_row)[e / 32] = __float2half_rn(d);
     } else {
         const int d_row = kv_stride * 32 / 9;

@@ -47,7 +47,7 @@ __device__ __forceinline__ void q8_block_value(float v, bool active, long long b
     float am = a;
     for (int off = 16; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
     const float id0 = am != 0.0f ? __fdiv_rn(127.0f, am) : 0.0f;
-    const int q0 = active ? (int)rintf(__fmul_rn(v, id0)) : 0;
+    const int q0 = active ? __float2int_rn(__fmul_rn(v, id0)) : 0;
     int sum0 = q0;
     for (int off = 16; off > 0; off >>= 1) sum0 += __shfl_xor_sync(0xffffffffu, sum0, off);
     if (active) {
@@ -79,7 +79,7 @@ __device__ __forceinline__ void q8_block_value(float v, bool active, long long b
     float iscale = 0.0f;
     if (fa != 0.0f) {
         iscale = __fdiv_rn(-127.0f, fv);
-        q = min(127, (int)rintf(__fmul_rn(iscale, v)));
+        q = min(127, __float2int_rn(__fmul_rn(iscale, v)));
     }
     int s16 = q;
     for (int off = 8; off > 0; off >>= 1) s16 += __shfl_xor_sync(0xffffffffu, s16, off);
@@ -140,7 +140,7 @@ k_q8_side(const float* x, long long K, Q8Side o) {
         const float id0 = am != 0.0f ? __fdiv_rn(127.0f, am) : 0.0f;
         int q[8], sum0 = 0;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { q[e] = (int)rintf(__fmul_rn(v[e], id0)); sum0 += q[e]; }
+        for (int e = 0; e < 8; ++e) { q[e] = __float2int_rn(__fmul_rn(v[e], id0)); sum0 += q[e]; }
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
         if (active) {
@@ -170,7 +170,7 @@ k_q8_side(const float* x, long long K, Q8Side o) {
         if (ba != 0.0f) {
             iscale = __fdiv_rn(-127.0f, bv);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { q[e] = min(127, (int)rintf(__fmul_rn(iscale, v[e]))); s8 += q[e]; }
+            for (int e = 0; e < 8; ++e) { q[e] = min(127, __float2int_rn(__fmul_rn(iscale, v[e]))); s8 += q[e]; }
         } else {
 #pragma unroll
             for (int e = 0; e < 8; ++e) q[e] = 0;
