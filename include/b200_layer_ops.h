@@ -91,6 +91,14 @@ cudaError_t gpu_moe_group(const int* ids, int T, int n_used, int n_expert, int t
  *   gpu_gemma_ffn_post:   c = the combine above (no shared expert); h = RMSNorm(mlp) * w1 + RMSNorm(c) * w2;
  *                         x_out = (x + RMSNorm(h) * w_post) * (*scale, or 1); y = RMSNorm(x_out) * w_next (side
  *                         outputs into q8 if set). x_out is not x.
+ *   gpu_moe_router:       per token, p = softmax(logits [T][n_expert]); ids / wts [T][n_used] = the n_used largest p in
+ *                         descending order (ties to the lower index) and p / max(their sum, 2^-14); with w_shexp,
+ *                         sg[t] = sigmoid(x[t] . w_shexp) (x [T][n]); ids_stride (0: n_used) > n_used: ids rows of
+ *                         ids_stride entries, entry n_used set to -1. n_expert <= 1024, n_used <= 64
+ *                         (src/gpu_ops.h:30-37).
+ *   gpu_moe_router_sigmoid: p = sigmoid(logits); the n_used largest p + bias; weights p, divided by max(sum, 2^-14)
+ *                         if norm, times scale (src/gpu_ops.h:119-123).
+ *   gpu_relu2:            out [rows][h] = max(x, 0)^2, row r of x at in + r * stride (side outputs into q8 if set).
  * cudaErrorInvalidValue for the reference's refusals and for NULL or not 16-byte aligned row pointers. */
 cudaError_t gpu_add_normed(const float* base, const float* a, const float* w, const float* scale, float* out, int n, int T,
                            float eps, cudaStream_t stream);
@@ -101,6 +109,11 @@ cudaError_t gpu_gemma_ffn_post(const float* x, const float* mlp, const float* do
                                const float* exp_scale, int n_used, const float* w1, const float* w2, const float* w_post,
                                const float* scale, float* x_out, const float* w_next, float* y, const qmatvec_q8* q8, int n,
                                int T, float eps, cudaStream_t stream);
+cudaError_t gpu_moe_router(const float* logits, const float* x, const float* w_shexp, int* ids, float* wts, float* sg,
+                           int n_expert, int n_used, int n, int T, cudaStream_t stream, int ids_stride);
+cudaError_t gpu_moe_router_sigmoid(const float* logits, const float* bias, int* ids, float* wts, int n_expert, int n_used,
+                                   int norm, float scale, int T, cudaStream_t stream);
+cudaError_t gpu_relu2(const float* in, float* out, int rows, int h, int stride, const qmatvec_q8* q8, cudaStream_t stream);
 cudaError_t gpu_moe_combine(const float* down, const float* wts, const float* shared, const float* sg, float* out,
                             int n_used, int n, int T, cudaStream_t stream);
 cudaError_t gpu_moe_combine_scaled(const float* down, const float* wts, const float* shared, const float* sg,

@@ -309,6 +309,61 @@ def gemma_attn_post(x, a, w_a, w1, w2, eps):
     return x_out, (vn * w1).astype(np.float32), None if w2 is None else (vn * np.asarray(w2, np.float32)).astype(np.float32)
 
 
+def _top_rounds(keys, weights, n_used):
+    """n_used rounds of 'largest remaining key, lowest index among equals' (src/gpu_ops.hip:150-182)."""
+    keys = np.array(keys, dtype=np.float32)
+    T = keys.shape[0]
+    ids = np.empty((T, n_used), dtype=np.int32)
+    w = np.empty((T, n_used), dtype=np.float32)
+    rows = np.arange(T)
+    for r in range(n_used):
+        best = np.argmax(keys, axis=1)          # the first (lowest index) among equals
+        ids[:, r] = best
+        w[:, r] = weights[rows, best]
+        keys[rows, best] = -np.inf
+    return ids, w
+
+
+def _normalised(w, norm, scale):
+    ws = np.zeros(w.shape[0], dtype=np.float32)
+    for r in range(w.shape[1]):
+        ws = (ws + w[:, r]).astype(np.float32)
+    ws = np.maximum(ws, np.float32(6.103515625e-5))
+    out = (w / ws[:, None]).astype(np.float32) if norm else w
+    return (out * np.float32(scale)).astype(np.float32) if scale != 1.0 else out
+
+
+def moe_router(logits, n_used, x=None, w_shexp=None):
+    """(ids, wts, sg) of the reference's softmax router (src/gpu_ops.hip:184-241): p = exp(l - max) * (1 / sum),
+    selection on p, weights p / max(sum of the selected, 2^-14); sg = sigmoid(x . w_shexp) or None. fp32 operations
+    one by one; the softmax sum and the dot product are carried in double."""
+    l = np.asarray(logits, dtype=np.float32)
+    ex = np.exp((l - l.max(axis=1, keepdims=True)).astype(np.float32)).astype(np.float32)
+    inv = np.float32(1.0) / ex.astype(np.float64).sum(axis=1, keepdims=True).astype(np.float32)
+    p = (ex * inv).astype(np.float32)
+    ids, w = _top_rounds(p, p, n_used)
+    sg = None
+    if w_shexp is not None:
+        d = (np.asarray(x, np.float64) * np.asarray(w_shexp, np.float64)).sum(axis=1).astype(np.float32)
+        sg = (np.float32(1.0) / (np.float32(1.0) + np.exp(-d).astype(np.float32))).astype(np.float32)
+    return ids, _normalised(w, True, 1.0), sg
+
+
+def moe_router_sigmoid(logits, bias, n_used, norm, scale):
+    """(ids, wts) of the reference's sigmoid router (src/gpu_ops.hip:794-824): keys sigmoid(l) + bias, weights
+    sigmoid(l), normalised if norm, times scale."""
+    l = np.asarray(logits, dtype=np.float32)
+    p = (np.float32(1.0) / (np.float32(1.0) + np.exp(-l).astype(np.float32))).astype(np.float32)
+    ids, w = _top_rounds((p + np.asarray(bias, np.float32)).astype(np.float32), p, n_used)
+    return ids, _normalised(w, norm, scale)
+
+
+def relu2(x):
+    """max(x, 0)^2 (src/gpu_ops.hip:826-838)."""
+    v = np.maximum(np.asarray(x, dtype=np.float32), np.float32(0.0))
+    return (v * v).astype(np.float32)
+
+
 def moe_combine(down, wts, shared=None, sg=None, ids=None, exp_scale=None):
     """out [T][n] = sum_j wts[t][j] * down[t][j] in slot order (+ shared * sg, or + shared), fp32 operations one by one
     (src/gpu_ops.hip:245-264): with exp_scale each term is (d * exp_scale[ids[t][j]]) * w; wts None: weight 1."""

@@ -16,6 +16,7 @@
 #include "embed.cuh"
 #include "kv_store.cuh"
 #include "moe_group.cuh"
+#include "moe_router.cuh"
 #include "norm_chains.cuh"
 #include "q8_side.cuh"
 #include "qk_norm_rope.cuh"
@@ -507,6 +508,25 @@ cudaError_t launch_moe_group(const int* ids, int T, int n_used, int n_expert, in
     return launched();
 }
 
+template <bool SIGMOID>
+cudaError_t launch_router(const float* logits, const float* x, const float* w_shexp, const float* bias, int* ids,
+                          float* wts, float* sg, int n_expert, int n_used, int n, long long T, int ids_stride, int norm,
+                          float scale, cudaStream_t stream) {
+    long long grid = (T + MOE_ROUTER_WARPS - 1) / MOE_ROUTER_WARPS;
+    const long long cap = resident_ctas(32 * MOE_ROUTER_WARPS) * 4;
+    if (grid > cap) grid = cap;
+#define ROUTER(PL) k_moe_router<PL, SIGMOID><<<(unsigned)grid, 32 * MOE_ROUTER_WARPS, 0, stream>>>( \
+        logits, x, w_shexp, bias, ids, wts, sg, n_expert, n_used, n, T, ids_stride, norm, scale)
+    if (n_expert <= 32) ROUTER(1);
+    else if (n_expert <= 64) ROUTER(2);
+    else if (n_expert <= 128) ROUTER(4);
+    else if (n_expert <= 256) ROUTER(8);
+    else if (n_expert <= 512) ROUTER(16);
+    else ROUTER(32);
+#undef ROUTER
+    return launched();
+}
+
 // ---------------------------------------------------------------- Gemma-4 norm chains, GEGLU, soft cap
 
 // Rows of n fp32 values, n % 256 == 0 and n <= 4096 (src/gpu_ops.cpp:189,198): exactly tpr * vpt vectors
@@ -638,6 +658,43 @@ cudaError_t gpu_gemma_ffn_post(const float* x, const float* mlp, const float* do
     const cudaError_t e = launched();
     if (e != cudaSuccess || !q8) return e;
     return launch_q8_side(y, (long long)n * T, q8, stream);
+}
+
+cudaError_t gpu_moe_router(const float* logits, const float* x, const float* w_shexp, int* ids, float* wts, float* sg,
+                           int n_expert, int n_used, int n, int T, cudaStream_t stream, int ids_stride) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (n_expert <= 0 || n_expert > MOE_MAX_EXPERTS || n_used <= 0 || n_used > MOE_MAX_USED || n_used > n_expert || T <= 0)
+        return cudaErrorInvalidValue;
+    if (ids_stride == 0) ids_stride = n_used;
+    if (ids_stride < n_used || !logits || !ids || !wts || (w_shexp && (!x || !sg || n <= 0))) return cudaErrorInvalidValue;
+    return launch_router<false>(logits, x, w_shexp, nullptr, ids, wts, sg, n_expert, n_used, n, T, ids_stride, 1, 1.0f,
+                                stream);
+}
+
+cudaError_t gpu_moe_router_sigmoid(const float* logits, const float* bias, int* ids, float* wts, int n_expert, int n_used,
+                                   int norm, float scale, int T, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || n_expert <= 0 || n_expert > MOE_MAX_EXPERTS || n_used <= 0 || n_used > MOE_MAX_USED ||
+        n_used > n_expert || !logits || !bias || !ids || !wts)
+        return cudaErrorInvalidValue;
+    return launch_router<true>(logits, nullptr, nullptr, bias, ids, wts, nullptr, n_expert, n_used, 0, T, n_used, norm,
+                               scale, stream);
+}
+
+cudaError_t gpu_relu2(const float* in, float* out, int rows, int h, int stride, const qmatvec_q8* q8, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    const long long n = (long long)rows * h;
+    if (rows <= 0 || h <= 0 || stride < h || n > INT_MAX || !in || !out || (q8 && (n % 32 != 0 || n > q8->max_k)))
+        return cudaErrorInvalidValue;
+    const bool vec = h % 4 == 0 && stride % 4 == 0 && al16(in) && al16(out);
+    const long long work = vec ? n / 4 : n, cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    if (vec) k_relu2<true><<<(unsigned)grid, 256, 0, stream>>>(in, out, rows, h, stride);
+    else k_relu2<false><<<(unsigned)grid, 256, 0, stream>>>(in, out, rows, h, stride);
+    const cudaError_t e = launched();
+    if (e != cudaSuccess || !q8) return e;
+    return launch_q8_side(out, n, q8, stream);
 }
 
 cudaError_t gpu_moe_combine_scaled(const float* down, const float* wts, const float* shared, const float* sg,

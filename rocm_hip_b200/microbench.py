@@ -73,6 +73,15 @@ def cases(T, n):
     nt = torch.zeros(1, device="cuda", dtype=torch.int32)
     te, ts, tn = (torch.empty(mt, device="cuda", dtype=torch.int32) for _ in range(3))
     yield "moe_group (%d x 8 entries)" % Tg, lambda: m.gpu_moe_group(gi, Tg, U, E, 64, tok, pair, nt, te, ts, tn), 12 * Tg * U
+    # routers: logits [T][256] in, 8 ids + 8 weights out; with the shared-expert gate the x row is read too
+    lg = R(T, 256)
+    rid = torch.empty(T, 8, device="cuda", dtype=torch.int32)
+    rw, rsg = torch.empty(T, 8, device="cuda"), torch.empty(T, device="cuda")
+    rb = torch.zeros(256, device="cuda")
+    yield "moe_router softmax (256 experts, top 8)", lambda: m.gpu_moe_router(lg, None, None, rid, rw, None, 256, 8, 0, T), T * (256 * 4 + 64)
+    yield "moe_router softmax + shared gate", lambda: m.gpu_moe_router(lg, x, w, rid, rw, rsg, 256, 8, n, T), T * (256 * 4 + 68 + 4 * n)
+    yield "moe_router sigmoid (256 experts, top 8)", lambda: m.gpu_moe_router_sigmoid(lg, rb, rid, rw, 256, 8, 1, 2.5, T), T * (256 * 4 + 64)
+    yield "relu2", lambda: m.gpu_relu2(x, o1, T, n, n), 8 * V
     # gated activations on rows, 12 bytes per value
     gu = R(T, 2 * n)
     yield "swiglu flat", lambda: m.gpu_swiglu(x, a, o1, V), 12 * V

@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
 ]
 
@@ -143,6 +143,24 @@ def gpu_gemma_ffn_post(x, mlp, down, wts, ids, exp_scale, n_used, w1, w2, w_post
     _check("gpu_gemma_ffn_post", _lib.load().gpu_gemma_ffn_post(
         _ptr(x), _ptr(mlp), _ptr(down), _ptr(wts), _ptr(ids), _ptr(exp_scale), n_used, _ptr(w1), _ptr(w2), _ptr(w_post),
         _ptr(scale), _ptr(x_out), _ptr(w_next), _ptr(y), q, n, T, eps, _stream()))
+
+
+def gpu_moe_router(logits, x, w_shexp, ids, wts, sg, n_expert, n_used, n, T, ids_stride=0):
+    """Softmax router (src/gpu_ops.h:30-37): ids / wts [T][n_used], optional shared-expert gate sg [T]."""
+    _check("gpu_moe_router", _lib.load().gpu_moe_router(_ptr(logits), _ptr(x), _ptr(w_shexp), _ptr(ids), _ptr(wts), _ptr(sg),
+                                                        n_expert, n_used, n, T, _stream(), ids_stride))
+
+
+def gpu_moe_router_sigmoid(logits, bias, ids, wts, n_expert, n_used, norm, scale, T):
+    """Sigmoid router (src/gpu_ops.h:119-123)."""
+    _check("gpu_moe_router_sigmoid", _lib.load().gpu_moe_router_sigmoid(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(wts),
+                                                                        n_expert, n_used, norm, scale, T, _stream()))
+
+
+def gpu_relu2(x, out, rows, h, stride, q8=None):
+    """out [rows][h] = max(x, 0)^2 on strided rows (src/gpu_ops.h:124)."""
+    q = C.byref(q8.struct()) if q8 is not None else None
+    _check("gpu_relu2", _lib.load().gpu_relu2(_ptr(x), _ptr(out), rows, h, stride, q, _stream()))
 
 
 def gpu_moe_combine(down, wts, shared, sg, out, n_used, n, T, ids=None, exp_scale=None):
