@@ -65,7 +65,7 @@ def cases(T, n):
     yield "moe_combine (8 slots)", lambda: m.gpu_moe_combine(down, wts, None, None, om1, U, n, Tm), 4 * (U + 1) * Tm * n
     yield "moe_combine_scaled + shared", lambda: m.gpu_moe_combine(down, wts, xm, torch.rand(Tm, device="cuda"), om1, U, n, Tm, ids, es), 4 * (U + 2) * Tm * n
     yield "gemma_ffn_post (8 slots)", lambda: m.gpu_gemma_ffn_post(xm, mlp, down, wts, ids, es, U, w, w1, w2, sc, om1, w3, om2, n, Tm, 1e-6), 4 * (U + 4) * Tm * n
-    # moe_group: ids in, two row lists out (12 bytes per entry): latency-bound by design (one CTA)
+    # moe_group: ids in, two row lists out (12 bytes per entry): 6 MB, latency-bound by nature
     Tg = min(T, 65536)
     gi = torch.randint(0, E, (Tg, U), device="cuda", dtype=torch.int32)
     tok, pair = (torch.empty(Tg * U, device="cuda", dtype=torch.int32) for _ in range(2))
