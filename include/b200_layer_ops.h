@@ -123,6 +123,33 @@ cudaError_t gpu_geglu(const float* gate, const float* up, float* out, int rows, 
                       const qmatvec_q8* q8, cudaStream_t stream);
 cudaError_t gpu_softcap(float* x, int n, float cap, cudaStream_t stream);
 
+/* The remaining row-parallel launchers of the reference's gpu_ops module, same signatures and argument rules
+ * (src/gpu_ops.h:78-105,117; src/gpu_ops.cpp:124-184,260-270; kernels src/gpu_ops.hip:322-476,763-792). The residual of
+ * a hyper-connection model is hc streams of n values per token, rows r = t * hc + c.
+ *   gpu_hc_norm:     with cur [T][n]: res_out[r] = res_in[r] + cur[t] * 2 * sigmoid(inject[r] / hc) first (res_out may be
+ *                    res_in); y[r] = RMSNorm(that) * w[c * n ..] (side outputs into q8 over the flattened
+ *                    [T * hc * n]). n % 256 == 0, n <= 4096.
+ *   gpu_hc_lowrank:  out [T][np] = SiLU(lo [T][n] / hc), zero-padded to rows of np >= n.
+ *   gpu_hc_mix:      out[t] = mean over the streams c of xn[r] * sigmoid(gate[r]).
+ *   gpu_ple_gate:    key, res, gated, normed [T][hc][n]; value [T][n]; gammas [hc * n]: per stream
+ *                    s = (RMSNorm(key) * wk) . (RMSNorm(res) * wq) / sqrt(n), g = sigmoid(sgn(s) * sqrt(max(|s|, 1e-6))),
+ *                    gated = value * g, normed = RMSNorm(gated) * wc.
+ *   gpu_mtp_concat:  out [T][hc][2 n] = [e[t] | h[t][c]].
+ *   gpu_mamba_gnorm: out [T][d_inner] = RMSNorm(y * SiLU(z)) * w per group of d_inner / n_group values (a multiple of
+ *                    256, at most 1024), z at the start of zx's rows (stride ld). */
+cudaError_t gpu_hc_norm(const float* res_in, float* res_out, const float* cur, const float* inject, const float* w, float* y,
+                        int n, int hc, int T, float eps, const qmatvec_q8* q8, cudaStream_t stream);
+cudaError_t gpu_hc_lowrank(const float* lo, float* out, int n, int np, int T, int hc, const qmatvec_q8* q8,
+                           cudaStream_t stream);
+cudaError_t gpu_hc_mix(const float* xn, const float* gate, float* out, int n, int hc, int T, const qmatvec_q8* q8,
+                       cudaStream_t stream);
+cudaError_t gpu_ple_gate(const float* key, const float* value, const float* res, const float* wk, const float* wq,
+                         const float* wc, float* gated, float* normed, int n, int hc, int T, float eps,
+                         cudaStream_t stream);
+cudaError_t gpu_mtp_concat(const float* e, const float* h, float* out, int n, int hc, int T, cudaStream_t stream);
+cudaError_t gpu_mamba_gnorm(const float* y, const float* zx, long long ld, const float* w, float* out, int d_inner,
+                            int n_group, int T, float eps, const qmatvec_q8* q8, cudaStream_t stream);
+
 /* ------------------------------------------------------------------------------------------------ Part 2 */
 
 /* bf16 storage (uint16_t bit patterns), fp32 arithmetic, one round-to-nearest-even per stored value (the rule of

@@ -364,6 +364,74 @@ def relu2(x):
     return (v * v).astype(np.float32)
 
 
+def _sigmoid32(x):
+    x = np.asarray(x, dtype=np.float32)
+    return (np.float32(1.0) / (np.float32(1.0) + np.exp(-x).astype(np.float32))).astype(np.float32)
+
+
+def _silu32(x):
+    x = np.asarray(x, dtype=np.float32)
+    return (x / (np.float32(1.0) + np.exp(-x).astype(np.float32))).astype(np.float32)
+
+
+def hc_norm(res_in, cur, inject, w, hc, eps):
+    """(res_out or None, y) of hc_norm (src/gpu_ops.hip:340-378): res [T][hc][n], cur [T][n] or None, inject [T][hc],
+    w [hc][n]; fp32 operations one by one."""
+    v = np.asarray(res_in, dtype=np.float32)
+    T, _, n = v.shape
+    out = None
+    if cur is not None:
+        wt = (np.float32(2.0) * _sigmoid32(np.asarray(inject, np.float32) * (np.float32(1.0) / np.float32(hc)))).astype(np.float32)
+        v = (v + (np.asarray(cur, np.float32)[:, None, :] * wt[:, :, None]).astype(np.float32)).astype(np.float32)
+        out = v
+    inv = _row_inv_rms(v.reshape(T * hc, n), eps).reshape(T, hc, 1)
+    return out, ((v * inv).astype(np.float32) * np.asarray(w, np.float32).reshape(1, hc, n)).astype(np.float32)
+
+
+def hc_lowrank(lo, np_, hc):
+    """SiLU(lo / hc) zero-padded to rows of np_ (src/gpu_ops.hip:380-394)."""
+    lo = np.asarray(lo, dtype=np.float32)
+    out = np.zeros((lo.shape[0], np_), dtype=np.float32)
+    out[:, :lo.shape[1]] = _silu32((lo * (np.float32(1.0) / np.float32(hc))).astype(np.float32))
+    return out
+
+
+def hc_mix(xn, gate, hc):
+    """Mean over the streams of xn * sigmoid(gate), streams added in order (src/gpu_ops.hip:396-409); [T][hc][n]."""
+    xn, gate = np.asarray(xn, np.float32), np.asarray(gate, np.float32)
+    acc = None
+    for c in range(hc):
+        p = (xn[:, c] * _sigmoid32(gate[:, c])).astype(np.float32)
+        acc = p if acc is None else (acc + p).astype(np.float32)
+    return (acc * (np.float32(1.0) / np.float32(hc))).astype(np.float32)
+
+
+def ple_gate(key, value, res, wk, wq, wc, eps):
+    """(gated, normed) of ple_gate (src/gpu_ops.hip:419-476): key / res [T][hc][n], value [T][n], gammas [hc][n]."""
+    key, res, value = (np.asarray(a, np.float32) for a in (key, res, value))
+    T, hc, n = key.shape
+    wk, wq, wc = (np.asarray(a, np.float32).reshape(1, hc, n) for a in (wk, wq, wc))
+    ik = _row_inv_rms(key.reshape(T * hc, n), eps).reshape(T, hc, 1)
+    iq = _row_inv_rms(res.reshape(T * hc, n), eps).reshape(T, hc, 1)
+    a = ((key * ik).astype(np.float32) * wk).astype(np.float32)
+    b = ((res * iq).astype(np.float32) * wq).astype(np.float32)
+    d = (a * b).astype(np.float32).astype(np.float64).sum(axis=2).astype(np.float32)
+    s = (d * (np.float32(1.0) / np.sqrt(np.float32(n)))).astype(np.float32)
+    mag = np.sqrt(np.maximum(np.abs(s), np.float32(1e-6))).astype(np.float32)
+    g = _sigmoid32((np.sign(s).astype(np.float32) * mag).astype(np.float32))
+    gated = (value[:, None, :] * g[:, :, None]).astype(np.float32)
+    ig = _row_inv_rms(gated.reshape(T * hc, n), eps).reshape(T, hc, 1)
+    return gated, ((gated * ig).astype(np.float32) * wc).astype(np.float32)
+
+
+def mamba_gnorm(y, z, w, n_group, eps):
+    """RMSNorm(y * SiLU(z)) * w per group of d_inner / n_group values (src/gpu_ops.hip:762-792)."""
+    y, z, w = (np.asarray(a, np.float32) for a in (y, z, w))
+    T, d = y.shape
+    v = (y * _silu32(z)).astype(np.float32).reshape(T * n_group, d // n_group)
+    return ((v * _row_inv_rms(v, eps)).astype(np.float32).reshape(T, d) * w).astype(np.float32)
+
+
 def moe_combine(down, wts, shared=None, sg=None, ids=None, exp_scale=None):
     """out [T][n] = sum_j wts[t][j] * down[t][j] in slot order (+ shared * sg, or + shared), fp32 operations one by one
     (src/gpu_ops.hip:245-264): with exp_scale each term is (d * exp_scale[ids[t][j]]) * w; wts None: weight 1."""

@@ -22,6 +22,7 @@
 #include "qk_norm_rope.cuh"
 #include "rmsnorm.cuh"
 #include "rope_f16.cuh"
+#include "stream_ops.cuh"
 #include "swiglu.cuh"
 
 using namespace b200;
@@ -658,6 +659,104 @@ cudaError_t gpu_gemma_ffn_post(const float* x, const float* mlp, const float* do
     const cudaError_t e = launched();
     if (e != cudaSuccess || !q8) return e;
     return launch_q8_side(y, (long long)n * T, q8, stream);
+}
+
+cudaError_t gpu_hc_norm(const float* res_in, float* res_out, const float* cur, const float* inject, const float* w, float* y,
+                        int n, int hc, int T, float eps, const qmatvec_q8* q8, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    int tpr, vpt;
+    if (T <= 0 || hc <= 0 || !plan_chain(n, &tpr, &vpt) || (q8 && (long long)n * hc * T > q8->max_k) || !res_in || !w ||
+        !y || (cur && (!res_out || !inject)) || !al16(res_in) || !al16(w) || !al16(y) ||
+        (cur && (!al16(cur) || !al16(res_out))))
+        return cudaErrorInvalidValue;
+    const long long rows = (long long)T * hc;
+    if (vpt == 4) {
+        long long grid = persistent_grid(k_hc_norm<4>, tpr, 0);
+        k_hc_norm<4><<<(unsigned)(grid < rows ? grid : rows), tpr, 0, stream>>>(res_in, res_out, cur, inject, w, y, n, hc, rows, eps);
+    } else {
+        long long grid = persistent_grid(k_hc_norm<2>, tpr, 0);
+        k_hc_norm<2><<<(unsigned)(grid < rows ? grid : rows), tpr, 0, stream>>>(res_in, res_out, cur, inject, w, y, n, hc, rows, eps);
+    }
+    const cudaError_t e = launched();
+    if (e != cudaSuccess || !q8) return e;
+    return launch_q8_side(y, rows * n, q8, stream);
+}
+
+cudaError_t gpu_hc_lowrank(const float* lo, float* out, int n, int np, int T, int hc, const qmatvec_q8* q8,
+                           cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || n <= 0 || hc <= 0 || np < n || !lo || !out || (q8 && (np % 32 != 0 || (long long)np * T > q8->max_k)))
+        return cudaErrorInvalidValue;
+    const long long total = (long long)np * T, cap = resident_ctas(256) * 8;
+    long long grid = (total + 255) / 256;
+    if (grid > cap) grid = cap;
+    k_hc_lowrank<<<(unsigned)grid, 256, 0, stream>>>(lo, out, n, np, T, 1.0f / (float)hc);
+    const cudaError_t e = launched();
+    if (e != cudaSuccess || !q8) return e;
+    return launch_q8_side(out, total, q8, stream);
+}
+
+cudaError_t gpu_hc_mix(const float* xn, const float* gate, float* out, int n, int hc, int T, const qmatvec_q8* q8,
+                       cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || n <= 0 || hc <= 0 || !xn || !gate || !out || (q8 && (n % 256 != 0 || (long long)n * T > q8->max_k)))
+        return cudaErrorInvalidValue;
+    const bool vec = n % 4 == 0 && al16(xn) && al16(gate) && al16(out);
+    const long long work = (long long)T * (vec ? n / 4 : n), cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    if (vec) k_hc_mix<true><<<(unsigned)grid, 256, 0, stream>>>(xn, gate, out, n, hc, T);
+    else k_hc_mix<false><<<(unsigned)grid, 256, 0, stream>>>(xn, gate, out, n, hc, T);
+    const cudaError_t e = launched();
+    if (e != cudaSuccess || !q8) return e;
+    return launch_q8_side(out, (long long)n * T, q8, stream);
+}
+
+cudaError_t gpu_ple_gate(const float* key, const float* value, const float* res, const float* wk, const float* wq,
+                         const float* wc, float* gated, float* normed, int n, int hc, int T, float eps,
+                         cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    int tpr, vpt;
+    if (T <= 0 || hc <= 0 || !plan_chain(n, &tpr, &vpt) || !key || !value || !res || !wk || !wq || !wc || !gated ||
+        !normed || !al16(key) || !al16(value) || !al16(res) || !al16(wk) || !al16(wq) || !al16(wc) || !al16(gated) ||
+        !al16(normed))
+        return cudaErrorInvalidValue;
+    if (vpt == 4) {
+        long long grid = persistent_grid(k_ple_gate<4>, tpr, 0);
+        k_ple_gate<4><<<(unsigned)(grid < T ? grid : T), tpr, 0, stream>>>(key, value, res, wk, wq, wc, gated, normed, n, hc, T, eps);
+    } else {
+        long long grid = persistent_grid(k_ple_gate<2>, tpr, 0);
+        k_ple_gate<2><<<(unsigned)(grid < T ? grid : T), tpr, 0, stream>>>(key, value, res, wk, wq, wc, gated, normed, n, hc, T, eps);
+    }
+    return launched();
+}
+
+cudaError_t gpu_mtp_concat(const float* e, const float* h, float* out, int n, int hc, int T, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || hc <= 0 || n <= 0 || !e || !h || !out) return cudaErrorInvalidValue;
+    const bool vec = n % 4 == 0 && al16(e) && al16(h) && al16(out);
+    const long long rows = (long long)T * hc, work = rows * (vec ? n / 2 : 2 * n), cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    if (vec) k_mtp_concat<true><<<(unsigned)grid, 256, 0, stream>>>(e, h, out, n, hc, rows);
+    else k_mtp_concat<false><<<(unsigned)grid, 256, 0, stream>>>(e, h, out, n, hc, rows);
+    return launched();
+}
+
+cudaError_t gpu_mamba_gnorm(const float* y, const float* zx, long long ld, const float* w, float* out, int d_inner,
+                            int n_group, int T, float eps, const qmatvec_q8* q8, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || n_group <= 0 || d_inner <= 0 || d_inner % n_group != 0) return cudaErrorInvalidValue;
+    const int gs = d_inner / n_group;
+    if (gs % 256 != 0 || gs > 1024 || (q8 && (long long)d_inner * T > q8->max_k) || !y || !zx || !w || !out || ld < d_inner ||
+        ld % 4 != 0 || !al16(y) || !al16(zx) || !al16(w) || !al16(out))
+        return cudaErrorInvalidValue;
+    const long long rows = (long long)T * n_group;
+    long long grid = persistent_grid(k_mamba_gnorm, gs / 8, 0);
+    k_mamba_gnorm<<<(unsigned)(grid < rows ? grid : rows), gs / 8, 0, stream>>>(y, zx, ld, w, out, d_inner, n_group, T, eps);
+    const cudaError_t e = launched();
+    if (e != cudaSuccess || !q8) return e;
+    return launch_q8_side(out, (long long)d_inner * T, q8, stream);
 }
 
 cudaError_t gpu_moe_router(const float* logits, const float* x, const float* w_shexp, int* ids, float* wts, float* sg,

@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_hc_norm", "gpu_hc_lowrank", "gpu_hc_mix", "gpu_ple_gate", "gpu_mtp_concat", "gpu_mamba_gnorm", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
 ]
 
@@ -143,6 +143,43 @@ def gpu_gemma_ffn_post(x, mlp, down, wts, ids, exp_scale, n_used, w1, w2, w_post
     _check("gpu_gemma_ffn_post", _lib.load().gpu_gemma_ffn_post(
         _ptr(x), _ptr(mlp), _ptr(down), _ptr(wts), _ptr(ids), _ptr(exp_scale), n_used, _ptr(w1), _ptr(w2), _ptr(w_post),
         _ptr(scale), _ptr(x_out), _ptr(w_next), _ptr(y), q, n, T, eps, _stream()))
+
+
+def _q8arg(q8):
+    return C.byref(q8.struct()) if q8 is not None else None
+
+
+def gpu_hc_norm(res_in, res_out, cur, inject, w, y, n, hc, T, eps, q8=None):
+    """Hyper-connection combine + per-stream RMSNorm (src/gpu_ops.h:80-85)."""
+    _check("gpu_hc_norm", _lib.load().gpu_hc_norm(_ptr(res_in), _ptr(res_out), _ptr(cur), _ptr(inject), _ptr(w), _ptr(y), n,
+                                                  hc, T, eps, _q8arg(q8), _stream()))
+
+
+def gpu_hc_lowrank(lo, out, n, np_, T, hc, q8=None):
+    """out [T][np_] = SiLU(lo / hc), zero-padded (src/gpu_ops.h:86-89)."""
+    _check("gpu_hc_lowrank", _lib.load().gpu_hc_lowrank(_ptr(lo), _ptr(out), n, np_, T, hc, _q8arg(q8), _stream()))
+
+
+def gpu_hc_mix(xn, gate, out, n, hc, T, q8=None):
+    """out[t] = mean over streams of xn * sigmoid(gate) (src/gpu_ops.h:90-92)."""
+    _check("gpu_hc_mix", _lib.load().gpu_hc_mix(_ptr(xn), _ptr(gate), _ptr(out), n, hc, T, _q8arg(q8), _stream()))
+
+
+def gpu_ple_gate(key, value, res, wk, wq, wc, gated, normed, n, hc, T, eps):
+    """PLE gate (src/gpu_ops.h:93-96)."""
+    _check("gpu_ple_gate", _lib.load().gpu_ple_gate(_ptr(key), _ptr(value), _ptr(res), _ptr(wk), _ptr(wq), _ptr(wc),
+                                                    _ptr(gated), _ptr(normed), n, hc, T, eps, _stream()))
+
+
+def gpu_mtp_concat(e, h, out, n, hc, T):
+    """out [T][hc][2 n] = [e[t] | h[t][c]] (src/gpu_ops.h:103-105)."""
+    _check("gpu_mtp_concat", _lib.load().gpu_mtp_concat(_ptr(e), _ptr(h), _ptr(out), n, hc, T, _stream()))
+
+
+def gpu_mamba_gnorm(y, zx, ld, w, out, d_inner, n_group, T, eps, q8=None):
+    """out = RMSNorm(y * SiLU(z)) * w per group (src/gpu_ops.h:117)."""
+    _check("gpu_mamba_gnorm", _lib.load().gpu_mamba_gnorm(_ptr(y), _ptr(zx), ld, _ptr(w), _ptr(out), d_inner, n_group, T, eps,
+                                                          _q8arg(q8), _stream()))
 
 
 def gpu_moe_router(logits, x, w_shexp, ids, wts, sg, n_expert, n_used, n, T, ids_stride=0):

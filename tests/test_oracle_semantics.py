@@ -237,3 +237,49 @@ def test_hadamard_rotation_statement(oracle):
         i, j = np.meshgrid(np.arange(N), np.arange(N), indexing="ij")
         sign = 1 - 2 * (np.array([bin(v).count("1") for v in (i & j).ravel()]).reshape(N, N) & 1)
         assert np.array_equal(np.sign(H), sign)
+
+
+def test_stream_op_statements_against_plain_double_precision(oracle):
+    """hc_norm, hc_lowrank, hc_mix, ple_gate, mamba_gnorm, the routers and relu2 of the oracle (src/gpu_ops.hip:118-241,
+    322-476, 762-838) against the same formulas in double precision."""
+    import numpy as np
+    rng = np.random.default_rng(17)
+    T, hc, n = 3, 4, 512
+    D = lambda t: np.asarray(t, dtype=np.float64)
+    sig = lambda v: 1 / (1 + np.exp(-D(v)))
+    rms = lambda v: D(v) / np.sqrt((D(v) ** 2).mean(axis=-1, keepdims=True) + 1e-6)
+    res, cur = rng.standard_normal((T, hc, n)).astype(np.float32), rng.standard_normal((T, n)).astype(np.float32)
+    inj, w = rng.standard_normal((T, hc)).astype(np.float32), (1 + 0.1 * rng.standard_normal((hc, n))).astype(np.float32)
+    ro, y = oracle.hc_norm(res, cur, inj, w, hc, 1e-6)
+    ref_ro = D(res) + D(cur)[:, None, :] * (2 * sig(D(inj) / hc))[:, :, None]
+    assert np.abs(ro - ref_ro).max() < 2e-6 and np.abs(y - rms(ref_ro) * D(w)).max() < 4e-6
+    assert oracle.hc_norm(res, None, None, w, hc, 1e-6)[0] is None
+    lo = (rng.standard_normal((T, 40)) * 3).astype(np.float32)
+    lr = oracle.hc_lowrank(lo, 64, hc)
+    assert np.abs(lr[:, :40] - D(lo) / hc * sig(D(lo) / hc)).max() < 1e-6 and not lr[:, 40:].any()
+    gate = rng.standard_normal((T, hc, n)).astype(np.float32)
+    assert np.abs(oracle.hc_mix(res, gate, hc) - (D(res) * sig(gate)).mean(axis=1)).max() < 1e-6
+    key, val = rng.standard_normal((T, hc, n)).astype(np.float32), rng.standard_normal((T, n)).astype(np.float32)
+    wk, wq, wc = ((1 + 0.1 * rng.standard_normal((hc, n))).astype(np.float32) for _ in range(3))
+    gated, normed = oracle.ple_gate(key, val, res, wk, wq, wc, 1e-6)
+    s = ((rms(key) * D(wk)) * (rms(res) * D(wq))).sum(axis=2) / np.sqrt(n)
+    g = sig(np.sign(s) * np.sqrt(np.maximum(np.abs(s), 1e-6)))
+    assert np.abs(gated - D(val)[:, None, :] * g[:, :, None]).max() < 2e-6
+    assert np.abs(normed - rms(D(val)[:, None, :] * g[:, :, None]) * D(wc)).max() < 1e-5
+    yv, z = rng.standard_normal((T, 1024)).astype(np.float32), rng.standard_normal((T, 1024)).astype(np.float32)
+    wg = (1 + 0.1 * rng.standard_normal(1024)).astype(np.float32)
+    v = (D(yv) * D(z) * sig(z)).reshape(T, 4, 256)
+    assert np.abs(oracle.mamba_gnorm(yv, z, wg, 4, 1e-6) - (rms(v).reshape(T, 1024) * D(wg))).max() < 1e-5
+    logits = rng.standard_normal((T, 60)).astype(np.float32)
+    ids, wts, sgate = oracle.moe_router(logits, 4, val, wg[:n])
+    p = np.exp(D(logits) - D(logits).max(axis=1, keepdims=True))
+    p /= p.sum(axis=1, keepdims=True)
+    top = np.argsort(-p, axis=1, kind="stable")[:, :4]
+    assert np.array_equal(ids, top)
+    assert np.abs(wts - np.take_along_axis(p, top, 1) / np.take_along_axis(p, top, 1).sum(axis=1, keepdims=True)).max() < 1e-6
+    assert np.abs(sgate - sig((D(val) * D(wg[:n])).sum(axis=1))).max() < 1e-6
+    bias = rng.standard_normal(60).astype(np.float32)
+    ids2, w2 = oracle.moe_router_sigmoid(logits, bias, 4, 0, 2.0)
+    top2 = np.argsort(-(sig(logits) + D(bias)), axis=1, kind="stable")[:, :4]
+    assert np.array_equal(ids2, top2) and np.abs(w2 - 2 * np.take_along_axis(sig(logits), top2, 1)).max() < 1e-6
+    assert np.array_equal(oracle.relu2(np.float32([-1, 0, 2, 0.5])), np.float32([0, 0, 4, 0.25]))
