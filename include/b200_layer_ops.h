@@ -137,6 +137,25 @@ cudaError_t gpu_softcap(float* x, int n, float cap, cudaStream_t stream);
  *   gpu_mtp_concat:  out [T][hc][2 n] = [e[t] | h[t][c]].
  *   gpu_mamba_gnorm: out [T][d_inner] = RMSNorm(y * SiLU(z)) * w per group of d_inner / n_group values (a multiple of
  *                    256, at most 1024), z at the start of zx's rows (stride ld). */
+/* The kernels of the same module that look back over earlier tokens (src/gpu_ops.h:96-116; src/gpu_ops.cpp:168-176,
+ * 236-258; kernels src/gpu_ops.hip:476-512,679-760), same signatures:
+ *   gpu_mamba_conv: out [T][conv_dim] = SiLU(causal conv1d of zx's xBC columns (at x_off, row stride ld) + bias),
+ *                   2 <= d_conv <= 8 taps, w [conv_dim][d_conv]; conv_state [conv_dim][d_conv - 1] holds the inputs
+ *                   before the batch and is advanced.
+ *   gpu_mamba_scan: the selective scan, state [n_head][64][128] (d_inner = 64 n_head), B / C of group h / (n_head /
+ *                   n_group) from xbc [T][d_inner + 256 n_group], dt from zx at dt_off: y [T][d_inner].
+ *   gpu_ple_conv:   res += gated + SiLU(dilated causal depthwise conv of normed), m channels, K fp16 taps w [m][K];
+ *                   state [(K - 1) dil][m] is advanced; state_mid (or NULL): p[j] receives the state after token j. */
+#ifndef DELTANET_H   /* (src/deltanet.h:19-21; include the reference's header first when both are used) */
+typedef struct deltanet_mid_states { float* p[3]; } deltanet_mid_states;
+#endif
+cudaError_t gpu_mamba_conv(const float* zx, long long ld, int x_off, float* conv_state, const float* w, const float* bias,
+                           float* out, int conv_dim, int d_conv, int T, cudaStream_t stream);
+cudaError_t gpu_mamba_scan(float* state, const float* xbc, const float* zx, long long ld, int dt_off, const float* dt_b,
+                           const float* A, const float* D, float* y, int n_head, int d_inner, int n_group, int T,
+                           cudaStream_t stream);
+cudaError_t gpu_ple_conv(const float* normed, const float* gated, float* res, float* state, const void* w, int m, int T,
+                         int K, int dil, const deltanet_mid_states* state_mid, cudaStream_t stream);
 cudaError_t gpu_hc_norm(const float* res_in, float* res_out, const float* cur, const float* inject, const float* w, float* y,
                         int n, int hc, int T, float eps, const qmatvec_q8* q8, cudaStream_t stream);
 cudaError_t gpu_hc_lowrank(const float* lo, float* out, int n, int np, int T, int hc, const qmatvec_q8* q8,

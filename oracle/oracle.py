@@ -432,6 +432,64 @@ def mamba_gnorm(y, z, w, n_group, eps):
     return ((v * _row_inv_rms(v, eps)).astype(np.float32).reshape(T, d) * w).astype(np.float32)
 
 
+def mamba_conv(zx, x_off, conv_state, w, bias, conv_dim, d_conv):
+    """(out [T][conv_dim], new conv_state [conv_dim][d_conv - 1]) of mamba_conv / mamba_conv_state
+    (src/gpu_ops.hip:702-728): window oldest first, products added one by one from 0, + bias, SiLU."""
+    zx, w, bias = np.asarray(zx, np.float32), np.asarray(w, np.float32), np.asarray(bias, np.float32)
+    st = np.asarray(conv_state, np.float32)
+    T, ns = zx.shape[0], d_conv - 1
+    x = np.concatenate([st.T, zx[:, x_off:x_off + conv_dim]], axis=0)          # rows: ns before the batch, then the batch
+    s = np.zeros((T, conv_dim), np.float32)
+    for k in range(d_conv):
+        s = (s + (x[k:k + T] * w[:, k][None, :]).astype(np.float32)).astype(np.float32)
+    return _silu32((s + bias[None, :]).astype(np.float32)), np.ascontiguousarray(x[T:T + ns].T)
+
+
+def ple_conv(normed, gated, res, state, w_f16_bits, K, dil, n_mid=0):
+    """(res, new state, mid states) of ple_conv (src/gpu_ops.hip:480-512): normed / gated / res [T][m], state
+    [(K - 1) dil][m], w fp16 bit patterns [m][K]."""
+    normed, gated, res, state = (np.asarray(a, np.float32) for a in (normed, gated, res, state))
+    w = f16_to_f32(np.asarray(w_f16_bits, np.uint16)).reshape(-1, K)
+    T, m = normed.shape
+    H = (K - 1) * dil
+    x = np.concatenate([state.reshape(H, m), normed], axis=0)
+    acc = None
+    for k in range(K):
+        j0 = H - (K - 1 - k) * dil                                         # row of x that token 0 reads for tap k
+        term = (x[j0:j0 + T] * w[:, k][None, :]).astype(np.float32)
+        acc = term if acc is None else (acc + term).astype(np.float32)
+    out = (res + (gated + _silu32(acc)).astype(np.float32)).astype(np.float32)
+    mids = [np.ascontiguousarray(x[j + 1:j + 1 + H]) for j in range(min(n_mid, 3, max(T - 1, 0)))]
+    return out, np.ascontiguousarray(x[T:T + H]), mids
+
+
+def mamba_scan(state, xbc, zx, dt_off, dt_b, A, D, n_head, n_group):
+    """(y [T][d_inner], new state) of mamba_scan (src/gpu_ops.hip:730-760): state [n_head][64][128]; per token
+    dt = softplus(dt_t + dt_b) (ggml's: x itself above 20), dA = exp(dt A), s = s dA + B (x dt), y = sum_j s_j C_j + x D,
+    the sum as 4 fused-multiply-add chains of 32 added pairwise ((0 + 1) + (2 + 3))."""
+    s = np.array(state, dtype=np.float32).reshape(n_head, 64, 128)
+    xbc, zx = np.asarray(xbc, np.float32), np.asarray(zx, np.float32)
+    dt_b, A, D = (np.asarray(a, np.float32) for a in (dt_b, A, D))
+    T, d_inner = xbc.shape[0], n_head * 64
+    grp = np.arange(n_head) // (n_head // n_group)
+    y = np.empty((T, d_inner), np.float32)
+    for t in range(T):
+        dv = (zx[t, dt_off:dt_off + n_head] + dt_b).astype(np.float32)
+        sp = np.where(dv > 20, dv, np.log1p(np.exp(np.minimum(dv, 30).astype(np.float32)).astype(np.float32))).astype(np.float32)
+        dA = np.exp((sp * A).astype(np.float32)).astype(np.float32)
+        x = xbc[t, :d_inner].reshape(n_head, 64)
+        xdt = (x * sp[:, None]).astype(np.float32)
+        B = xbc[t, d_inner:d_inner + n_group * 128].reshape(n_group, 128)[grp]
+        Cm = xbc[t, d_inner + n_group * 128:].reshape(n_group, 128)[grp]
+        s = ((s * dA[:, None, None]).astype(np.float32) + (B[:, None, :] * xdt[:, :, None]).astype(np.float32)).astype(np.float32)
+        q = np.zeros((n_head, 64, 4), np.float32)
+        for j in range(32):                                               # fmaf chains: exact product, one rounding
+            q = (s.reshape(n_head, 64, 4, 32)[..., j].astype(np.float64) * Cm.reshape(n_head, 1, 4, 32)[..., j] + q).astype(np.float32)
+        acc = ((q[..., 0] + q[..., 1]).astype(np.float32) + (q[..., 2] + q[..., 3]).astype(np.float32)).astype(np.float32)
+        y[t] = (acc + (x * D[:, None]).astype(np.float32)).astype(np.float32).reshape(d_inner)
+    return y, s
+
+
 def moe_combine(down, wts, shared=None, sg=None, ids=None, exp_scale=None):
     """out [T][n] = sum_j wts[t][j] * down[t][j] in slot order (+ shared * sg, or + shared), fp32 operations one by one
     (src/gpu_ops.hip:245-264): with exp_scale each term is (d * exp_scale[ids[t][j]]) * w; wts None: weight 1."""

@@ -49,6 +49,9 @@ SIGNATURES = {
     "gpu_add_normed": (_i, [_p, _p, _p, _p, _p, _i, _i, _f, _p]),
     "gpu_gemma_attn_post": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p]),
     "gpu_gemma_ffn_post": (_i, [_p] * 6 + [_i] + [_p] * 8 + [_i, _i, _f, _p]),
+    "gpu_mamba_conv": (_i, [_p, _ll, _i, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "gpu_mamba_scan": (_i, [_p, _p, _p, _ll, _i, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "gpu_ple_conv": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p]),
     "gpu_hc_norm": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _f, _p, _p]),
     "gpu_hc_lowrank": (_i, [_p, _p, _i, _i, _i, _i, _p, _p]),
     "gpu_hc_mix": (_i, [_p, _p, _p, _i, _i, _i, _p, _p]),

@@ -24,6 +24,7 @@
 #include "rope_f16.cuh"
 #include "stream_ops.cuh"
 #include "swiglu.cuh"
+#include "window_ops.cuh"
 
 using namespace b200;
 
@@ -757,6 +758,55 @@ cudaError_t gpu_mamba_gnorm(const float* y, const float* zx, long long ld, const
     const cudaError_t e = launched();
     if (e != cudaSuccess || !q8) return e;
     return launch_q8_side(out, (long long)d_inner * T, q8, stream);
+}
+
+cudaError_t gpu_mamba_conv(const float* zx, long long ld, int x_off, float* conv_state, const float* w, const float* bias,
+                           float* out, int conv_dim, int d_conv, int T, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || d_conv < 2 || d_conv > MAMBA_MAXC || conv_dim <= 0 || !zx || !conv_state || !w || !bias || !out ||
+        x_off < 0 || ld < (long long)x_off + conv_dim)
+        return cudaErrorInvalidValue;
+    const bool vec = conv_dim % 4 == 0 && ld % 4 == 0 && x_off % 4 == 0 && al16(zx) && al16(out);
+    const long long work = (long long)T * (vec ? conv_dim / 4 : conv_dim), cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    if (vec) k_mamba_conv<4><<<(unsigned)grid, 256, 0, stream>>>(zx, ld, x_off, conv_state, w, bias, out, conv_dim, d_conv, T);
+    else k_mamba_conv<1><<<(unsigned)grid, 256, 0, stream>>>(zx, ld, x_off, conv_state, w, bias, out, conv_dim, d_conv, T);
+    const cudaError_t e = launched();
+    if (e != cudaSuccess) return e;
+    k_mamba_conv_state<<<(unsigned)((conv_dim + 255) / 256), 256, 0, stream>>>(zx, ld, x_off, conv_state, conv_dim, d_conv, T);
+    return launched();
+}
+
+cudaError_t gpu_mamba_scan(float* state, const float* xbc, const float* zx, long long ld, int dt_off, const float* dt_b,
+                           const float* A, const float* D, float* y, int n_head, int d_inner, int n_group, int T,
+                           cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || n_head <= 0 || d_inner != n_head * MAMBA_P || n_group <= 0 || n_head % n_group != 0 || !state || !xbc ||
+        !zx || !dt_b || !A || !D || !y || dt_off < 0 || !al16(state) || !al16(xbc))
+        return cudaErrorInvalidValue;
+    k_mamba_scan<<<(unsigned)n_head * 4, 64, 0, stream>>>(state, xbc, zx, ld, dt_off, dt_b, A, D, y, n_head, d_inner, n_group, T);
+    return launched();
+}
+
+cudaError_t gpu_ple_conv(const float* normed, const float* gated, float* res, float* state, const void* w, int m, int T,
+                         int K, int dil, const deltanet_mid_states* state_mid, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || K < 1 || dil < 1 || m <= 0 || !normed || !gated || !res || !w || (K > 1 && !state))
+        return cudaErrorInvalidValue;
+    MidStates mid = {{nullptr, nullptr, nullptr}};
+    if (state_mid) memcpy(&mid, state_mid, sizeof(mid));
+    const bool vec = m % 4 == 0 && al16(normed) && al16(gated) && al16(res) && (K == 1 || al16(state));
+    const long long work = (long long)T * (vec ? m / 4 : m), cap = resident_ctas(256) * 8;
+    long long grid = (work + 255) / 256;
+    if (grid > cap) grid = cap;
+    const __half* wh = static_cast<const __half*>(w);
+    if (vec) k_ple_conv<4><<<(unsigned)grid, 256, 0, stream>>>(normed, gated, res, state, wh, m, T, K, dil);
+    else k_ple_conv<1><<<(unsigned)grid, 256, 0, stream>>>(normed, gated, res, state, wh, m, T, K, dil);
+    const cudaError_t e = launched();
+    if (e != cudaSuccess || K == 1) return e;
+    k_ple_conv_state<<<(unsigned)((m + 255) / 256), 256, 0, stream>>>(normed, state, m, T, K, dil, mid);
+    return launched();
 }
 
 cudaError_t gpu_moe_router(const float* logits, const float* x, const float* w_shexp, int* ids, float* wts, float* sg,

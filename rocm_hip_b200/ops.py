@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_hc_norm", "gpu_hc_lowrank", "gpu_hc_mix", "gpu_ple_gate", "gpu_mtp_concat", "gpu_mamba_gnorm", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_mamba_conv", "gpu_mamba_scan", "gpu_ple_conv", "gpu_hc_norm", "gpu_hc_lowrank", "gpu_hc_mix", "gpu_ple_gate", "gpu_mtp_concat", "gpu_mamba_gnorm", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
 ]
 
@@ -147,6 +147,29 @@ def gpu_gemma_ffn_post(x, mlp, down, wts, ids, exp_scale, n_used, w1, w2, w_post
 
 def _q8arg(q8):
     return C.byref(q8.struct()) if q8 is not None else None
+
+
+def gpu_mamba_conv(zx, ld, x_off, conv_state, w, bias, out, conv_dim, d_conv, T):
+    """Mamba-2 causal conv1d + bias + SiLU, conv state advanced (src/gpu_ops.h:112)."""
+    _check("gpu_mamba_conv", _lib.load().gpu_mamba_conv(_ptr(zx), ld, x_off, _ptr(conv_state), _ptr(w), _ptr(bias), _ptr(out),
+                                                        conv_dim, d_conv, T, _stream()))
+
+
+def gpu_mamba_scan(state, xbc, zx, ld, dt_off, dt_b, A, D, y, n_head, d_inner, n_group, T):
+    """Mamba-2 selective scan (src/gpu_ops.h:114)."""
+    _check("gpu_mamba_scan", _lib.load().gpu_mamba_scan(_ptr(state), _ptr(xbc), _ptr(zx), ld, dt_off, _ptr(dt_b), _ptr(A),
+                                                        _ptr(D), _ptr(y), n_head, d_inner, n_group, T, _stream()))
+
+
+def gpu_ple_conv(normed, gated, res, state, w, m, T, K, dil, state_mid=None):
+    """PLE dilated causal depthwise conv (src/gpu_ops.h:97-101). w: float16 CUDA tensor [m][K]; state_mid: up to three
+    CUDA tensors (or None entries) that receive the states after the first tokens."""
+    mid = None
+    if state_mid is not None:
+        arr = (C.c_void_p * 3)(*[(t.data_ptr() if t is not None else None) for t in (list(state_mid) + [None] * 3)[:3]])
+        mid = C.cast(arr, C.c_void_p)
+    _check("gpu_ple_conv", _lib.load().gpu_ple_conv(_ptr(normed), _ptr(gated), _ptr(res), _ptr(state), _ptr(w), m, T, K, dil,
+                                                    mid, _stream()))
 
 
 def gpu_hc_norm(res_in, res_out, cur, inject, w, y, n, hc, T, eps, q8=None):

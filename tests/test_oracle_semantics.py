@@ -283,3 +283,50 @@ def test_stream_op_statements_against_plain_double_precision(oracle):
     top2 = np.argsort(-(sig(logits) + D(bias)), axis=1, kind="stable")[:, :4]
     assert np.array_equal(ids2, top2) and np.abs(w2 - 2 * np.take_along_axis(sig(logits), top2, 1)).max() < 1e-6
     assert np.array_equal(oracle.relu2(np.float32([-1, 0, 2, 0.5])), np.float32([0, 0, 4, 0.25]))
+
+
+def test_window_op_statements_against_plain_double_precision(oracle):
+    """mamba_conv, ple_conv and mamba_scan of the oracle (src/gpu_ops.hip:476-512, 679-760) against direct
+    double-precision loops over the tokens."""
+    import numpy as np
+    rng = np.random.default_rng(19)
+    f = lambda *s: rng.standard_normal(s).astype(np.float32)
+    T, cd, dc = 5, 8, 4
+    zx, st, w, b = f(T, cd + 3), f(cd, dc - 1), f(cd, dc), f(cd)
+    out, new = oracle.mamba_conv(zx, 2, st, w, b, cd, dc)
+    x = np.concatenate([st.T, zx[:, 2:2 + cd]], 0).astype(np.float64)
+    for t in range(T):
+        s = (x[t:t + dc] * w.T).sum(0) + b
+        assert np.abs(out[t] - s / (1 + np.exp(-s))).max() < 2e-6
+    assert np.array_equal(new, x[T:].T.astype(np.float32))
+    m, K, dil = 6, 3, 2
+    H = (K - 1) * dil
+    n_, g, r, s0 = f(T, m), f(T, m), f(T, m), f(H, m)
+    wb = oracle.f32_to_f16(f(m, K)).reshape(m, K)
+    wf = oracle.f16_to_f32(wb).reshape(m, K).astype(np.float64)
+    res, new, mids = oracle.ple_conv(n_, g, r, s0, wb, K, dil, 3)
+    x = np.concatenate([s0, n_], 0).astype(np.float64)
+    for t in range(T):
+        acc = sum(x[H + t - (K - 1 - k) * dil] * wf[:, k] for k in range(K))
+        assert np.abs(res[t] - (r[t] + g[t] + acc / (1 + np.exp(-acc)))).max() < 2e-6
+    assert np.array_equal(new, x[T:T + H].astype(np.float32)) and len(mids) == 3
+    assert all(np.array_equal(mids[j], x[j + 1:j + 1 + H].astype(np.float32)) for j in range(3))
+    nh, ng, T = 4, 2, 6
+    di = nh * 64
+    cd = di + 2 * ng * 128
+    xbc, zz, S = f(T, cd), f(T, di + cd + nh), (f(nh, 64, 128) * 0.1)
+    dtb, A, D = f(nh), -np.abs(f(nh)), f(nh)
+    y, s1 = oracle.mamba_scan(S, xbc, zz, di + cd, dtb, A, D, nh, ng)
+    s = S.astype(np.float64)
+    grp = np.arange(nh) // (nh // ng)
+    for t in range(T):
+        dv = zz[t, di + cd:di + cd + nh].astype(np.float64) + dtb
+        sp = np.log1p(np.exp(dv))
+        dA = np.exp(sp * A)
+        xx = xbc[t, :di].reshape(nh, 64).astype(np.float64)
+        B = xbc[t, di:di + ng * 128].reshape(ng, 128)[grp]
+        Cm = xbc[t, di + ng * 128:].reshape(ng, 128)[grp]
+        s = s * dA[:, None, None] + B[:, None, :] * (xx * sp[:, None])[:, :, None]
+        yr = ((s * Cm[:, None, :]).sum(2) + xx * D[:, None]).reshape(di)
+        assert np.abs(y[t] - yr).max() < 1e-4 * max(1.0, np.abs(yr).max())
+    assert np.abs(s1 - s).max() < 1e-5
