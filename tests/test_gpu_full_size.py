@@ -125,3 +125,113 @@ def test_embed_full(ops):
         scale = rows[:, :, 0:2].contiguous().view(torch.float16).float()    # [c][nb][1]
         vals = rows[:, :, 2:].contiguous().view(torch.int8).float() * scale
         assert torch.equal(out[r:r + CH].view(torch.int16), vals.view(-1, E).to(bf).view(torch.int16))
+
+
+def test_moe_bookkeeping_full(ops):
+    """The MoE configuration's bookkeeping at 262,144 tokens x 8 slots of 256 experts (2,097,152 entries): the router's
+    selection against torch.topk, the grouping as a sorted permutation with exact tile bookkeeping, and the combine
+    against a torch einsum, all rows."""
+    n_expert, n_used, n = 256, 8, 512
+    g = torch.Generator(device="cuda").manual_seed(11)
+    logits = torch.randn(T, n_expert, device="cuda", generator=g) * 2
+    ids = torch.empty(T, n_used, dtype=torch.int32, device="cuda")
+    wts = torch.empty(T, n_used, device="cuda")
+    ops.gpu_moe_router(logits, None, None, ids, wts, None, n_expert, n_used, 0, T)
+    p = torch.softmax(logits.double(), dim=1)
+    top = torch.topk(p, n_used, dim=1)
+    same = (ids.long() == top.indices)
+    # (two probabilities that differ in double can round to one float, where the kernel's rule is the lower index)
+    assert same.all(dim=1).float().mean() > 0.9999
+    rows = same.all(dim=1)
+    ref_w = (top.values / top.values.sum(dim=1, keepdim=True)).float()
+    assert (wts[rows] - ref_w[rows]).abs().max() <= 2e-6
+    assert torch.allclose(wts.sum(dim=1), torch.ones(T, device="cuda"), atol=1e-5)
+
+    m = T * n_used
+    tile = 128
+    tok, pair = (torch.full((m,), -1, dtype=torch.int32, device="cuda") for _ in range(2))
+    mt = ops.gpu_moe_max_tiles(T, n_used, n_expert, tile)
+    ntl, te, ts, tn = (torch.zeros(k, dtype=torch.int32, device="cuda") for k in (1, mt, mt, mt))
+    ops.gpu_moe_group(ids, T, n_used, n_expert, tile, tok, pair, ntl, te, ts, tn)
+    flat = ids.reshape(-1).long()
+    order = pair.long()
+    assert torch.equal(torch.sort(order).values, torch.arange(m, device="cuda"))           # a permutation
+    ex = flat[order]
+    assert (ex[1:] >= ex[:-1]).all()                                                       # grouped by expert
+    same_e = ex[1:] == ex[:-1]
+    assert (order[1:][same_e] > order[:-1][same_e]).all()                                  # ascending inside a run
+    assert torch.equal(tok.long(), order // n_used)
+    counts = torch.bincount(flat, minlength=n_expert)
+    k = int(ntl.item())
+    assert k == int(((counts + tile - 1) // tile).sum()) <= mt
+    assert torch.equal(torch.bincount(te[:k].long(), weights=tn[:k].double(), minlength=n_expert).long(), counts)
+    starts = torch.cumsum(counts, 0) - counts
+    first = torch.ones(k, dtype=torch.bool, device="cuda")
+    first[1:] = te[1:k] != te[:k - 1]
+    assert torch.equal(ts[:k][first].long(), starts[te[:k][first].long()])
+    assert (tn[:k] >= 1).all() and (tn[:k] <= tile).all()
+
+    down = torch.empty(T, n_used, n, device="cuda")
+    for r in range(0, T, CH):
+        down[r:r + CH] = torch.randn(CH, n_used, n, device="cuda", generator=g)
+    out = torch.empty(T, n, device="cuda")
+    ops.gpu_moe_combine(down, wts, None, None, out, n_used, n, T)
+    for r in range(0, T, CH):
+        ref = torch.einsum("tu,tun->tn", wts[r:r + CH].double(), down[r:r + CH].double())
+        assert (out[r:r + CH].double() - ref).abs().max() <= 2e-6
+
+
+def test_kv_rows_full(ops):
+    """K rows of the whole batch into a block-major cache (blocks of 256 positions, 2 layers): FP16 rows exact against
+    torch's conversion, Q8_0 rows dequantised within half a step, every other byte of the cache untouched."""
+    n_vals, shift, layers = NKV * D, 8, 2
+    B = 1 << shift
+    src = rand((T, n_vals), 21).float()
+    for kq in (0, 1):
+        stride = n_vals if kq == 0 else n_vals * 17 // 32
+        bstride = 2 * layers * B * stride
+        cache = torch.full(((T // B) * bstride,), 0x7B7B, dtype=torch.int16, device="cuda")
+        if kq == 0:
+            ops.gpu_kv_store_f16(src, cache.view(torch.float16), n_vals, None, 0, T, stride, shift, bstride)
+        else:
+            ops.gpu_kv_store_q(src, cache, n_vals, None, 0, T, stride, shift, bstride, 1)
+        blocks = cache.view(T // B, 2 * layers, B, stride)
+        assert (blocks[:, 1:] == 0x7B7B).all()                       # V of this layer and the other layer: untouched
+        rows = blocks[:, 0].reshape(T, stride)
+        if kq == 0:
+            assert torch.equal(rows.view(torch.float16), src.half())
+        else:
+            b8 = rows.contiguous().view(torch.int8)
+            q = b8[:, :n_vals].float().view(T, n_vals // 32, 32)
+            d = b8[:, n_vals:n_vals + n_vals // 16].contiguous().view(torch.float16).float()
+            amax = src.view(T, n_vals // 32, 32).abs().amax(dim=2)
+            assert torch.equal(d, (amax / 127).half().float())
+            err = (q * (amax / 127).unsqueeze(2) - src.view(T, n_vals // 32, 32)).abs()
+            assert (err <= (amax / 127).unsqueeze(2) * 0.5001 + 1e-12).all()
+            assert (b8[:, n_vals + n_vals // 16:] == 0x7B).all()    # (no padding in these rows: empty slice)
+
+
+def test_norm_chain_full(ops):
+    """gemma_attn_post over the whole batch (n = 4096) against the separate launchers it fuses, bit for bit, and
+    against a double-precision torch evaluation."""
+    n = 4096
+    g = torch.Generator(device="cuda").manual_seed(31)
+    x, a = (torch.empty(T, n, device="cuda") for _ in range(2))
+    for r in range(0, T, CH):
+        x[r:r + CH] = torch.randn(CH, n, device="cuda", generator=g)
+        a[r:r + CH] = torch.randn(CH, n, device="cuda", generator=g) * 2
+    w_a, w1 = (1 + 0.1 * torch.randn(n, device="cuda", generator=g) for _ in range(2))
+    x_out, y1 = torch.empty_like(x), torch.empty_like(x)
+    ops.gpu_gemma_attn_post(x, a, w_a, x_out, w1, y1, None, None, n, T, 1e-6)
+    sx = torch.empty_like(x)
+    ops.gpu_add_normed(x, a, w_a, None, sx, n, T, 1e-6)
+    assert torch.equal(sx, x_out)
+    del sx
+    worst = 0.0
+    for r in range(0, T, CH):
+        ad = a[r:r + CH].double()
+        ref_x = x[r:r + CH].double() + ad * torch.rsqrt((ad * ad).mean(dim=1, keepdim=True) + 1e-6) * w_a.double()
+        ref_y = ref_x * torch.rsqrt((ref_x * ref_x).mean(dim=1, keepdim=True) + 1e-6) * w1.double()
+        worst = max(worst, float(((x_out[r:r + CH].double() - ref_x).abs().amax(dim=1) / ref_x.abs().amax(dim=1)).max()),
+                    float(((y1[r:r + CH].double() - ref_y).abs().amax(dim=1) / ref_y.abs().amax(dim=1)).max()))
+    assert worst <= 1e-6
