@@ -252,8 +252,11 @@ cudaError_t gpu_kv_store_q_rot_bf16(const uint16_t* src, void* cache, int n_vals
                                     int rot_block, cudaStream_t stream);
 
 /* Token-embedding gather + dequantisation: out row t = decode(table row tokens[t]) * scale, the loop of
- * src/qwen_model.cpp:980-986 (scale: embd_scale of :1409; pass 1 for none). type: 8 (Q8_0) or 2 (Q4_0), the ggml
- * ids of src/quant_types.h:19-27; row_bytes as qt_row_size(type, E) or larger (a row stride); E % 32 == 0.
+ * src/qwen_model.cpp:980-986 (scale: embd_scale of :1409; pass 1 for none). type: a ggml id of src/quant_types.h:19-41:
+ * 8 (Q8_0) and 2 (Q4_0), the formats the path is measured on, and the other formats a token_embd.weight comes in:
+ * 0 (F32), 1 (F16), 30 (BF16), 3 (Q4_1), 6 (Q5_0), 7 (Q5_1), 12 (Q4_K), 13 (Q5_K), 14 (Q6_K), each decoded as the
+ * reference's qt_to_float decodes it (src/quant_types.cpp:58-345); row_bytes as qt_row_size(type, E) or larger (a row
+ * stride); E % 32 == 0 (E % 256 == 0 for the K formats).
  * tokens are device memory. bad_row: device int the caller sets to INT_MAX beforehand; an id outside [0, vocab)
  * zero-fills its output row and lowers *bad_row to that row's index (the reference returns an error for such an id
  * before decoding anything; read the flag after the stream is synchronised). Bit-exact. */

@@ -17,6 +17,10 @@ PORT_PATH = os.path.join(HERE, "liboracle.so")
 REF_PATH = os.path.join(HERE, "_ref", "libref_cpu.so")
 
 Q4_0, Q8_0 = 2, 8
+F32, F16, Q4_1, Q5_0, Q5_1, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 3, 6, 7, 12, 13, 14, 30
+# (values per block, bytes per block) of every row format the embedding gather decodes (src/quant_types.cpp:583-598)
+BLOCK = {F32: (1, 4), F16: (1, 2), BF16: (1, 2), Q4_0: (32, 18), Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24),
+         Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
 
 _p, _i, _ll, _f, _sz = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_size_t
 

@@ -4,6 +4,7 @@
 #include "oracle_ops.h"
 
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 /* ---------------------------------------------------------------- scalars */
@@ -216,39 +217,145 @@ static float rd_f16(const uint8_t* p) {
     return orc_fp16_to_fp32(h);
 }
 
-/* src/quant_types.cpp:635-639 for the two types on this path: 32 values per block, 18 / 34 bytes */
-size_t orc_row_size(int type, int64_t ne0) {
-    if (ne0 % 32 != 0) return 0;
-    if (type == ORC_Q8_0) return (size_t)(ne0 / 32) * 34;
-    if (type == ORC_Q4_0) return (size_t)(ne0 / 32) * 18;
-    return 0;
+/* Values and bytes per block of the GGUF types the embedding gather decodes (src/quant_types.cpp:583-598) */
+static int orc_block(int type, int* values, int* bytes) {
+    switch (type) {
+        case ORC_F32: *values = 1; *bytes = 4; return 1;
+        case ORC_F16: *values = 1; *bytes = 2; return 1;
+        case ORC_BF16: *values = 1; *bytes = 2; return 1;
+        case ORC_Q4_0: *values = 32; *bytes = 18; return 1;
+        case ORC_Q4_1: *values = 32; *bytes = 20; return 1;
+        case ORC_Q5_0: *values = 32; *bytes = 22; return 1;
+        case ORC_Q5_1: *values = 32; *bytes = 24; return 1;
+        case ORC_Q8_0: *values = 32; *bytes = 34; return 1;
+        case ORC_Q4_K: *values = 256; *bytes = 144; return 1;
+        case ORC_Q5_K: *values = 256; *bytes = 176; return 1;
+        case ORC_Q6_K: *values = 256; *bytes = 210; return 1;
+        default: return 0;
+    }
 }
 
-/* src/quant_types.cpp:181-189 (Q8_0: y = qs[j] * d) and :78-91 (Q4_0: low nibbles are values 0..15, high
- * nibbles 16..31, each (nibble - 8) * d); one fp32 multiply per value */
-int orc_to_float(int type, const void* src, float* y, int64_t n) {
-    const uint8_t* b = (const uint8_t*)src;
-    if (n % 32 != 0) return -1;
-    if (type == ORC_Q8_0) {
-        for (int64_t i = 0; i < n / 32; ++i, b += 34, y += 32) {
+/* src/quant_types.cpp:635-639: bytes of a row of ne0 values, 0 when the type is unknown or ne0 is not whole blocks */
+size_t orc_row_size(int type, int64_t ne0) {
+    int v, b;
+    if (!orc_block(type, &v, &b) || ne0 % v != 0) return 0;
+    return (size_t)(ne0 / v) * (size_t)b;
+}
+
+/* The 6-bit scale and minimum j of a K-quant super-block's 12 packed bytes (src/quant_types.cpp:192-200) */
+static void k4_scale_min(int j, const uint8_t* q, int* sc, int* mn) {
+    if (j < 4) {
+        *sc = q[j] & 63;
+        *mn = q[j + 4] & 63;
+    } else {
+        *sc = (q[j + 4] & 0x0F) | ((q[j - 4] >> 6) << 4);
+        *mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+    }
+}
+
+/* One block of `type` into y, value by value, every product, sum and difference rounded on its own (the decoders of
+ * src/quant_types.cpp: plain :58-74, Q4_0 :78-91, Q4_1 :126-140, Q5_0 :142-159, Q5_1 :161-179, Q8_0 :181-189,
+ * Q4_K :264-287, Q5_K :289-316, Q6_K :318-345) */
+static void orc_block_to_float(int type, const uint8_t* b, float* y) {
+    switch (type) {
+        case ORC_F32: memcpy(y, b, 4); return;
+        case ORC_F16: y[0] = rd_f16(b); return;
+        case ORC_BF16: { uint16_t h; memcpy(&h, b, 2); y[0] = orc_bf16_to_fp32(h); return; }
+        case ORC_Q8_0: {
             const float d = rd_f16(b);
             const int8_t* qs = (const int8_t*)(b + 2);
             for (int j = 0; j < 32; ++j) y[j] = qs[j] * d;
+            return;
         }
-        return 0;
-    }
-    if (type == ORC_Q4_0) {
-        for (int64_t i = 0; i < n / 32; ++i, b += 18, y += 32) {
+        case ORC_Q4_0: {
             const float d = rd_f16(b);
             const uint8_t* qs = b + 2;
             for (int j = 0; j < 16; ++j) {
                 y[j] = ((qs[j] & 0x0F) - 8) * d;
                 y[j + 16] = ((qs[j] >> 4) - 8) * d;
             }
+            return;
         }
-        return 0;
+        case ORC_Q4_1: {
+            const float d = rd_f16(b), m = rd_f16(b + 2);
+            const uint8_t* qs = b + 4;
+            for (int j = 0; j < 16; ++j) {
+                const float lo = (float)(qs[j] & 0x0F) * d, hi = (float)(qs[j] >> 4) * d;
+                y[j] = lo + m;
+                y[j + 16] = hi + m;
+            }
+            return;
+        }
+        case ORC_Q5_0:
+        case ORC_Q5_1: {
+            const int one = type == ORC_Q5_1;
+            const float d = rd_f16(b), m = one ? rd_f16(b + 2) : 0.0f;
+            uint32_t qh;
+            memcpy(&qh, b + (one ? 4 : 2), 4);
+            const uint8_t* qs = b + (one ? 8 : 6);
+            for (int j = 0; j < 16; ++j) {
+                const int h0 = ((qh >> j) << 4) & 0x10, h1 = (qh >> (j + 12)) & 0x10;
+                const int x0 = (qs[j] & 0x0F) | h0, x1 = (qs[j] >> 4) | h1;
+                if (one) {
+                    const float lo = (float)x0 * d, hi = (float)x1 * d;
+                    y[j] = lo + m;
+                    y[j + 16] = hi + m;
+                } else {
+                    y[j] = (float)(x0 - 16) * d;
+                    y[j + 16] = (float)(x1 - 16) * d;
+                }
+            }
+            return;
+        }
+        case ORC_Q4_K:
+        case ORC_Q5_K: {
+            const int five = type == ORC_Q5_K;
+            const float d = rd_f16(b), dmin = rd_f16(b + 2);
+            const uint8_t* scales = b + 4;
+            const uint8_t* qh = b + 16;                 /* Q5_K only */
+            const uint8_t* ql = b + (five ? 48 : 16);
+            for (int g = 0; g < 4; ++g) {               /* 64 values: 32 low nibbles, then 32 high nibbles */
+                for (int half = 0; half < 2; ++half) {
+                    int sc, mn;
+                    k4_scale_min(2 * g + half, scales, &sc, &mn);
+                    const float dd = d * (float)sc, mm = dmin * (float)mn;
+                    for (int l = 0; l < 32; ++l) {
+                        int v = half ? ql[g * 32 + l] >> 4 : ql[g * 32 + l] & 0x0F;
+                        if (five && (qh[l] & ((half ? 2 : 1) << (2 * g)))) v += 16;
+                        const float p = dd * (float)v;
+                        y[g * 64 + half * 32 + l] = p - mm;
+                    }
+                }
+            }
+            return;
+        }
+        case ORC_Q6_K: {
+            const float d = rd_f16(b + 208);
+            const uint8_t* ql = b;
+            const uint8_t* qh = b + 128;
+            const int8_t* sc = (const int8_t*)(b + 192);
+            for (int h = 0; h < 2; ++h)
+                for (int quarter = 0; quarter < 4; ++quarter)
+                    for (int l = 0; l < 32; ++l) {
+                        const uint8_t lb = ql[h * 64 + l + ((quarter & 1) ? 32 : 0)];
+                        const int low = quarter < 2 ? lb & 0x0F : lb >> 4;
+                        const int q = (int)(int8_t)(low | (((qh[h * 32 + l] >> (2 * quarter)) & 3) << 4)) - 32;
+                        const float ds = d * (float)sc[h * 8 + l / 16 + 2 * quarter];
+                        y[h * 128 + quarter * 32 + l] = ds * (float)q;
+                    }
+            return;
+        }
+        default: return;
     }
-    return -1;
+}
+
+/* qt_to_float of src/quant_types.cpp:641-646 for the types above: n values (whole blocks) from src into y */
+int orc_to_float(int type, const void* src, float* y, int64_t n) {
+    int v, bb;
+    if (!orc_block(type, &v, &bb) || n % v != 0) return -1;
+    const uint8_t* b = (const uint8_t*)src;
+    for (int64_t i = 0; i < n / v; ++i, b += bb, y += v) orc_block_to_float(type, b, y);
+    return 0;
 }
 
 /* src/qwen_model.cpp:980-986: range check, decode row tokens[t] into out row t; :1409 multiplies by embd_scale
@@ -267,22 +374,19 @@ int orc_embed_rows(int type, const void* table, size_t row_bytes, int vocab, con
 
 int orc_embed_rows_bf16(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens,
                         uint16_t* out, int E, int T, float scale) {
-    float row[32];
-    if (E % 32 != 0) return -1;
-    const size_t bb = type == ORC_Q8_0 ? 34 : type == ORC_Q4_0 ? 18 : 0;
-    if (!bb) return -1;
+    if (orc_row_size(type, E) == 0) return -1;
+    float* row = (float*)malloc((size_t)E * sizeof(float));
+    if (!row) return -1;
     for (int t = 0; t < T; ++t) {
-        if (tokens[t] < 0 || tokens[t] >= vocab) return -1;
-        const char* src = (const char*)table + (size_t)tokens[t] * row_bytes;
-        for (int b = 0; b < E / 32; ++b) {
-            orc_to_float(type, src + b * bb, row, 32);
-            for (int j = 0; j < 32; ++j) {
-                float v = row[j];
-                if (scale != 1.0f) v *= scale;
-                out[(size_t)t * E + b * 32 + j] = orc_fp32_to_bf16(v);
-            }
+        if (tokens[t] < 0 || tokens[t] >= vocab) { free(row); return -1; }
+        orc_to_float(type, (const char*)table + (size_t)tokens[t] * row_bytes, row, E);
+        for (int j = 0; j < E; ++j) {
+            float v = row[j];
+            if (scale != 1.0f) v *= scale;
+            out[(size_t)t * E + j] = orc_fp32_to_bf16(v);
         }
     }
+    free(row);
     return 0;
 }
 

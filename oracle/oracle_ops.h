@@ -21,9 +21,18 @@
 extern "C" {
 #endif
 
-/* ggml type ids used on this path (src/quant_types.h:19-27) */
+/* ggml type ids (src/quant_types.h:19-41) of the row formats the embedding gather decodes */
+#define ORC_F32 0
+#define ORC_F16 1
 #define ORC_Q4_0 2
+#define ORC_Q4_1 3
+#define ORC_Q5_0 6
+#define ORC_Q5_1 7
 #define ORC_Q8_0 8
+#define ORC_Q4_K 12
+#define ORC_Q5_K 13
+#define ORC_Q6_K 14
+#define ORC_BF16 30
 
 /* ---- scalar conversions */
 float    orc_fp16_to_fp32(uint16_t h);   /* src/quant_types.cpp:16-40 */

@@ -111,6 +111,165 @@ k_embed_rows(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* t
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The other row formats a GGUF token_embd.weight comes in (src/quant_types.cpp:58-74 plain, :126-179 Q4_1 / Q5_0 /
+// Q5_1, :264-345 Q4_K / Q5_K / Q6_K), decoded value for value as the reference's qt_to_float does, each product, sum
+// and difference rounded on its own. Same shape as k_embed_rows: a warp per token, the row staged in the warp's
+// shared-memory slice in chunks of whole blocks, a lane decoding runs of VPL consecutive values (a run never leaves
+// a 16-value group, so one set of block constants serves it) and storing one 16-byte vector per run.
+
+#define B200_QT_F32 0
+#define B200_QT_F16 1
+#define B200_QT_Q4_1 3
+#define B200_QT_Q5_0 6
+#define B200_QT_Q5_1 7
+#define B200_QT_Q4_K 12
+#define B200_QT_Q5_K 13
+#define B200_QT_Q6_K 14
+#define B200_QT_BF16 30
+
+template <int TYPE>
+struct RowFormat {   // BLK values in BB bytes; plain types are taken 32 values at a time
+    static constexpr int BLK = (TYPE == B200_QT_Q4_K || TYPE == B200_QT_Q5_K || TYPE == B200_QT_Q6_K) ? 256 : 32;
+    static constexpr int BB = TYPE == B200_QT_F32 ? 128 : (TYPE == B200_QT_F16 || TYPE == B200_QT_BF16) ? 64
+                            : TYPE == B200_QT_Q4_1 ? 20 : TYPE == B200_QT_Q5_0 ? 22 : TYPE == B200_QT_Q5_1 ? 24
+                            : TYPE == B200_QT_Q4_K ? 144 : TYPE == B200_QT_Q5_K ? 176 : TYPE == B200_QT_Q6_K ? 210
+                            : TYPE == B200_QT_Q8_0 ? 34 : 18;
+    // blocks per staged chunk: as many as fit the warp's slice, a count whose bytes are a multiple of 16
+    static constexpr int GRAIN = BB % 16 == 0 ? 1 : BB % 8 == 0 ? 2 : BB % 4 == 0 ? 4 : 8;
+    static constexpr int CHUNK = (EMBED_CHUNK_BLOCKS * 34 / BB) / GRAIN * GRAIN;
+};
+
+__device__ __forceinline__ float sm_f16(const uint8_t* p) { return f16_bits_to_f32((uint16_t)(p[0] | (p[1] << 8))); }
+
+// The 6-bit scale and minimum j of a K-quant super-block's 12 packed bytes (src/quant_types.cpp:192-200)
+__device__ __forceinline__ void k4_scale_min(int j, const uint8_t* q, int& sc, int& mn) {
+    if (j < 4) {
+        sc = q[j] & 63;
+        mn = q[j + 4] & 63;
+    } else {
+        sc = (q[j + 4] & 0x0F) | ((q[j - 4] >> 6) << 4);
+        mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+    }
+}
+
+// Values j0 .. j0 + N - 1 of the block at blk (N = 4 or 8, j0 a multiple of N)
+template <int TYPE, int N>
+__device__ __forceinline__ void decode_run(const uint8_t* blk, int j0, float* y) {
+    if constexpr (TYPE == B200_QT_F32) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) y[k] = __uint_as_float(*reinterpret_cast<const uint32_t*>(blk + 4 * (j0 + k)));
+    } else if constexpr (TYPE == B200_QT_F16) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) y[k] = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(blk + 2 * (j0 + k)));
+    } else if constexpr (TYPE == B200_QT_BF16) {
+#pragma unroll
+        for (int k = 0; k < N; ++k)
+            y[k] = __uint_as_float((uint32_t)*reinterpret_cast<const uint16_t*>(blk + 2 * (j0 + k)) << 16);
+    } else if constexpr (TYPE == B200_QT_Q4_1) {
+        const float d = sm_f16(blk), m = sm_f16(blk + 2);
+        const uint8_t* qs = blk + 4 + (j0 & 15);
+        const int shift = j0 < 16 ? 0 : 4;
+#pragma unroll
+        for (int k = 0; k < N; ++k) y[k] = __fadd_rn(__fmul_rn((float)((qs[k] >> shift) & 15), d), m);
+    } else if constexpr (TYPE == B200_QT_Q5_0 || TYPE == B200_QT_Q5_1) {
+        constexpr bool ONE = TYPE == B200_QT_Q5_1;
+        const float d = sm_f16(blk), m = ONE ? sm_f16(blk + 2) : 0.0f;
+        const uint8_t* hb = blk + (ONE ? 4 : 2);
+        const uint32_t qh = hb[0] | (hb[1] << 8) | (hb[2] << 16) | ((uint32_t)hb[3] << 24);
+        const uint8_t* qs = blk + (ONE ? 8 : 6) + (j0 & 15);
+        const int shift = j0 < 16 ? 0 : 4;
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            const int x = ((qs[k] >> shift) & 15) | (int)(((qh >> (j0 + k)) & 1u) << 4);   // bit j of qh is value j's fifth bit
+            y[k] = ONE ? __fadd_rn(__fmul_rn((float)x, d), m) : __fmul_rn((float)(x - 16), d);
+        }
+    } else if constexpr (TYPE == B200_QT_Q4_K || TYPE == B200_QT_Q5_K) {
+        constexpr bool FIVE = TYPE == B200_QT_Q5_K;
+        const float d = sm_f16(blk), dmin = sm_f16(blk + 2);
+        const int g = j0 >> 6, half = (j0 >> 5) & 1, l0 = j0 & 31;
+        int sc, mn;
+        k4_scale_min(2 * g + half, blk + 4, sc, mn);
+        const float dd = __fmul_rn(d, (float)sc), mm = __fmul_rn(dmin, (float)mn);
+        const uint8_t* ql = blk + (FIVE ? 48 : 16) + g * 32 + l0;
+        const uint8_t* qh = blk + 16 + l0;
+        const int shift = half ? 4 : 0, hbit = (half ? 2 : 1) << (2 * g);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            int v = (ql[k] >> shift) & 15;
+            if (FIVE && (qh[k] & hbit)) v += 16;
+            y[k] = __fsub_rn(__fmul_rn(dd, (float)v), mm);
+        }
+    } else if constexpr (TYPE == B200_QT_Q6_K) {
+        const float d = sm_f16(blk + 208);
+        const int h = j0 >> 7, quarter = (j0 >> 5) & 3, l0 = j0 & 31;
+        const uint8_t* ql = blk + h * 64 + l0 + ((quarter & 1) ? 32 : 0);
+        const uint8_t* qh = blk + 128 + h * 32 + l0;
+        const float ds = __fmul_rn(d, (float)(int8_t)blk[192 + h * 8 + (l0 >> 4) + 2 * quarter]);
+        const int lshift = quarter < 2 ? 0 : 4, hshift = 2 * quarter;
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            const int q = (int)(int8_t)(((ql[k] >> lshift) & 15) | (((qh[k] >> hshift) & 3) << 4)) - 32;
+            y[k] = __fmul_rn(ds, (float)q);
+        }
+    }
+}
+
+template <typename OUT, int TYPE>
+__global__ void __launch_bounds__(EMBED_WARPS * 32)
+k_embed_rows_any(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out, int E, long long T,
+                 float scale, int* bad_row, int vec_ok) {
+    using F = RowFormat<TYPE>;
+    constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;
+    __shared__ __align__(16) uint8_t stage[EMBED_WARPS][EMBED_CHUNK_BLOCKS * 34];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    uint8_t* sm = stage[wid];
+    const int nb = E / F::BLK;
+    const long long warp0 = (long long)blockIdx.x * EMBED_WARPS + wid, nwarps = (long long)gridDim.x * EMBED_WARPS;
+    for (long long t = warp0; t < T; t += nwarps) {
+        const int tok = tokens[t];
+        OUT* orow = out + (size_t)t * E;
+        if (tok < 0 || tok >= vocab) {
+            if (lane == 0) atomicMin(bad_row, (int)(t < 0x7fffffff ? t : 0x7ffffffe));
+            for (int c = lane * VPL; c < E; c += 32 * VPL) st_stream(orow + c, make_uint4(0, 0, 0, 0));
+            continue;
+        }
+        const uint8_t* src = table + (size_t)tok * row_bytes;
+        for (int b0 = 0; b0 < nb; b0 += F::CHUNK) {
+            const int cb = min(F::CHUNK, nb - b0), bytes = cb * F::BB;
+            const uint8_t* s = src + (size_t)b0 * F::BB;
+            __syncwarp();
+            if (vec_ok) {
+                const int nv = bytes >> 4;
+                for (int i = lane; i < nv; i += 32) reinterpret_cast<uint4*>(sm)[i] = ld_stream(s + (size_t)i * 16);
+                for (int i = (nv << 4) + lane * 2; i < bytes; i += 64)
+                    *reinterpret_cast<uint16_t*>(sm + i) = *reinterpret_cast<const uint16_t*>(s + i);
+            } else {
+                for (int i = lane * 2; i < bytes; i += 64)
+                    *reinterpret_cast<uint16_t*>(sm + i) = *reinterpret_cast<const uint16_t*>(s + i);
+            }
+            __syncwarp();
+            for (int v = lane * VPL; v < cb * F::BLK; v += 32 * VPL) {
+                const int b = v / F::BLK, j0 = v % F::BLK;
+                float y[VPL];
+                decode_run<TYPE, VPL>(sm + b * F::BB, j0, y);
+                if (scale != 1.0f) {
+#pragma unroll
+                    for (int k = 0; k < VPL; ++k) y[k] = __fmul_rn(y[k], scale);
+                }
+                OUT* o = orow + (size_t)(b0 + b) * F::BLK + j0;
+                if constexpr (sizeof(OUT) == 4) {
+                    st_stream(o, make_uint4(__float_as_uint(y[0]), __float_as_uint(y[1]), __float_as_uint(y[2]),
+                                            __float_as_uint(y[3])));
+                } else {
+                    st_stream(o, make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]),
+                                            pack_bf16(y[6], y[7])));
+                }
+            }
+        }
+    }
+}
+
 }  // namespace b200
 
 #endif  // B200_EMBED_CUH

@@ -37,13 +37,19 @@ struct KvEntry {
 };
 
 // ggml type id -> (values per block, bytes per block) for the types this library handles
-// (src/quant_types.h:19-47 ids; block layouts src/quant_types.cpp:78-91,181-189)
+// (src/quant_types.h:19-47 ids; block sizes src/quant_types.cpp:583-598)
 bool type_layout(int type, int* blck, int* bytes) {
     switch (type) {
         case 0: *blck = 1; *bytes = 4; return true;     // F32
         case 1: *blck = 1; *bytes = 2; return true;     // F16
         case 2: *blck = 32; *bytes = 18; return true;   // Q4_0
+        case 3: *blck = 32; *bytes = 20; return true;   // Q4_1
+        case 6: *blck = 32; *bytes = 22; return true;   // Q5_0
+        case 7: *blck = 32; *bytes = 24; return true;   // Q5_1
         case 8: *blck = 32; *bytes = 34; return true;   // Q8_0
+        case 12: *blck = 256; *bytes = 144; return true;  // Q4_K
+        case 13: *blck = 256; *bytes = 176; return true;  // Q5_K
+        case 14: *blck = 256; *bytes = 210; return true;  // Q6_K
         case 30: *blck = 1; *bytes = 2; return true;    // BF16
         default: return false;
     }

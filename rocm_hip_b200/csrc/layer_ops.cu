@@ -377,21 +377,46 @@ template <typename OUT>
 cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out,
                          int E, long long T, float scale, int* bad_row, cudaStream_t stream) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
-    const size_t bb = type == B200_QT_Q8_0 ? 34 : type == B200_QT_Q4_0 ? 18 : 0;
-    if (!bb || T <= 0 || E <= 0 || E % 32 != 0 || vocab <= 0 || !table || !tokens || !out || !bad_row ||
-        row_bytes < (size_t)(E / 32) * bb || row_bytes % 2 != 0 || (reinterpret_cast<uintptr_t>(table) & 1u) ||
-        !al16(out))
+    size_t blk = 0, bb = 0;   // values and bytes per block (src/quant_types.cpp:583-598)
+    switch (type) {
+        case B200_QT_F32: blk = 1; bb = 4; break;
+        case B200_QT_F16: case B200_QT_BF16: blk = 1; bb = 2; break;
+        case B200_QT_Q4_0: blk = 32; bb = 18; break;
+        case B200_QT_Q4_1: blk = 32; bb = 20; break;
+        case B200_QT_Q5_0: blk = 32; bb = 22; break;
+        case B200_QT_Q5_1: blk = 32; bb = 24; break;
+        case B200_QT_Q8_0: blk = 32; bb = 34; break;
+        case B200_QT_Q4_K: blk = 256; bb = 144; break;
+        case B200_QT_Q5_K: blk = 256; bb = 176; break;
+        case B200_QT_Q6_K: blk = 256; bb = 210; break;
+        default: break;
+    }
+    if (!bb || T <= 0 || E <= 0 || E % 32 != 0 || E % (int)blk != 0 || vocab <= 0 || !table || !tokens || !out || !bad_row ||
+        row_bytes < (size_t)E / blk * bb || row_bytes % 2 != 0 || (reinterpret_cast<uintptr_t>(table) & 1u) || !al16(out))
         return cudaErrorInvalidValue;
     const int vec_ok = al16(table) && row_bytes % 16 == 0;
     const long long need = (T + EMBED_WARPS - 1) / EMBED_WARPS;
     const uint8_t* tb = static_cast<const uint8_t*>(table);
-    if (type == B200_QT_Q8_0) {
-        const long long res = persistent_grid(k_embed_rows<OUT, B200_QT_Q8_0>, EMBED_WARPS * 32, 0);
-        k_embed_rows<OUT, B200_QT_Q8_0><<<(unsigned)(need < res ? need : res), EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row, vec_ok);
-    } else {
-        const long long res = persistent_grid(k_embed_rows<OUT, B200_QT_Q4_0>, EMBED_WARPS * 32, 0);
-        k_embed_rows<OUT, B200_QT_Q4_0><<<(unsigned)(need < res ? need : res), EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row, vec_ok);
+#define EMBED(K, TY)                                                                                             \
+    do {                                                                                                         \
+        const long long res = persistent_grid(K<OUT, TY>, EMBED_WARPS * 32, 0);                                  \
+        K<OUT, TY><<<(unsigned)(need < res ? need : res), EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, \
+                                                                                         E, T, scale, bad_row, vec_ok);     \
+    } while (0)
+    switch (type) {
+        case B200_QT_Q8_0: EMBED(k_embed_rows, B200_QT_Q8_0); break;
+        case B200_QT_Q4_0: EMBED(k_embed_rows, B200_QT_Q4_0); break;
+        case B200_QT_F32: EMBED(k_embed_rows_any, B200_QT_F32); break;
+        case B200_QT_F16: EMBED(k_embed_rows_any, B200_QT_F16); break;
+        case B200_QT_BF16: EMBED(k_embed_rows_any, B200_QT_BF16); break;
+        case B200_QT_Q4_1: EMBED(k_embed_rows_any, B200_QT_Q4_1); break;
+        case B200_QT_Q5_0: EMBED(k_embed_rows_any, B200_QT_Q5_0); break;
+        case B200_QT_Q5_1: EMBED(k_embed_rows_any, B200_QT_Q5_1); break;
+        case B200_QT_Q4_K: EMBED(k_embed_rows_any, B200_QT_Q4_K); break;
+        case B200_QT_Q5_K: EMBED(k_embed_rows_any, B200_QT_Q5_K); break;
+        default: EMBED(k_embed_rows_any, B200_QT_Q6_K); break;
     }
+#undef EMBED
     return launched();
 }
 

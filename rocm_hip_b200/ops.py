@@ -14,18 +14,22 @@ from . import _lib
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
     "gpu_qk_norm_rope", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_mamba_conv", "gpu_mamba_scan", "gpu_ple_conv", "gpu_hc_norm", "gpu_hc_lowrank", "gpu_hc_mix", "gpu_ple_gate", "gpu_mtp_concat", "gpu_mamba_gnorm", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
-    "QT_Q4_0", "QT_Q8_0", "qt_row_size", "HostRows", "HostGroup",
+    "QT_Q4_0", "QT_Q8_0", "QT_F32", "QT_F16", "QT_BF16", "QT_Q4_1", "QT_Q5_0", "QT_Q5_1", "QT_Q4_K", "QT_Q5_K", "QT_Q6_K",
+    "QT_BLOCKS", "qt_row_size", "HostRows", "HostGroup",
 ]
 
 QT_Q4_0 = 2  # ggml type ids, src/quant_types.h:19-27 of the reference
 QT_Q8_0 = 8
+QT_F32, QT_F16, QT_Q4_1, QT_Q5_0, QT_Q5_1, QT_Q4_K, QT_Q5_K, QT_Q6_K, QT_BF16 = 0, 1, 3, 6, 7, 12, 13, 14, 30
+# (values per block, bytes per block) of the row formats gpu_embed_rows decodes (src/quant_types.cpp:583-598)
+QT_BLOCKS = {QT_F32: (1, 4), QT_F16: (1, 2), QT_BF16: (1, 2), QT_Q4_0: (32, 18), QT_Q4_1: (32, 20), QT_Q5_0: (32, 22),
+             QT_Q5_1: (32, 24), QT_Q8_0: (32, 34), QT_Q4_K: (256, 144), QT_Q5_K: (256, 176), QT_Q6_K: (256, 210)}
 
 
 def qt_row_size(qtype, ne0):
     """Bytes of one table row of ne0 values (src/quant_types.cpp:635-639); 0 if ne0 is not whole blocks."""
-    if ne0 % 32:
-        return 0
-    return ne0 // 32 * {QT_Q8_0: 34, QT_Q4_0: 18}.get(qtype, 0)
+    blk, bb = QT_BLOCKS.get(qtype, (1, 0))
+    return 0 if ne0 % blk else ne0 // blk * bb
 
 
 class LayerOpError(RuntimeError):

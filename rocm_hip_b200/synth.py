@@ -78,6 +78,33 @@ def q4_0_table(seed, name, vocab, E, row0=0, rows=None):
     return out.reshape(rows, nb * 18)
 
 
+# ggml type id -> (values per block, bytes per block, byte offsets of the fp16 fields of a block)
+GGUF_BLOCKS = {0: (1, 4, ()), 1: (1, 2, ()), 30: (1, 2, ()), 2: (32, 18, (0,)), 3: (32, 20, (0, 2)), 6: (32, 22, (0,)),
+               7: (32, 24, (0, 2)), 8: (32, 34, (0,)), 12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,))}
+
+
+def gguf_table(seed, name, qtype, rows, E):
+    """A table of `rows` rows of E values in GGUF row format `qtype` (a ggml type id of GGUF_BLOCKS) as uint8
+    [rows][row bytes]: every payload byte uniform in [0, 255], the fp16 scale / minimum fields finite values
+    ~U(1e-3, 2e-2) with random sign; F32 / F16 / BF16 rows are N(0, 1) values in that format."""
+    blk, bb, halves = GGUF_BLOCKS[qtype]
+    assert E % blk == 0
+    if blk == 1:
+        v = normal(seed, name + ".v", 0, rows * E)
+        if qtype == 0:
+            return v.view(np.uint8).reshape(rows, E * 4).copy()
+        if qtype == 1:
+            return v.astype(np.float16).view(np.uint8).reshape(rows, E * 2).copy()
+        return f32_to_bf16_bits(v).view(np.uint8).reshape(rows, E * 2).copy()
+    nblk = rows * (E // blk)
+    out = randint(seed, name + ".q", 0, nblk * bb, 0, 256).astype(np.uint8).reshape(nblk, bb)
+    for k, off in enumerate(halves):
+        d = (1e-3 + uniform(seed, name + ".d%d" % k, 0, nblk) * (2e-2 - 1e-3))
+        d = (d * np.where(uniform(seed, name + ".s%d" % k, 0, nblk) < 0.25, -1.0, 1.0)).astype(np.float16)
+        out[:, off:off + 2] = d.view(np.uint8).reshape(nblk, 2)
+    return out.reshape(rows, (E // blk) * bb)
+
+
 def moe_routing(seed, name, T, n_expert, n_used):
     """Per token n_used distinct experts drawn uniformly; returns (ids [T][n_used], order) where order lists the
     T * n_used (token, slot) rows sorted by expert id, stable, as an expert-grouping pass would."""

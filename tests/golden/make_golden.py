@@ -76,6 +76,25 @@ def main():
         cases[name + "_table"], cases[name + "_out"] = tab, out
     np.savez_compressed(os.path.join(OUT, "dequant.npz"), **cases)
 
+    # ---- qt_to_float for the other row formats the gather decodes (src/quant_types.cpp:58-74,126-179,264-345):
+    #      random payload bytes (every nibble / high-bit / 6-bit scale pattern occurs), finite fp16 scales of both
+    #      signs, and in the first blocks the special fp16 scales of above
+    cases = {}
+    E, rows = 512, 12
+    for qt in (O.F32, O.F16, O.BF16, O.Q4_1, O.Q5_0, O.Q5_1, O.Q4_K, O.Q5_K, O.Q6_K):
+        tab = synth.gguf_table(0, "g.any.%d" % qt, qt, rows, E).copy()
+        blk, bb, halves = synth.GGUF_BLOCKS[qt]
+        if halves:
+            blocks = tab.reshape(-1, bb)
+            for off in halves:
+                blocks[: special.size, off:off + 2] = special.view(np.uint8).reshape(-1, 2)
+        out = np.empty((rows, E), dtype=np.float32)
+        for r in range(rows):
+            assert R.qt_to_float(qt, p(tab[r]), p(out[r]), E) == 0
+        assert R.qt_row_size(qt, E) == tab.shape[1]
+        cases["t%d_table" % qt], cases["t%d_out" % qt] = tab, out
+    np.savez_compressed(os.path.join(OUT, "dequant_more.npz"), **cases)
+
     # ---- qt_fp16_to_fp32 over every fp16 bit pattern, qt_bf16_to_fp32 likewise (src/quant_types.cpp:16-48)
     h = np.arange(65536, dtype=np.uint32)
     f16 = np.array([R.qt_fp16_to_fp32(int(v)) for v in h], dtype=np.float32)

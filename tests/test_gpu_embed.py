@@ -118,7 +118,60 @@ def test_argument_errors(ops):
     t = torch.zeros(1024, dtype=torch.uint8, device="cuda")
     ids = torch.zeros(4, dtype=torch.int32, device="cuda")
     out = torch.zeros(4, 64, device="cuda")
-    for qt, E, rb in ((7, 64, 68), (8, 48, 68), (8, 64, 60), (8, 64, 69)):
+    for qt, E, rb in ((9, 64, 68), (8, 48, 68), (8, 64, 60), (8, 64, 69)):
         with pytest.raises(ops.LayerOpError) as e:
             ops.gpu_embed_rows(qt, t, rb, 10, ids, out, E, 4)
         assert e.value.code == 1
+
+
+ALL_FORMATS = ["QT_F32", "QT_F16", "QT_BF16", "QT_Q4_1", "QT_Q5_0", "QT_Q5_1", "QT_Q4_K", "QT_Q5_K", "QT_Q6_K"]
+
+
+@pytest.mark.parametrize("fmt", ALL_FORMATS)
+@pytest.mark.parametrize("E", [512, 5120, 2304])
+def test_other_row_formats_bit_exact(ops, oracle, fmt, E):
+    """The other formats a token_embd.weight comes in (src/quant_types.cpp:58-74,126-179,264-345): fp32 and bf16 output,
+    with and without an embedding scale, a row stride larger than the row, bad ids -- bit for bit against the oracle,
+    whose decoders are pinned to the reference build's qt_to_float."""
+    qt = getattr(ops, fmt)
+    vocab, T = 300, 517
+    table = synth.gguf_table(5, "emb." + fmt, qt, vocab, E)
+    assert ops.qt_row_size(qt, E) == table.shape[1]
+    ids = synth.randint(5, "emb.ids", 0, T, 0, vocab).astype(np.int32)
+    dt, d_ids = dev(table), dev(ids)
+    for scale in (1.0, 0.0625 * 3):
+        out = torch.zeros(T, E, device="cuda")
+        flag = ops.gpu_embed_rows(qt, dt, table.shape[1], vocab, d_ids, out, E, T, scale)
+        torch.cuda.synchronize()
+        st, want = oracle.embed_rows(qt, table, table.shape[1], vocab, ids, E, scale)
+        assert st == 0 and int(flag.item()) == 2**31 - 1
+        assert np.array_equal(host(out).view(np.uint32), want.view(np.uint32))
+        ob = torch.zeros(T, E, device="cuda", dtype=torch.bfloat16)
+        ops.gpu_embed_rows(qt, dt, table.shape[1], vocab, d_ids, ob, E, T, scale)
+        torch.cuda.synchronize()
+        _, wb = oracle.embed_rows(qt, table, table.shape[1], vocab, ids, E, scale, bf16=True)
+        assert np.array_equal(host(ob), wb)
+    # rows at a stride (2 extra bytes: rows no longer 16-byte aligned -> the 2-byte staging path), and a bad id
+    wide = np.zeros((vocab, table.shape[1] + 2), np.uint8)
+    wide[:, :table.shape[1]] = table
+    bad = ids.copy()
+    bad[77] = vocab + 5
+    out = torch.full((T, E), -1.0, device="cuda")
+    flag = ops.gpu_embed_rows(qt, dev(wide), wide.shape[1], vocab, dev(bad), out, E, T, 1.0)
+    torch.cuda.synchronize()
+    _, want = oracle.embed_rows(qt, table, table.shape[1], vocab, ids, E)
+    got = host(out)
+    assert int(flag.item()) == 77 and not got[77].any()
+    keep = np.arange(T) != 77
+    assert np.array_equal(got[keep].view(np.uint32), want[keep].view(np.uint32))
+
+
+def test_k_formats_need_whole_super_blocks(ops):
+    t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    ids = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = torch.zeros(4, 128, device="cuda")
+    with pytest.raises(ops.LayerOpError) as e:
+        ops.gpu_embed_rows(ops.QT_Q6_K, t, 210, 16, ids, out, 128, 4, 1.0)      # 128 is not a multiple of 256
+    assert e.value.code == 1
+    with pytest.raises(ops.LayerOpError):
+        ops.gpu_embed_rows(9, t, 64, 16, ids, out, 128, 4, 1.0)                 # ggml id 9 (Q8_1) is not a row format

@@ -74,7 +74,28 @@ def test_dequant_golden(oracle):
             st, _ = oracle.embed_rows(qt, tab, tab.shape[1], rows, np.array([0, bad, 1]), E)
             assert st == -1
     assert oracle.port().orc_row_size(oracle.Q8_0, 33) == 0
-    assert oracle.port().orc_to_float(7, None, None, 32) == -1
+    assert oracle.port().orc_to_float(9, None, None, 32) == -1        # (ggml id 9, Q8_1, is not a row format here)
+
+
+def test_dequant_golden_other_row_formats(oracle):
+    """F32 / F16 / BF16 / Q4_1 / Q5_0 / Q5_1 / Q4_K / Q5_K / Q6_K rows: the restatement against the reference build's
+    qt_to_float on random payloads (every bit pattern of the packed fields occurs), finite scales of both signs and the
+    special fp16 scales (zero, subnormal, largest, negative), bit for bit."""
+    g = load("dequant_more.npz")
+    for qt in (oracle.F32, oracle.F16, oracle.BF16, oracle.Q4_1, oracle.Q5_0, oracle.Q5_1, oracle.Q4_K, oracle.Q5_K,
+               oracle.Q6_K):
+        tab, want = g["t%d_table" % qt], g["t%d_out" % qt]
+        rows, E = want.shape
+        blk, bb = oracle.BLOCK[qt]
+        assert oracle.port().orc_row_size(qt, E) == tab.shape[1] == E // blk * bb
+        assert oracle.port().orc_row_size(qt, E + 1) == (0 if blk > 1 else (E + 1) * bb)
+        st, out = oracle.embed_rows(qt, tab, tab.shape[1], rows, np.arange(rows), E)
+        assert st == 0
+        ok = ~np.isnan(want)                                   # (a NaN scale has no defined payload)
+        assert np.array_equal(bits(out)[ok], bits(want)[ok]) and np.array_equal(np.isnan(out), np.isnan(want)), qt
+        perm = synth.randint(3, "perm2", 0, 50, 0, rows)
+        st, out = oracle.embed_rows(qt, tab, tab.shape[1], rows, perm, E, scale=0.125)
+        assert st == 0 and np.array_equal(bits(out)[ok[perm]], bits((want[perm] * np.float32(0.125)).astype(np.float32))[ok[perm]])
 
 
 def test_half_tables_golden(oracle):
