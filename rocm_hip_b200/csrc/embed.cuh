@@ -153,7 +153,26 @@ __device__ __forceinline__ void k4_scale_min(int j, const uint8_t* q, int& sc, i
     }
 }
 
-// Values j0 .. j0 + N - 1 of the block at blk (N = 4 or 8, j0 a multiple of N)
+// N (4 or 8) consecutive bytes at p as one little-endian word, fetched with the widest shared-memory loads that the
+// alignment A (a power of two that divides p's offset in the stage buffer) allows
+template <int N, int A>
+__device__ __forceinline__ uint64_t ld_bytes(const uint8_t* p) {
+    if constexpr (A >= 8 && N == 8) {
+        return *reinterpret_cast<const uint64_t*>(p);
+    } else if constexpr (A >= 4) {
+        uint64_t w = *reinterpret_cast<const uint32_t*>(p);
+        if constexpr (N == 8) w |= (uint64_t)*reinterpret_cast<const uint32_t*>(p + 4) << 32;
+        return w;
+    } else {
+        uint64_t w = 0;
+#pragma unroll
+        for (int k = 0; k < N / 2; ++k) w |= (uint64_t)*reinterpret_cast<const uint16_t*>(p + 2 * k) << (16 * k);
+        return w;
+    }
+}
+
+// Values j0 .. j0 + N - 1 of the block at blk (N = 4 or 8, j0 a multiple of N). Block starts are multiples of
+// gcd(BB, 16) bytes in the stage buffer, which fixes the alignment of every field below.
 template <int TYPE, int N>
 __device__ __forceinline__ void decode_run(const uint8_t* blk, int j0, float* y) {
     if constexpr (TYPE == B200_QT_F32) {
@@ -168,20 +187,18 @@ __device__ __forceinline__ void decode_run(const uint8_t* blk, int j0, float* y)
             y[k] = __uint_as_float((uint32_t)*reinterpret_cast<const uint16_t*>(blk + 2 * (j0 + k)) << 16);
     } else if constexpr (TYPE == B200_QT_Q4_1) {
         const float d = sm_f16(blk), m = sm_f16(blk + 2);
-        const uint8_t* qs = blk + 4 + (j0 & 15);
-        const int shift = j0 < 16 ? 0 : 4;
+        const uint64_t qs = ld_bytes<N, 4>(blk + 4 + (j0 & 15)) >> (j0 < 16 ? 0 : 4);
 #pragma unroll
-        for (int k = 0; k < N; ++k) y[k] = __fadd_rn(__fmul_rn((float)((qs[k] >> shift) & 15), d), m);
+        for (int k = 0; k < N; ++k) y[k] = __fadd_rn(__fmul_rn((float)((uint32_t)(qs >> (8 * k)) & 15u), d), m);
     } else if constexpr (TYPE == B200_QT_Q5_0 || TYPE == B200_QT_Q5_1) {
         constexpr bool ONE = TYPE == B200_QT_Q5_1;
         const float d = sm_f16(blk), m = ONE ? sm_f16(blk + 2) : 0.0f;
         const uint8_t* hb = blk + (ONE ? 4 : 2);
         const uint32_t qh = hb[0] | (hb[1] << 8) | (hb[2] << 16) | ((uint32_t)hb[3] << 24);
-        const uint8_t* qs = blk + (ONE ? 8 : 6) + (j0 & 15);
-        const int shift = j0 < 16 ? 0 : 4;
+        const uint64_t qs = ld_bytes<N, ONE ? 8 : 2>(blk + (ONE ? 8 : 6) + (j0 & 15)) >> (j0 < 16 ? 0 : 4);
 #pragma unroll
         for (int k = 0; k < N; ++k) {
-            const int x = ((qs[k] >> shift) & 15) | (int)(((qh >> (j0 + k)) & 1u) << 4);   // bit j of qh is value j's fifth bit
+            const int x = (int)((uint32_t)(qs >> (8 * k)) & 15u) | (int)(((qh >> (j0 + k)) & 1u) << 4);   // bit j of qh: value j's fifth bit
             y[k] = ONE ? __fadd_rn(__fmul_rn((float)x, d), m) : __fmul_rn((float)(x - 16), d);
         }
     } else if constexpr (TYPE == B200_QT_Q4_K || TYPE == B200_QT_Q5_K) {
@@ -191,25 +208,23 @@ __device__ __forceinline__ void decode_run(const uint8_t* blk, int j0, float* y)
         int sc, mn;
         k4_scale_min(2 * g + half, blk + 4, sc, mn);
         const float dd = __fmul_rn(d, (float)sc), mm = __fmul_rn(dmin, (float)mn);
-        const uint8_t* ql = blk + (FIVE ? 48 : 16) + g * 32 + l0;
-        const uint8_t* qh = blk + 16 + l0;
-        const int shift = half ? 4 : 0, hbit = (half ? 2 : 1) << (2 * g);
+        const uint64_t ql = ld_bytes<N, 8>(blk + (FIVE ? 48 : 16) + g * 32 + l0) >> (half ? 4 : 0);
+        const uint64_t qh = FIVE ? ld_bytes<N, 8>(blk + 16 + l0) >> (2 * g + half) : 0;
 #pragma unroll
         for (int k = 0; k < N; ++k) {
-            int v = (ql[k] >> shift) & 15;
-            if (FIVE && (qh[k] & hbit)) v += 16;
+            int v = (int)((uint32_t)(ql >> (8 * k)) & 15u);
+            if (FIVE) v += (int)((uint32_t)(qh >> (8 * k)) & 1u) << 4;
             y[k] = __fsub_rn(__fmul_rn(dd, (float)v), mm);
         }
     } else if constexpr (TYPE == B200_QT_Q6_K) {
         const float d = sm_f16(blk + 208);
         const int h = j0 >> 7, quarter = (j0 >> 5) & 3, l0 = j0 & 31;
-        const uint8_t* ql = blk + h * 64 + l0 + ((quarter & 1) ? 32 : 0);
-        const uint8_t* qh = blk + 128 + h * 32 + l0;
+        const uint64_t ql = ld_bytes<N, 2>(blk + h * 64 + l0 + ((quarter & 1) ? 32 : 0)) >> (quarter < 2 ? 0 : 4);
+        const uint64_t qh = ld_bytes<N, 2>(blk + 128 + h * 32 + l0) >> (2 * quarter);
         const float ds = __fmul_rn(d, (float)(int8_t)blk[192 + h * 8 + (l0 >> 4) + 2 * quarter]);
-        const int lshift = quarter < 2 ? 0 : 4, hshift = 2 * quarter;
 #pragma unroll
         for (int k = 0; k < N; ++k) {
-            const int q = (int)(int8_t)(((ql[k] >> lshift) & 15) | (((qh[k] >> hshift) & 3) << 4)) - 32;
+            const int q = (int)(((uint32_t)(ql >> (8 * k)) & 15u) | (((uint32_t)(qh >> (8 * k)) & 3u) << 4)) - 32;
             y[k] = __fmul_rn(ds, (float)q);
         }
     }

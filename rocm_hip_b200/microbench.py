@@ -73,6 +73,16 @@ def cases(T, n):
     nt = torch.zeros(1, device="cuda", dtype=torch.int32)
     te, ts, tn = (torch.empty(mt, device="cuda", dtype=torch.int32) for _ in range(3))
     yield "moe_group (%d x 8 entries)" % Tg, lambda: m.gpu_moe_group(gi, Tg, U, E, 64, tok, pair, nt, te, ts, tn), 12 * Tg * U
+    # embedding gather, bf16 rows of 5120 out: 4 (id) + row bytes + 2 * 5120 per token
+    from rocm_hip_b200 import synth
+    Ee, vocab = 5120, 32768
+    eid = torch.randint(0, vocab, (T,), device="cuda", dtype=torch.int32)
+    eout = torch.empty(T, Ee, device="cuda", dtype=torch.bfloat16)
+    for qn in ("QT_Q8_0", "QT_Q4_0", "QT_Q4_K", "QT_Q6_K", "QT_Q5_1", "QT_F16"):
+        qt = getattr(m, qn)
+        rb = m.qt_row_size(qt, Ee)
+        tab = torch.from_numpy(synth.gguf_table(0, "mb." + qn, qt, 64, Ee)).cuda().repeat(vocab // 64, 1).contiguous()
+        yield "embed_rows %s -> bf16" % qn[3:], (lambda qt=qt, rb=rb, tab=tab: m.gpu_embed_rows(qt, tab, rb, vocab, eid, eout, Ee, T)), T * (4 + rb + 2 * Ee)
     # routers: logits [T][256] in, 8 ids + 8 weights out; with the shared-expert gate the x row is read too
     lg = R(T, 256)
     rid = torch.empty(T, 8, device="cuda", dtype=torch.int32)
