@@ -32,4 +32,38 @@ typedef cudaEvent_t hipEvent_t;
 #define hipMemcpyDeviceToDevice cudaMemcpyDeviceToDevice
 #define hipMemsetAsync cudaMemsetAsync
 
+/* The module-launch and pinned-host calls of the reference's component test programs
+ * (tests/layernorm_verify.cpp:78-98, tests/rope_verify.cpp:95-116), onto the CUDA driver's module API and the
+ * runtime's host registration, so that those programs compile unchanged and load this library's module images in
+ * place of their .co files. Off unless B200_HIP_SHIM_MODULE_API is defined: it needs cuda.h and -lcuda. */
+#ifdef B200_HIP_SHIM_MODULE_API
+#include <cuda.h>
+
+typedef CUmodule hipModule_t;
+typedef CUfunction hipFunction_t;
+#define hipHostRegisterDefault cudaHostRegisterDefault
+#define hipHostRegister cudaHostRegister
+#define hipHostUnregister cudaHostUnregister
+#define hipHostGetDevicePointer cudaHostGetDevicePointer
+
+static inline hipError_t b200_hip_from_cu(CUresult r) { return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorUnknown; }
+static inline hipError_t hipInit(unsigned flags) {
+    const CUresult r = cuInit(flags);
+    if (r != CUDA_SUCCESS) return cudaErrorUnknown;
+    return cudaFree(0);   /* the driver calls below need the runtime's primary context current on this thread */
+}
+static inline hipError_t hipModuleLoadData(hipModule_t* mod, const void* image) {
+    return b200_hip_from_cu(cuModuleLoadData(mod, image));
+}
+static inline hipError_t hipModuleGetFunction(hipFunction_t* fn, hipModule_t mod, const char* name) {
+    return b200_hip_from_cu(cuModuleGetFunction(fn, mod, name));
+}
+static inline hipError_t hipModuleLaunchKernel(hipFunction_t fn, unsigned gx, unsigned gy, unsigned gz, unsigned bx,
+                                               unsigned by, unsigned bz, unsigned shared_bytes, hipStream_t stream,
+                                               void** params, void** extra) {
+    return b200_hip_from_cu(cuLaunchKernel(fn, gx, gy, gz, bx, by, bz, shared_bytes, stream, params, extra));
+}
+static inline hipError_t hipModuleUnload(hipModule_t mod) { return b200_hip_from_cu(cuModuleUnload(mod)); }
+#endif
+
 #endif
