@@ -543,6 +543,10 @@ def main():
         cpu = {"value": rows / dt, "unit": "rows/s", "cores": cs.threads, "kind": cs.kind,
                "sample": f"{rows} token rows of the same sweep per step, 3 steps, fp32 (the reference's CPU precision), "
                          f"{cs.threads} host threads"}
+        # one thread, which is how the reference runs its embedding decode (src/qwen_model.cpp:980): a smaller sample
+        rows1 = max(256, rows // 16)
+        _, dt1 = time_cpu(wl, rows1, 2, 1, threads=1)
+        cpu["single_thread"] = {"value": rows1 / dt1, "unit": "rows/s", "cores": 1, "sample": f"{rows1} token rows, 2 steps"}
 
     if rank == 0:
         line = {
