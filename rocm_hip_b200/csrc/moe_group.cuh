@@ -133,9 +133,9 @@ k_moe_seg_count(const int* ids, int n, int n_expert, int seg_len, int n_segs, in
     if (seg >= n_segs) return;
     int* h = hist[w];
     moe_zero_row(h, n_expert, lane);
-    const int lo = seg * seg_len, hi = min(n, lo + seg_len);
-    for (int base = lo; base < hi; base += 32) {
-        const int i = base + lane;
+    const long long lo = (long long)seg * seg_len, hi = min((long long)n, lo + seg_len);   // (n may be near INT_MAX)
+    for (long long base = lo; base < hi; base += 32) {
+        const long long i = base + lane;
         const int e = i < hi ? ids[i] : -1;
         const bool ok = e >= 0 && e < n_expert;
         const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
@@ -218,9 +218,9 @@ k_moe_seg_scatter(const int* ids, int n, int n_used, int n_expert, int seg_len, 
     int* nx = next[w];
     for (int e = lane; e < n_expert; e += 32) nx[e] = offsets[(size_t)seg * n_expert + e];
     __syncwarp();
-    const int lo = seg * seg_len, hi = min(n, lo + seg_len);
-    for (int base = lo; base < hi; base += 32) {
-        const int i = base + lane;
+    const long long lo = (long long)seg * seg_len, hi = min((long long)n, lo + seg_len);
+    for (long long base = lo; base < hi; base += 32) {
+        const long long i = base + lane;
         const int e = i < hi ? ids[i] : -1;
         const bool ok = e >= 0 && e < n_expert;
         const unsigned peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
@@ -231,8 +231,8 @@ k_moe_seg_scatter(const int* ids, int n, int n_used, int n_expert, int seg_len, 
         if (ok && rank == 0) nx[e] += __popc(peers);
         __syncwarp();
         if (ok) {
-            tok_rows[p] = i / n_used;
-            pair_rows[p] = i;
+            tok_rows[p] = (int)(i / n_used);
+            pair_rows[p] = (int)i;
         }
     }
 }
