@@ -33,7 +33,8 @@ typedef cudaEvent_t hipEvent_t;
 #define hipMemsetAsync cudaMemsetAsync
 
 /* The module-launch and pinned-host calls of the reference's component test programs
- * (tests/layernorm_verify.cpp:78-98, tests/rope_verify.cpp:95-116), onto the CUDA driver's module API and the
+ * (tests/layernorm_verify.cpp:78-98, tests/rope_verify.cpp:95-116) and of its launcher sources (src/gpu_ops.cpp,
+ * src/kernel_loader.cpp), onto the CUDA driver's module API and the
  * runtime's host registration, so that those programs compile unchanged and load this library's module images in
  * place of their .co files. Off unless B200_HIP_SHIM_MODULE_API is defined: it needs cuda.h and -lcuda. */
 #ifdef B200_HIP_SHIM_MODULE_API
@@ -53,7 +54,12 @@ static inline hipError_t hipInit(unsigned flags) {
     return cudaFree(0);   /* the driver calls below need the runtime's primary context current on this thread */
 }
 static inline hipError_t hipModuleLoadData(hipModule_t* mod, const void* image) {
+    if (cudaFree(0) != cudaSuccess) return cudaErrorUnknown;
     return b200_hip_from_cu(cuModuleLoadData(mod, image));
+}
+static inline hipError_t hipModuleLoad(hipModule_t* mod, const char* path) {
+    if (cudaFree(0) != cudaSuccess) return cudaErrorUnknown;   /* (makes the primary context current) */
+    return b200_hip_from_cu(cuModuleLoad(mod, path));
 }
 static inline hipError_t hipModuleGetFunction(hipFunction_t* fn, hipModule_t mod, const char* name) {
     return b200_hip_from_cu(cuModuleGetFunction(fn, mod, name));

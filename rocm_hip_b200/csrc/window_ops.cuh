@@ -65,10 +65,10 @@ k_mamba_conv(const float* zx, long long ld, int x_off, const float* conv_state, 
     }
 }
 
-__global__ void __launch_bounds__(256)
-k_mamba_conv_state(const float* zx, long long ld, int x_off, float* conv_state, int conv_dim, int d_conv, long long T) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x, ns = d_conv - 1;
-    if (c >= conv_dim) return;
+// Channel c's conv state after T tokens: the last d_conv - 1 inputs, oldest first
+__device__ __forceinline__ void mamba_conv_state_channel(const float* zx, long long ld, int x_off, float* conv_state, int c,
+                                                         int d_conv, long long T) {
+    const int ns = d_conv - 1;
     float* st = conv_state + (size_t)c * ns;
     float h[MAMBA_MAXC];
     for (int i = 0; i < ns; ++i) {
@@ -76,6 +76,12 @@ k_mamba_conv_state(const float* zx, long long ld, int x_off, float* conv_state, 
         h[i] = tt >= 0 ? zx[tt * ld + x_off + c] : st[i + T];
     }
     for (int i = 0; i < ns; ++i) st[i] = h[i];
+}
+
+__global__ void __launch_bounds__(256)
+k_mamba_conv_state(const float* zx, long long ld, int x_off, float* conv_state, int conv_dim, int d_conv, long long T) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < conv_dim) mamba_conv_state_channel(zx, ld, x_off, conv_state, c, d_conv, T);
 }
 
 template <int W>
@@ -118,10 +124,8 @@ k_ple_conv(const float* normed, const float* gated, float* res, const float* sta
 
 // The states after the first tokens, then the state after the batch: row i of a state is row (tokens seen + i) of
 // [old state rows | normed rows]. One thread per channel; ascending i only reads rows above i of the old state.
-__global__ void __launch_bounds__(256)
-k_ple_conv_state(const float* normed, float* state, int m, long long T, int K, int dil, MidStates mid) {
-    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
-    if (ch >= m) return;
+__device__ __forceinline__ void ple_conv_state_channel(const float* normed, float* state, int m, long long T, int K, int dil,
+                                                       const MidStates& mid, int ch) {
     const int H = (K - 1) * dil;
     for (int j = 0; j < 3 && j < T - 1; ++j)
         if (mid.p[j])
@@ -135,12 +139,17 @@ k_ple_conv_state(const float* normed, float* state, int m, long long T, int K, i
     }
 }
 
-// CTA of 64 threads: dims 16 part .. 16 part + 15 of head h, four threads per dim with 32 state values each
-__global__ void __launch_bounds__(64)
-k_mamba_scan(float* state, const float* xbc, const float* zx, long long ld, int dt_off, const float* dt_b, const float* A,
-             const float* D, float* y, int n_head, int d_inner, int n_group, long long T) {
-    const int h = blockIdx.x >> 2, part = blockIdx.x & 3, tid = threadIdx.x;
-    const int i = part * 16 + (tid >> 2), q = tid & 3;
+__global__ void __launch_bounds__(256)
+k_ple_conv_state(const float* normed, float* state, int m, long long T, int K, int dil, MidStates mid) {
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch < m) ple_conv_state_channel(normed, state, m, T, K, dil, mid, ch);
+}
+
+// The recurrence of one thread: dim i of head h, state values 32 q .. 32 q + 31 (the four threads of a dim are four
+// neighbouring lanes)
+__device__ __forceinline__ void mamba_scan_thread(float* state, const float* xbc, const float* zx, long long ld, int dt_off,
+                                                  const float* dt_b, const float* A, const float* D, float* y, int n_head,
+                                                  int d_inner, int n_group, long long T, int h, int i, int q) {
     const int g = h / (n_head / n_group), conv_dim = d_inner + 2 * n_group * MAMBA_DS;
     float* st = state + ((size_t)h * MAMBA_P + i) * MAMBA_DS + 32 * q;
     float s[32];
@@ -173,6 +182,14 @@ k_mamba_scan(float* state, const float* xbc, const float* zx, long long ld, int 
     }
 #pragma unroll
     for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(st + j) = Io<float>::pack(s + j);
+}
+
+// CTA of 64 threads: dims 16 part .. 16 part + 15 of head h, four threads per dim
+__global__ void __launch_bounds__(64)
+k_mamba_scan(float* state, const float* xbc, const float* zx, long long ld, int dt_off, const float* dt_b, const float* A,
+             const float* D, float* y, int n_head, int d_inner, int n_group, long long T) {
+    mamba_scan_thread(state, xbc, zx, ld, dt_off, dt_b, A, D, y, n_head, d_inner, n_group, T, blockIdx.x >> 2,
+                      (blockIdx.x & 3) * 16 + (threadIdx.x >> 2), threadIdx.x & 3);
 }
 
 }  // namespace b200
