@@ -277,7 +277,7 @@ cudaError_t gpu_embed_rows_host_ids(int type, const void* table, size_t row_byte
  * and the bad-id flag live in an array built into the library, so the call allocates nothing and takes no scratch
  * arguments. Limits: T <= 262144 ids per call (cudaErrorInvalidValue beyond that; the array costs every GPU that
  * loads the library 1 MiB for the life of the process); all calls on a device share the array, so calls whose GPU work
- * may overlap race; the first call on a device resolves the array's address and should precede any stream capture.
+ * may overlap race.
  * Ids are range-checked on the host first: an id outside [0, vocab) returns cudaErrorInvalidValue and queues nothing.
  * tokens_host must stay valid until its copy has run on `stream`. fp32 output, same bits as gpu_embed_rows. */
 cudaError_t gpu_embed_rows_static_scratch(int type, const void* table, size_t row_bytes, int vocab,

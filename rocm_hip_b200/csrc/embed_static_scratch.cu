@@ -13,9 +13,7 @@
 //     different threads) race on it: keep calls on one stream, or order them yourself;
 //   * the array keeps whatever the previous call left: each call overwrites the ids it needs and resets the flag
 //     word before launching, nothing else is assumed clean.
-// The first call on each device looks up the array's device address (cudaGetSymbolAddress). That lookup initialises
-// the CUDA context's view of the module if nothing has yet, so make the first call on a device before any stream
-// capture begins on it.
+// The first call on each device looks up the array's device address (cudaGetSymbolAddress), once.
 
 #include "b200_layer_ops.h"
 
