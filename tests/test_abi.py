@@ -91,3 +91,18 @@ def test_ctypes_struct_matches_c_layout():
     from rocm_hip_b200 import _lib
     assert C.sizeof(_lib.qmatvec_q8) == 72
     assert _lib.qmatvec_q8.max_k.offset == 48 and _lib.qmatvec_q8.xh.offset == 56 and _lib.qmatvec_q8.xh_bf16.offset == 64
+
+
+@pytest.mark.skipif(not shutil.which("g++"), reason="g++ not present")
+def test_hip_shim_headers_compile_alone(tmp_path):
+    """The hip/ shim headers stand on their own, with and without the module-API section (which the reference's
+    launcher sources and test programs need: hipModuleLoadData, hipModuleLaunchKernel, hipHostRegister ...)."""
+    for defs in ([], ["-DB200_HIP_SHIM_MODULE_API"]):
+        src = tmp_path / "shim.cpp"
+        src.write_text('#include <hip/hip_runtime.h>\n#include <hip/hip_fp16.h>\n'
+                       'hipError_t f(hipStream_t s) { return hipStreamSynchronize(s) == hipSuccess ? hipSuccess : hipErrorInvalidValue; }\n'
+                       + ('hipError_t g(hipModule_t* m, hipFunction_t* k, const void* img) { hipError_t e = hipModuleLoadData(m, img); '
+                          'return e != hipSuccess ? e : hipModuleGetFunction(k, *m, "rmsnorm"); }\n' if defs else ''))
+        r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", f"-I{ROOT}/include", "-I/usr/local/cuda/include"] + defs + [str(src)],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
