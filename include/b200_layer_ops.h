@@ -208,6 +208,22 @@ cudaError_t gpu_qk_norm_rope_bf16(const uint16_t* qfull, const uint16_t* k, cons
                                   int rot_pairs, const int* positions, int pos0, long long T, float freq_base,
                                   float eps, int gated, int qk_norm, const float* freq_factors, cudaStream_t stream);
 
+/* gpu_qk_norm_rope with the K write of the reference's attn_prep folded in (src/attention.hip:286-299, FP16 cache):
+ * the K heads go, rounded to fp16, straight to row pos_t of k_cache (the layer's K row 0; row addressing as
+ * gpu_kv_store_f16 below) instead of a k_out tensor, so K makes no extra round trip; q as in gpu_qk_norm_rope. fp32
+ * rows: the same bits as gpu_qk_norm_rope followed by gpu_kv_store_f16; bf16 rows: K is rounded once, from fp32 to fp16
+ * (not to bf16 on the way). kv_stride >= n_kv * head_dim. V rows: gpu_kv_store_f16. */
+cudaError_t gpu_qk_norm_rope_kv(const float* qfull, const float* k, const float* q_norm, const float* k_norm, float* q_out,
+                                uint16_t* k_cache, int kv_stride, int kv_shift, long long kv_bstride, int n_q, int n_kv,
+                                int head_dim, int n_rot, int rot_pairs, const int* positions, int pos0, long long T,
+                                float freq_base, float eps, int gated, int qk_norm, const float* freq_factors,
+                                cudaStream_t stream);
+cudaError_t gpu_qk_norm_rope_kv_bf16(const uint16_t* qfull, const uint16_t* k, const float* q_norm, const float* k_norm,
+                                     uint16_t* q_out, uint16_t* k_cache, int kv_stride, int kv_shift, long long kv_bstride,
+                                     int n_q, int n_kv, int head_dim, int n_rot, int rot_pairs, const int* positions,
+                                     int pos0, long long T, float freq_base, float eps, int gated, int qk_norm,
+                                     const float* freq_factors, cudaStream_t stream);
+
 /* The K / V write of the reference's attn_prep kernels for an unquantised (FP16) cache (src/attention.hip:279-300):
  * row t of src [T][n_vals] (n_vals = n_kv * head_dim; K after gpu_qk_norm_rope, V as projected) is rounded to fp16 and
  * stored at cache + kv_row(pos_t), kv_row(p) = (p >> kv_shift) * kv_bstride + (p & ((1 << kv_shift) - 1)) * kv_stride

@@ -65,6 +65,8 @@ SIGNATURES = {
     "gpu_moe_combine_scaled": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "gpu_geglu": (_i, [_p, _p, _p, _i, _i, _i, _i, _p, _p]),
     "gpu_softcap": (_i, [_p, _i, _f, _p]),
+    "gpu_qk_norm_rope_kv": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
+    "gpu_qk_norm_rope_kv_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_kv_store_f16": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _p]),
     "gpu_kv_store_f16_bf16": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _p]),
     "gpu_kv_store_q": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _i, _p]),

@@ -277,11 +277,23 @@ const RopeFreq& rope_freq(float freq_base, int n_rot) {
     return fr;
 }
 
-template <typename IO>
+struct KvTarget {   // where the K heads go when they are written into the KV cache instead of k_out
+    __half* cache;
+    int kv_stride, kv_shift;
+    long long kv_bstride;
+};
+
+template <typename IO, bool KVC = false>
 cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const float* k_norm, IO* q_out, IO* k_out,
                       int n_q, int n_kv, int D, int n_rot, int rot_pairs, const int* positions, int pos0, long long T,
-                      float freq_base, float eps, int gated, int qk_norm, const float* ff, cudaStream_t stream) {
+                      float freq_base, float eps, int gated, int qk_norm, const float* ff, cudaStream_t stream,
+                      KvTarget kv = KvTarget{nullptr, 0, 0, 0}) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (KVC) {
+        if (!kv.cache || n_kv <= 0 || kv.kv_shift < 0 || kv.kv_shift > 30 || kv.kv_stride < n_kv * D || kv.kv_bstride < 0)
+            return cudaErrorInvalidValue;
+        k_out = const_cast<IO*>(k);   // unused; keeps the pointer checks below uniform
+    }
     // the checks of attention_forward_opts (src/attention.cpp:139-143) that concern this step
     if (T <= 0 || n_q < 0 || n_kv < 0 || n_q + n_kv <= 0 || D <= 0 || D > 1024 || n_rot < 0 || n_rot > D ||
         n_rot % 2 != 0 || n_rot / 2 > B200_MAX_ROT_PAIRS || rot_pairs > n_rot / 2 || (!positions && pos0 < 0) ||
@@ -294,13 +306,15 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     a.n_q = n_q; a.n_kv = n_kv; a.D = D; a.q_stride = gated ? 2 * D : D;
     a.n_rot = n_rot; a.rot_pairs = rot_pairs; a.pos0 = pos0; a.do_norm = qk_norm ? 1 : 0;
     a.T = T; a.eps = eps;
+    a.k_cache = KVC ? kv.cache : nullptr; a.kv_stride = kv.kv_stride; a.kv_shift = kv.kv_shift; a.kv_bstride = kv.kv_bstride;
     const RopeFreq& fr = rope_freq(freq_base, n_rot);
 
     constexpr int VE = Io<IO>::VE;
     const int NV = D / VE;
     int ppt = 0;
     if (D % VE == 0 && n_rot % (2 * VE) == 0 && (n_q == 0 || (al16(qfull) && al16(q_out))) &&
-        (n_kv == 0 || (al16(k) && al16(k_out))) && (!q_norm || al16(q_norm)) && (!k_norm || al16(k_norm))) {
+        (n_kv == 0 || (al16(k) && al16(k_out))) && (!q_norm || al16(q_norm)) && (!k_norm || al16(k_norm)) &&
+        (!KVC || (al16(kv.cache) && kv.kv_stride % 8 == 0 && kv.kv_bstride % 8 == 0))) {
         for (int c = 1; c <= 2 && !ppt; ++c)
             if (NV % (2 * c) == 0) {
                 const int tph = NV / (2 * c);
@@ -332,11 +346,11 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
         QkArgs m = a;
         m.T = tiles * FTT;
         if (n_rot == D) {
-            const long long res = persistent_grid(k_qk_norm_rope_fast<IO, FTT, true>, block, smem);
-            k_qk_norm_rope_fast<IO, FTT, true><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(m, fr);
+            const long long res = persistent_grid(k_qk_norm_rope_fast<IO, FTT, true, KVC>, block, smem);
+            k_qk_norm_rope_fast<IO, FTT, true, KVC><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(m, fr);
         } else {
-            const long long res = persistent_grid(k_qk_norm_rope_fast<IO, FTT, false>, block, smem);
-            k_qk_norm_rope_fast<IO, FTT, false><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(m, fr);
+            const long long res = persistent_grid(k_qk_norm_rope_fast<IO, FTT, false, KVC>, block, smem);
+            k_qk_norm_rope_fast<IO, FTT, false, KVC><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(m, fr);
         }
         const cudaError_t e = launched();
         const long long rest = T - m.T;
@@ -360,8 +374,8 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     const size_t smem = 2 * 2 * (size_t)tt * (n_rot / 2 > 0 ? n_rot / 2 : 4) * sizeof(float);
 #define QK_LAUNCH(P, TTV)                                                                  \
     do {                                                                                   \
-        const long long res = persistent_grid(k_qk_norm_rope<IO, P, TTV>, block, smem);    \
-        k_qk_norm_rope<IO, P, TTV><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(a, fr); \
+        const long long res = persistent_grid(k_qk_norm_rope<IO, P, TTV, KVC>, block, smem);    \
+        k_qk_norm_rope<IO, P, TTV, KVC><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(a, fr); \
     } while (0)
     if (ppt == 1 && tt == 4) QK_LAUNCH(1, 4);
     else if (ppt == 1) QK_LAUNCH(1, 1);
@@ -1000,6 +1014,28 @@ cudaError_t gpu_qk_norm_rope_bf16(const uint16_t* qfull, const uint16_t* k, cons
                                     reinterpret_cast<__nv_bfloat16*>(q_out), reinterpret_cast<__nv_bfloat16*>(k_out),
                                     n_q, n_kv, head_dim, n_rot, rot_pairs, positions, pos0, T, freq_base, eps, gated,
                                     qk_norm, freq_factors, stream);
+}
+
+cudaError_t gpu_qk_norm_rope_kv(const float* qfull, const float* k, const float* q_norm, const float* k_norm, float* q_out,
+                                uint16_t* k_cache, int kv_stride, int kv_shift, long long kv_bstride, int n_q, int n_kv,
+                                int head_dim, int n_rot, int rot_pairs, const int* positions, int pos0, long long T,
+                                float freq_base, float eps, int gated, int qk_norm, const float* freq_factors,
+                                cudaStream_t stream) {
+    return launch_qk<float, true>(qfull, k, q_norm, k_norm, q_out, nullptr, n_q, n_kv, head_dim, n_rot, rot_pairs, positions,
+                                  pos0, T, freq_base, eps, gated, qk_norm, freq_factors, stream,
+                                  KvTarget{reinterpret_cast<__half*>(k_cache), kv_stride, kv_shift, kv_bstride});
+}
+
+cudaError_t gpu_qk_norm_rope_kv_bf16(const uint16_t* qfull, const uint16_t* k, const float* q_norm, const float* k_norm,
+                                     uint16_t* q_out, uint16_t* k_cache, int kv_stride, int kv_shift, long long kv_bstride,
+                                     int n_q, int n_kv, int head_dim, int n_rot, int rot_pairs, const int* positions,
+                                     int pos0, long long T, float freq_base, float eps, int gated, int qk_norm,
+                                     const float* freq_factors, cudaStream_t stream) {
+    return launch_qk<__nv_bfloat16, true>(reinterpret_cast<const __nv_bfloat16*>(qfull),
+                                          reinterpret_cast<const __nv_bfloat16*>(k), q_norm, k_norm,
+                                          reinterpret_cast<__nv_bfloat16*>(q_out), nullptr, n_q, n_kv, head_dim, n_rot,
+                                          rot_pairs, positions, pos0, T, freq_base, eps, gated, qk_norm, freq_factors, stream,
+                                          KvTarget{reinterpret_cast<__half*>(k_cache), kv_stride, kv_shift, kv_bstride});
 }
 
 cudaError_t gpu_kv_store_f16(const float* src, uint16_t* cache, int n_vals, const int* positions, int pos0, long long T,

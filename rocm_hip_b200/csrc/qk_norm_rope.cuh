@@ -22,6 +22,7 @@
 #define B200_QK_NORM_ROPE_CUH
 
 #include "common.cuh"
+#include "kv_store.cuh"
 
 namespace b200 {
 
@@ -46,7 +47,25 @@ struct QkArgs {
     int pos0, do_norm;
     long long T;
     float eps;
+    // KVC kernels only: the K heads go, rounded to fp16, into the block-major KV cache instead of k_out
+    // (the K write of the reference's attn_prep, src/attention.hip:286-299; row addressing :38-42)
+    __half* k_cache;
+    int kv_stride, kv_shift;
+    long long kv_bstride;
 };
+
+// VE consecutive values of token t's K row, starting at element e of the row (e a multiple of VE), into the cache
+template <int VE>
+__device__ __forceinline__ void kv_put(const QkArgs& a, long long t, int e, const float* v) {
+    const int pos = a.positions ? a.positions[t] : a.pos0 + (int)t;
+    __half* row = a.k_cache + kv_row(pos, a.kv_stride, a.kv_shift, a.kv_bstride) + e;
+    if constexpr (VE == 8) {
+        st_stream(row, Io<__half>::pack(v));
+    } else {
+        const uint2 r = make_uint2(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]));
+        asm volatile("st.global.L1::no_allocate.v2.u32 [%0], {%1,%2};" ::"l"(row), "r"(r.x), "r"(r.y) : "memory");
+    }
+}
 
 // Rotates two pairs at once: (x0, x1) -> (x0 c - x1 s, x0 s + x1 c) with every product and sum rounded separately, as
 // the CPU reference evaluates it (src/qwen_ops.cpp:21-22). The four products are two-wide multiplies; the sums are
@@ -147,7 +166,7 @@ __device__ __forceinline__ void stage_inv_freq(double* dst, const RopeFreq& fr, 
 // Dynamic shared memory: 2 passes x (cos, sin) x TT x n_rot / 2 floats (a pass writes one half while slower threads
 // may still read the other). Values travel as packed fp32 pairs (two-wide multiplies, adds and subtractions, each lane
 // rounded as the scalar instruction would).
-template <typename IO, int PPT, int TT>
+template <typename IO, int PPT, int TT, bool KVC = false>
 __global__ void __launch_bounds__(384, 2)
 k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
@@ -276,8 +295,13 @@ k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                                 upk2(hi[p][k], fhi[2 * k], fhi[2 * k + 1]);
                             }
                         }
-                        st_stream(dst + (tt * out_vec + (unsigned)vlo[p]), Io<IO>::pack(flo));
-                        st_stream(dst + (tt * out_vec + (unsigned)vhi[p]), Io<IO>::pack(fhi));
+                        if (KVC && !isq) {
+                            kv_put<VE>(a, t0 + tt, (h - a.n_q) * D + vlo[p] * VE, flo);
+                            kv_put<VE>(a, t0 + tt, (h - a.n_q) * D + vhi[p] * VE, fhi);
+                        } else {
+                            st_stream(dst + (tt * out_vec + (unsigned)vlo[p]), Io<IO>::pack(flo));
+                            st_stream(dst + (tt * out_vec + (unsigned)vhi[p]), Io<IO>::pack(fhi));
+                        }
                     }
                 }
             }
@@ -290,7 +314,7 @@ k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
 // normalisation on. FULL: n_rot == D, so every thread rotates. The gammas of q and k sit in shared memory next to the
 // tables (read with immediate offsets: no address arithmetic in the token loop).
 // Shared memory: [2 * D floats: q gamma, k gamma][2 passes x (cos, sin) x TT x n_rot / 2 floats].
-template <typename IO, int TT, bool FULL>
+template <typename IO, int TT, bool FULL, bool KVC = false>
 __global__ void __launch_bounds__(384, TT <= 2 ? 3 : 2)
 k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
@@ -388,8 +412,13 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                     upk2(hi[k], fhi[2 * k], fhi[2 * k + 1]);
                 }
             }
-            st_stream(dst + (tt * out_vec + (unsigned)vlo), Io<IO>::pack(flo));
-            st_stream(dst + (tt * out_vec + (unsigned)vhi), Io<IO>::pack(fhi));
+            if (KVC && !isq) {
+                kv_put<VE>(a, t0 + tt, (h - a.n_q) * D + vlo * VE, flo);
+                kv_put<VE>(a, t0 + tt, (h - a.n_q) * D + vhi * VE, fhi);
+            } else {
+                st_stream(dst + (tt * out_vec + (unsigned)vlo), Io<IO>::pack(flo));
+                st_stream(dst + (tt * out_vec + (unsigned)vhi), Io<IO>::pack(fhi));
+            }
         }
         if (tile + gridDim.x < ntiles) {   // the other buffer was last read one pass ago, before this pass's barrier
             float* ncos = tab + (flip ^ 1) * (2 * TT * half);
@@ -445,7 +474,12 @@ k_qk_norm_rope_generic(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                     x = d < half ? __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn))
                                  : __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
                 }
-                Io<IO>::store1(dst + d, x);
+                if (!isq && a.k_cache) {
+                    const int pos = a.positions ? a.positions[t] : a.pos0 + (int)t;
+                    a.k_cache[kv_row(pos, a.kv_stride, a.kv_shift, a.kv_bstride) + (size_t)(h - a.n_q) * D + d] = __float2half_rn(x);
+                } else {
+                    Io<IO>::store1(dst + d, x);
+                }
             }
             __syncthreads();  // v is rewritten by the next head
         }

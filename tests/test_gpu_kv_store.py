@@ -184,3 +184,49 @@ def test_rotated_quantised_rows(ops, oracle, kq, n_vals, rot):
     assert np.allclose(dots, (q.astype(np.float64) * src).sum(axis=1), rtol=1e-4, atol=1e-3)
     with pytest.raises(ops.LayerOpError):
         ops.gpu_kv_store_q(d_src, cache, n_vals, None, 0, T, kv_stride, 30, 0, kq, rot_block=96)
+
+
+@pytest.mark.parametrize("T,nq,nkv,D,n_rot,kv_shift,bf16,use_pos", [
+    (1500, 8, 2, 128, 128, 30, False, False),     # long batch: the trimmed kernel + a tail through the general one
+    (1501, 8, 2, 128, 128, 5, True, False),       # bf16, block-major cache, 1 tail token
+    (1500, 4, 2, 256, 64, 4, True, True),         # partial rotary, explicit positions
+    (37, 8, 4, 128, 128, 3, False, True),         # short batch: the general kernel
+    (9, 3, 2, 80, 40, 30, False, False),          # head size without a vector layout: the scalar kernel
+    (2000, 16, 8, 64, 64, 30, True, False)])
+def test_k_heads_straight_into_the_cache(ops, oracle, T, nq, nkv, D, n_rot, kv_shift, bf16, use_pos):
+    """gpu_qk_norm_rope_kv: q as gpu_qk_norm_rope gives it, K rows in the cache exactly as gpu_qk_norm_rope followed by
+    gpu_kv_store_f16 leaves them, every other element of the cache untouched."""
+    dt = torch.bfloat16 if bf16 else torch.float32
+    g = torch.Generator(device="cuda").manual_seed(9)
+    q = torch.randn(T, nq * D, device="cuda", generator=g).to(dt)
+    k = torch.randn(T, nkv * D, device="cuda", generator=g).to(dt)
+    qn, kn = 1 + 0.1 * torch.randn(D, device="cuda", generator=g), 1 + 0.1 * torch.randn(D, device="cuda", generator=g)
+    d_kv, layers = nkv * D, 2
+    n_ctx = 4096
+    B = 1 << min(kv_shift, 12)
+    bstride = 2 * layers * B * d_kv if kv_shift < 30 else 0
+    size = int(rows_of([n_ctx - 1], d_kv, kv_shift, bstride)[0]) + d_kv
+    pos = torch.randperm(n_ctx, device="cuda", generator=g)[:T].to(torch.int32) if use_pos else None
+    pos0 = 0 if use_pos else 1000
+    fill = torch.full((size,), -3.0, device="cuda", dtype=torch.float16)
+    c_sep, c_fused = fill.clone(), fill.clone()
+    q1, q2 = torch.empty_like(q), torch.empty_like(q)
+    # the two-launch form; for bf16 rows K is taken from the fp32 launcher on the widened inputs, because the fused
+    # form rounds K once, to fp16, not to bf16 first
+    kf = k.float()
+    k1 = torch.empty_like(kf)
+    ops.gpu_qk_norm_rope(q, k, qn, kn, q1, torch.empty_like(k), nq, nkv, D, n_rot, 0, pos, pos0, T, 1e6, 1e-6)
+    ops.gpu_qk_norm_rope(None, kf, None, kn, None, k1, 0, nkv, D, n_rot, 0, pos, pos0, T, 1e6, 1e-6)
+    ops.gpu_kv_store_f16(k1, c_sep, d_kv, pos, pos0, T, d_kv, kv_shift, bstride)
+    ops.gpu_qk_norm_rope_kv(q, k, qn, kn, q2, c_fused, d_kv, kv_shift, bstride, nq, nkv, D, n_rot, 0, pos, pos0, T, 1e6, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(q1.view(torch.int16 if bf16 else torch.int32), q2.view(torch.int16 if bf16 else torch.int32))
+    if bf16:   # (the bf16 and fp32 kernels sum a head's squares in different orders: 1/rms can differ in its last bit)
+        diff = (c_sep.view(torch.int16).int() - c_fused.view(torch.int16).int()).abs()
+        assert int(diff.max()) <= 1 and float((diff != 0).float().mean()) < 1e-3
+    else:
+        assert torch.equal(c_sep.view(torch.int16), c_fused.view(torch.int16))
+    touched = int((c_fused != -3.0).sum())
+    assert touched >= T * d_kv - 8 and int((c_fused == -3.0).sum()) >= size - T * d_kv     # only the T rows were written
+    with pytest.raises(ops.LayerOpError):
+        ops.gpu_qk_norm_rope_kv(q, k, qn, kn, q2, c_fused, d_kv - 8, kv_shift, bstride, nq, nkv, D, n_rot, 0, pos, pos0, T, 1e6, 1e-6)
