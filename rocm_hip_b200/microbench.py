@@ -107,6 +107,15 @@ def cases(T, n):
     yield "add+rmsnorm + bf16 copy (one launch)", lambda: m.gpu_add_rmsnorm(x, a, o2, w, o1, n, T, 1e-6, q8=qx), 18 * V
     yield "swiglu + bf16 copy (one launch)", lambda: m.gpu_swiglu(x, a, o1, V, q8=qx), 14 * V
     yield "rmsnorm + bf16 copy + Q8_0/Q8_K (two launches)", lambda: m.gpu_add_rmsnorm(x, None, None, w, o1, n, T, 1e-6, q8=qa), (10 + 4 + 2.53) * V
+    # q/k norm + RoPE (bf16, 40 + 8 heads of 128): 2 bytes in and out per value; with the K heads written to the cache
+    nq, nkv, D = 40, 8, 128
+    qb, kb = R(T, nq * D).bfloat16(), R(T, nkv * D).bfloat16()
+    qo, ko = torch.empty_like(qb), torch.empty_like(kb)
+    qn, kn = 1 + 0.1 * R(D), 1 + 0.1 * R(D)
+    kc = torch.zeros(T * nkv * D, device="cuda", dtype=torch.float16)
+    yield "qk_norm_rope (bf16)", lambda: m.gpu_qk_norm_rope(qb, kb, qn, kn, qo, ko, nq, nkv, D, D, 0, None, 0, T, 1e6, 1e-6), 4 * T * (nq + nkv) * D
+    yield "qk_norm_rope_kv (bf16, K into the fp16 cache)", lambda: m.gpu_qk_norm_rope_kv(qb, kb, qn, kn, qo, kc, nkv * D, 30, 0, nq, nkv, D, D, 0, None, 0, T, 1e6, 1e-6), 4 * T * (nq + nkv) * D
+    yield "qk_norm_rope + kv_store_f16 (two launches)", lambda: (m.gpu_qk_norm_rope(qb, kb, qn, kn, qo, ko, nq, nkv, D, D, 0, None, 0, T, 1e6, 1e-6), m.gpu_kv_store_f16(ko, kc, nkv * D, None, 0, T, nkv * D, 30, 0)), 4 * T * (nq + nkv) * D + 4 * T * nkv * D
     # KV rows: 1024 values per token row (8 heads x 128), 4 T rows
     nv, Tk = 1024, 4 * T
     src = R(Tk, nv)
