@@ -224,6 +224,20 @@ cudaError_t gpu_qk_norm_rope_kv_bf16(const uint16_t* qfull, const uint16_t* k, c
                                      int pos0, long long T, float freq_base, float eps, int gated, int qk_norm,
                                      const float* freq_factors, cudaStream_t stream);
 
+/* The whole first stage of the reference's attention for an FP16 cache (attn_prep, src/attention.hip:266-300, without
+ * biases, V norm and interleaved pairs): gpu_qk_norm_rope_kv for q and K, then the V rows (v [T][n_kv * head_dim]) into
+ * V; two launches on `stream`. K and V are the layer's row 0 of the two halves of the cache. */
+cudaError_t gpu_attn_prep_f16(const float* qfull, const float* k, const float* v, const float* q_norm, const float* k_norm,
+                              float* q_out, uint16_t* K, uint16_t* V, int kv_stride, int kv_shift, long long kv_bstride,
+                              int n_q, int n_kv, int head_dim, int n_rot, int rot_pairs, const int* positions, int pos0,
+                              long long T, float freq_base, float eps, int gated, int qk_norm, const float* freq_factors,
+                              cudaStream_t stream);
+cudaError_t gpu_attn_prep_f16_bf16(const uint16_t* qfull, const uint16_t* k, const uint16_t* v, const float* q_norm,
+                                   const float* k_norm, uint16_t* q_out, uint16_t* K, uint16_t* V, int kv_stride,
+                                   int kv_shift, long long kv_bstride, int n_q, int n_kv, int head_dim, int n_rot,
+                                   int rot_pairs, const int* positions, int pos0, long long T, float freq_base, float eps,
+                                   int gated, int qk_norm, const float* freq_factors, cudaStream_t stream);
+
 /* The K / V write of the reference's attn_prep kernels for an unquantised (FP16) cache (src/attention.hip:279-300):
  * row t of src [T][n_vals] (n_vals = n_kv * head_dim; K after gpu_qk_norm_rope, V as projected) is rounded to fp16 and
  * stored at cache + kv_row(pos_t), kv_row(p) = (p >> kv_shift) * kv_bstride + (p & ((1 << kv_shift) - 1)) * kv_stride

@@ -67,6 +67,8 @@ SIGNATURES = {
     "gpu_softcap": (_i, [_p, _i, _f, _p]),
     "gpu_qk_norm_rope_kv": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_qk_norm_rope_kv_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
+    "gpu_attn_prep_f16": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
+    "gpu_attn_prep_f16_bf16": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_kv_store_f16": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _p]),
     "gpu_kv_store_f16_bf16": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _p]),
     "gpu_kv_store_q": (_i, [_p, _p, _i, _p, _i, _ll, _i, _i, _ll, _i, _p]),

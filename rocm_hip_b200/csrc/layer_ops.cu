@@ -1038,6 +1038,32 @@ cudaError_t gpu_qk_norm_rope_kv_bf16(const uint16_t* qfull, const uint16_t* k, c
                                           KvTarget{reinterpret_cast<__half*>(k_cache), kv_stride, kv_shift, kv_bstride});
 }
 
+cudaError_t gpu_attn_prep_f16(const float* qfull, const float* k, const float* v, const float* q_norm, const float* k_norm,
+                              float* q_out, uint16_t* K, uint16_t* V, int kv_stride, int kv_shift, long long kv_bstride,
+                              int n_q, int n_kv, int head_dim, int n_rot, int rot_pairs, const int* positions, int pos0,
+                              long long T, float freq_base, float eps, int gated, int qk_norm, const float* freq_factors,
+                              cudaStream_t stream) {
+    const cudaError_t e = gpu_qk_norm_rope_kv(qfull, k, q_norm, k_norm, q_out, K, kv_stride, kv_shift, kv_bstride, n_q, n_kv,
+                                              head_dim, n_rot, rot_pairs, positions, pos0, T, freq_base, eps, gated, qk_norm,
+                                              freq_factors, stream);
+    if (e != cudaSuccess) return e;
+    return launch_kv_store<float>(v, reinterpret_cast<__half*>(V), n_kv * head_dim, positions, pos0, T, kv_stride, kv_shift,
+                                  kv_bstride, stream);
+}
+
+cudaError_t gpu_attn_prep_f16_bf16(const uint16_t* qfull, const uint16_t* k, const uint16_t* v, const float* q_norm,
+                                   const float* k_norm, uint16_t* q_out, uint16_t* K, uint16_t* V, int kv_stride,
+                                   int kv_shift, long long kv_bstride, int n_q, int n_kv, int head_dim, int n_rot,
+                                   int rot_pairs, const int* positions, int pos0, long long T, float freq_base, float eps,
+                                   int gated, int qk_norm, const float* freq_factors, cudaStream_t stream) {
+    const cudaError_t e = gpu_qk_norm_rope_kv_bf16(qfull, k, q_norm, k_norm, q_out, K, kv_stride, kv_shift, kv_bstride, n_q,
+                                                   n_kv, head_dim, n_rot, rot_pairs, positions, pos0, T, freq_base, eps, gated,
+                                                   qk_norm, freq_factors, stream);
+    if (e != cudaSuccess) return e;
+    return launch_kv_store<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(v), reinterpret_cast<__half*>(V),
+                                          n_kv * head_dim, positions, pos0, T, kv_stride, kv_shift, kv_bstride, stream);
+}
+
 cudaError_t gpu_kv_store_f16(const float* src, uint16_t* cache, int n_vals, const int* positions, int pos0, long long T,
                              int kv_stride, int kv_shift, long long kv_bstride, cudaStream_t stream) {
     return launch_kv_store<float>(src, reinterpret_cast<__half*>(cache), n_vals, positions, pos0, T, kv_stride, kv_shift,

@@ -230,3 +230,25 @@ def test_k_heads_straight_into_the_cache(ops, oracle, T, nq, nkv, D, n_rot, kv_s
     assert touched >= T * d_kv - 8 and int((c_fused == -3.0).sum()) >= size - T * d_kv     # only the T rows were written
     with pytest.raises(ops.LayerOpError):
         ops.gpu_qk_norm_rope_kv(q, k, qn, kn, q2, c_fused, d_kv - 8, kv_shift, bstride, nq, nkv, D, n_rot, 0, pos, pos0, T, 1e6, 1e-6)
+
+
+def test_attn_prep_f16_in_one_call(ops, oracle):
+    """gpu_attn_prep_f16 against the reference-named attn_prep semantics restated by the oracle: q out, K = fp16 of the
+    normed and rotated k, V = fp16 of v, at the rows of the positions (src/attention.hip:266-300)."""
+    T, nq, nkv, D, pos0, n_ctx = 130, 8, 2, 128, 40, 512
+    q = synth.normal(0, "ap1.q", 0, T * nq * D).reshape(T, nq * D)
+    k = synth.normal(0, "ap1.k", 0, T * nkv * D).reshape(T, nkv * D)
+    v = synth.normal(0, "ap1.v", 0, T * nkv * D).reshape(T, nkv * D)
+    qn, kn = synth.normal(0, "ap1.qn", 0, D, 1.0, 0.1), synth.normal(0, "ap1.kn", 0, D, 1.0, 0.1)
+    d_kv = nkv * D
+    K = torch.zeros(n_ctx * d_kv, device="cuda", dtype=torch.float16)
+    V = torch.zeros_like(K)
+    q_out = torch.zeros(T, nq * D, device="cuda")
+    ops.gpu_attn_prep_f16(dev(q), dev(k), dev(v), dev(qn), dev(kn), q_out, K, V, d_kv, 30, 0, nq, nkv, D, D, 0, None, pos0, T,
+                          1e6, 1e-6)
+    torch.cuda.synchronize()
+    wq, wk = oracle.qk_norm_rope(q, k, qn, kn, nq, nkv, D, D, 0, None, pos0, 1e6, 1e-6)
+    assert np.array_equal(host(q_out).view(np.uint32), wq.view(np.uint32))
+    assert np.array_equal(host(K).reshape(n_ctx, d_kv)[pos0:pos0 + T], oracle.f32_to_f16(wk).reshape(T, d_kv))
+    assert np.array_equal(host(V).reshape(n_ctx, d_kv)[pos0:pos0 + T], oracle.f32_to_f16(v).reshape(T, d_kv))
+    assert not host(K).reshape(n_ctx, d_kv)[:pos0].any() and not host(V).reshape(n_ctx, d_kv)[pos0 + T:].any()
