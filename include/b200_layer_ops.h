@@ -1,13 +1,15 @@
 /* b200_layer_ops.h -- C ABI of libb200_layer_ops.so: the fused per-token layer kernels (RMSNorm with optional
  * residual add, per-head q/k norm + NeoX RoPE, SwiGLU, Q8_0 / Q4_0 embedding gather) for NVIDIA B200 (sm_100a).
  *
- * Part 1 re-declares, with identical names, argument order and meaning, the launchers the reference engine's
- * forward pass calls (src/gpu_ops.h:16-29): a build of the reference's qwen_model.cpp that includes its own
+ * Part 1 re-declares, with identical names, argument order and meaning, the launchers of the reference engine's
+ * gpu_ops module (src/gpu_ops.h:16-125; the two its Qwen forward pass calls first, then the MoE, Gemma-4,
+ * hyper-connection / PLE / MTP and Mamba-2 ones): a build of the reference's qwen_model.cpp that includes its own
  * gpu_ops.h through the hip/ shim headers next to this file links against this library unchanged. hipError_t is
  * cudaError_t and hipStream_t is cudaStream_t there, as here.
- * Part 2 declares what the reference does elsewhere than in a launcher of its own (bf16 rows, the q/k norm + RoPE it
- * runs inside attn_prep, the embedding decode it runs in a host loop, the FP16 component kernels it launches by
- * name) and is additive.
+ * Part 2 declares what the reference does elsewhere than in a launcher of its own (bf16 rows, the q/k norm + RoPE and
+ * the KV-cache row writes it runs inside attn_prep, the embedding decode it runs in a host loop, the FP16 component
+ * kernels it launches by name) and is additive. Part 3: the same operations on host buffers, streamed through one or
+ * several GPUs. Part 4: reading a GGUF file's tensor table and uploading a tensor.
  *
  * Conventions, all from the reference (src/gpu_ops.h:1-2, src/gpu_ops.cpp:66-86): every pointer is device memory
  * owned by the caller unless a parameter says "host"; launches are asynchronous on `stream` and never synchronise;
