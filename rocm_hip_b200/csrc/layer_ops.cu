@@ -11,6 +11,7 @@
 
 #include <atomic>
 #include <cmath>
+#include <stdlib.h>
 #include <type_traits>
 
 #include "embed.cuh"
@@ -475,6 +476,22 @@ cudaError_t launch_kv_store_q(const IO* src, void* cache, int n_vals, const int*
     long long grid = (octets + 256 * U - 1) / (256 * U);
     if (grid > cap) grid = cap;
     __half* c = reinterpret_cast<__half*>(cache);
+    {   // Rotated rows and 16-bit sources take the block-per-lane kernel (measured on 262,144 x 1,024 values, fraction of
+        // the copy bandwidth, 8-per-lane -> block-per-lane: bf16 Q8_0 0.68 -> 0.99, bf16 Q4_0 0.47 -> 0.74, rotated fp32
+        // 0.52 -> 0.58 and 0.43 -> 0.57); fp32 sources without rotation stay on the 8-per-lane one (0.96 / 0.84 against
+        // 0.79 / 0.75: a lane's 128-byte run costs the fp32 loads their sector efficiency)
+        const bool ok32 = kv_stride % 8 == 0 && kv_bstride % 8 == 0 && al16(cache);
+        if (ok32 && (rot || sizeof(IO) == 2)) {
+            const long long nblk = T * (n_vals / 32), cap32 = resident_ctas(128) * 8;
+            long long g32 = (nblk + 127) / 128;
+            if (g32 > cap32) g32 = cap32;
+#define KVQ32(KQ, R) k_kv_store_q32<IO, KQ, R><<<(unsigned)g32, 128, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, rot)
+            if (kv_quant == 1) { if (rot) KVQ32(1, true); else KVQ32(1, false); }
+            else { if (rot) KVQ32(2, true); else KVQ32(2, false); }
+#undef KVQ32
+            return launched();
+        }
+    }
 #define KVQ(KQ, R) k_kv_store_q<IO, KQ, U, R><<<(unsigned)grid, 256, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, rot)
     if (kv_quant == 1) { if (rot) KVQ(1, true); else KVQ(1, false); }
     else { if (rot) KVQ(2, true); else KVQ(2, false); }
