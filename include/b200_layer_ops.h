@@ -210,6 +210,25 @@ cudaError_t gpu_qk_norm_rope_bf16(const uint16_t* qfull, const uint16_t* k, cons
                                   int rot_pairs, const int* positions, int pos0, long long T, float freq_base,
                                   float eps, int gated, int qk_norm, const float* freq_factors, cudaStream_t stream);
 
+/* The same with the cos / sin of the angles taken from tables, so that a forward pass evaluates them once and every
+ * layer's call only streams rows (the reference's FP16 component kernel takes host-built tables the same way,
+ * src/rope_embedding.hip:18-37, tests/rope_verify.cpp:73-81).
+ * gpu_rope_table fills cos_tab / sin_tab [T][n_rot / 2] fp32 (device memory, caller-owned): row t = token t at
+ * positions[t] (or pos0 + t), entry i = cos / sin of the double-precision angle pos * freq_base^(-2 i / n_rot)
+ * (/ freq_factors[i]), rounded once; pairs at or beyond rot_pairs hold (1, 0). n_rot 0: nothing to do.
+ * gpu_qk_norm_rope_tab[_bf16] is gpu_qk_norm_rope with positions, base, factors and rot_pairs replaced by the tables
+ * (NULL allowed when n_rot is 0): the same results as gpu_qk_norm_rope given the same angles. */
+cudaError_t gpu_rope_table(const int* positions, int pos0, long long T, int n_rot, int rot_pairs, float freq_base,
+                           const float* freq_factors, float* cos_tab, float* sin_tab, cudaStream_t stream);
+cudaError_t gpu_qk_norm_rope_tab(const float* qfull, const float* k, const float* q_norm, const float* k_norm,
+                                 float* q_out, float* k_out, int n_q, int n_kv, int head_dim, int n_rot,
+                                 const float* cos_tab, const float* sin_tab, long long T, float eps, int gated,
+                                 int qk_norm, cudaStream_t stream);
+cudaError_t gpu_qk_norm_rope_tab_bf16(const uint16_t* qfull, const uint16_t* k, const float* q_norm, const float* k_norm,
+                                      uint16_t* q_out, uint16_t* k_out, int n_q, int n_kv, int head_dim, int n_rot,
+                                      const float* cos_tab, const float* sin_tab, long long T, float eps, int gated,
+                                      int qk_norm, cudaStream_t stream);
+
 /* gpu_qk_norm_rope with the K write of the reference's attn_prep folded in (src/attention.hip:286-299, FP16 cache):
  * the K heads go, rounded to fp16, straight to row pos_t of k_cache (the layer's K row 0; row addressing as
  * gpu_kv_store_f16 below) instead of a k_out tensor, so K makes no extra round trip; q as in gpu_qk_norm_rope. fp32
@@ -311,7 +330,9 @@ cudaError_t gpu_embed_rows_host_ids(int type, const void* table, size_t row_byte
  * loads the library 1 MiB for the life of the process); all calls on a device share the array, so calls whose GPU work
  * may overlap race.
  * Ids are range-checked on the host first: an id outside [0, vocab) returns cudaErrorInvalidValue and queues nothing.
- * tokens_host must stay valid until its copy has run on `stream`. fp32 output, same bits as gpu_embed_rows. */
+ * tokens_host must stay valid until its copy has run on `stream`. fp32 output, same bits as gpu_embed_rows. Tables of
+ * type 8 (Q8_0) and 2 (Q4_0) only: any other type is cudaErrorInvalidValue (use gpu_embed_rows_host_ids for those).
+ * cudaErrorInvalidDeviceFunction before gpu_ops_init, like every launcher. */
 cudaError_t gpu_embed_rows_static_scratch(int type, const void* table, size_t row_bytes, int vocab,
                                           const int32_t* tokens_host, float* out, int E, long long T, float scale,
                                           cudaStream_t stream);
@@ -354,6 +375,55 @@ cudaError_t b200_host_qk_norm_rope(b200_host_ctx* ctx, int elem, const void* qfu
 cudaError_t b200_host_embed_rows(b200_host_ctx* ctx, int elem, int type, const void* table_dev, size_t row_bytes,
                                  int vocab, const int32_t* tokens, void* out, int E, long long T, float scale);
 
+/* The layer's whole op sequence in ONE call, in the order a layer of the reference's forward pass issues it around its
+ * matmuls (src/qwen_model.cpp:980-990 gather + first norm; attn_prep's q/k norm + RoPE; :946-948 residual + ffn norm;
+ * :951 SwiGLU; :955-957 residual + the next layer's norm). Every true input comes from host memory and every result
+ * goes back to it, but the residual stream x, which the reference keeps in place between these ops (s.x / s.x_alt),
+ * stays on the device between the kernels of a chunk instead of crossing the bus twice per op:
+ *   x = embed(tokens) * embd_scale;            xn_attn = RMSNorm(x) * w_attn_norm;
+ *   q_out, k_out = qk_norm_rope(qfull, k);     x' = x + attn_proj;  xn_ffn = RMSNorm(x') * w_ffn_norm;
+ *   act = SiLU(gate) * up;                     x_out = x' + ffn_proj;  xn_next = RMSNorm(x_out) * w_next_norm.
+ * Row pointers are host memory ([T] rows each), gammas host memory, table_dev device memory. Each row gets the bits
+ * the six separate calls give it. Errors as the separate calls (an out-of-range id: cudaErrorInvalidValue, nothing run). */
+typedef struct b200_layer_sweep {
+    int elem;                 /* 4 = fp32 rows, 2 = bf16 rows */
+    long long T;
+    int qtype;                /* embedding table: ggml type id, device pointer, row stride, rows */
+    const void* table_dev;
+    size_t row_bytes;
+    int vocab;
+    const int32_t* tokens;    /* [T] */
+    int E;
+    float embd_scale;         /* 1 for none */
+    const float* w_attn_norm; /* [E] each; NULL: no gamma */
+    const float* w_ffn_norm;
+    const float* w_next_norm;
+    float eps;
+    void* xn_attn;            /* out [T][E] */
+    const void* qfull;        /* in [T][n_q * (gated ? 2 : 1) * head_dim] */
+    const void* k;            /* in [T][n_kv * head_dim] */
+    void* q_out;              /* out [T][n_q * head_dim] */
+    void* k_out;              /* out [T][n_kv * head_dim] */
+    const float* q_norm;      /* [head_dim] or NULL */
+    const float* k_norm;
+    int n_q, n_kv, head_dim, n_rot, rot_pairs;
+    const int* positions;     /* [T] or NULL: pos0 + t */
+    int pos0;
+    float freq_base;
+    int gated, qk_norm;
+    const float* freq_factors;/* [n_rot / 2] or NULL */
+    const void* attn_proj;    /* in [T][E] */
+    void* xn_ffn;             /* out [T][E] */
+    const void* gate;         /* in [T][FF] */
+    const void* up;           /* in [T][FF] */
+    int FF;
+    void* act;                /* out [T][FF] */
+    const void* ffn_proj;     /* in [T][E] */
+    void* x_out;              /* out [T][E]: the residual stream after the layer */
+    void* xn_next;            /* out [T][E] */
+} b200_layer_sweep;
+cudaError_t b200_host_layer_sweep(b200_host_ctx* ctx, const b200_layer_sweep* args);
+
 /* The same over several GPUs of one box from one process: rows are cut into contiguous ranges, one per device, and
  * one host thread per device runs the single-device call on its range; nothing is exchanged between devices and a
  * row gets the bits one device would give it. n_devices <= 0: all visible devices. tables_dev: one device pointer
@@ -380,8 +450,9 @@ cudaError_t b200_host_group_embed_rows(b200_host_group* grp, int elem, int type,
 /* From a GGUF file to a device-resident table. The reference maps the file and lets kernels read weights in place
  * from unified memory (src/gguf_mmap.h:15-17; QuantWeight::row, src/inference_internal.h:33-40); here the mapping is
  * the source of one upload. A reader of the container layout only (GGUF version 2 / 3; no split files). Tensor byte
- * sizes are known for F32 (0), F16 (1), Q4_0 (2), Q8_0 (8), BF16 (30); tensors of other types are listed with
- * nbytes 0 and cannot be uploaded. b200_gguf_open returns NULL for a missing, truncated or malformed file. */
+ * sizes are known for the row formats gpu_embed_rows decodes: F32 (0), F16 (1), Q4_0 (2), Q4_1 (3), Q5_0 (6), Q5_1 (7),
+ * Q8_0 (8), Q4_K (12), Q5_K (13), Q6_K (14), BF16 (30); tensors of other types are listed with nbytes 0 and cannot be
+ * uploaded. b200_gguf_open returns NULL for a missing, truncated or malformed file. */
 typedef struct b200_gguf b200_gguf;
 b200_gguf* b200_gguf_open(const char* path);
 void b200_gguf_close(b200_gguf* g);

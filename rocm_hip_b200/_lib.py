@@ -25,6 +25,19 @@ class qmatvec_q8(C.Structure):
 
 _p, _i, _ll, _f, _sz = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_size_t
 
+
+class b200_layer_sweep(C.Structure):
+    """Layout of struct b200_layer_sweep (include/b200_layer_ops.h): host row pointers of a layer's op sequence."""
+    _fields_ = [
+        ("elem", _i), ("T", _ll), ("qtype", _i), ("table_dev", _p), ("row_bytes", _sz), ("vocab", _i), ("tokens", _p),
+        ("E", _i), ("embd_scale", _f), ("w_attn_norm", _p), ("w_ffn_norm", _p), ("w_next_norm", _p), ("eps", _f),
+        ("xn_attn", _p), ("qfull", _p), ("k", _p), ("q_out", _p), ("k_out", _p), ("q_norm", _p), ("k_norm", _p),
+        ("n_q", _i), ("n_kv", _i), ("head_dim", _i), ("n_rot", _i), ("rot_pairs", _i), ("positions", _p), ("pos0", _i),
+        ("freq_base", _f), ("gated", _i), ("qk_norm", _i), ("freq_factors", _p), ("attn_proj", _p), ("xn_ffn", _p),
+        ("gate", _p), ("up", _p), ("FF", _i), ("act", _p), ("ffn_proj", _p), ("x_out", _p), ("xn_next", _p),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/b200_layer_ops.h declares
 SIGNATURES = {
     "gpu_ops_init": (_i, [C.c_char_p]),
@@ -65,6 +78,9 @@ SIGNATURES = {
     "gpu_moe_combine_scaled": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "gpu_geglu": (_i, [_p, _p, _p, _i, _i, _i, _i, _p, _p]),
     "gpu_softcap": (_i, [_p, _i, _f, _p]),
+    "gpu_rope_table": (_i, [_p, _i, _ll, _i, _i, _f, _p, _p, _p, _p]),
+    "gpu_qk_norm_rope_tab": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _ll, _f, _i, _i, _p]),
+    "gpu_qk_norm_rope_tab_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _ll, _f, _i, _i, _p]),
     "gpu_qk_norm_rope_kv": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_qk_norm_rope_kv_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_attn_prep_f16": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
@@ -89,6 +105,7 @@ SIGNATURES = {
     "b200_host_group_destroy": (None, [_p]),
     "b200_host_group_size": (_i, [_p]),
     "b200_host_group_add_rmsnorm": (_i, [_p, _i, _p, _p, _p, _p, _p, _i, _ll, _f]),
+    "b200_host_layer_sweep": (_i, [_p, C.POINTER(b200_layer_sweep)]),
     "b200_host_group_swiglu": (_i, [_p, _i, _p, _p, _p, _ll, _i]),
     "b200_host_group_qk_norm_rope": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p]),
     "b200_host_group_embed_rows": (_i, [_p, _i, _i, _p, _sz, _i, _p, _p, _i, _ll, _f]),

@@ -32,6 +32,60 @@ __device__ __forceinline__ void st_stream(void* p, const uint4& v) {
                  : "memory");
 }
 
+// ---------------------------------------------------------------- asynchronous copies into shared memory
+//
+// Two forms. cp_async16: one 16-byte copy per thread and instruction, completion by cp.async.wait_group in the issuing
+// thread. bulk_g2s: ONE instruction copies a whole contiguous run (a 16-byte aligned source and destination, a
+// multiple of 16 bytes) through the copy engine and signals an mbarrier with the bytes written; no registers, no
+// per-thread address arithmetic. Sources are always this GPU's own memory and no copy is multicast.
+// Every wait on an mbarrier is bounded: mbar_wait gives up after a fixed number of polls and reports it, so a copy
+// that never lands cannot hang the device.
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() {
+    cp_async_commit();
+    cp_async_wait<0>();
+}
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+// makes the initialised barriers visible to the copy engine
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+// orders this thread's earlier shared-memory accesses before copy-engine writes it starts afterwards
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// One thread: arms the barrier for `bytes` and starts the copy of `bytes` from global src to shared dst
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    const unsigned b = smem_u32(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(b)
+                 : "memory");
+}
+
+// Waits until the barrier's phase of the given parity has completed; false after MBAR_POLLS unsuccessful polls
+#define MBAR_POLLS (1 << 18)
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned b = smem_u32(bar);
+    for (int i = 0; i < MBAR_POLLS; ++i) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok)
+                     : "r"(b), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 // ---------------------------------------------------------------- storage types
 
 // bf16 <-> fp32. Widening is exact; narrowing is round-to-nearest-even, the same rule as the integer formula

@@ -30,11 +30,80 @@ namespace b200 {
 
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
-// One value of a block from its byte (Q8_0) or nibble (Q4_0), times the block scale, times the embedding scale
-__device__ __forceinline__ float deq(int q, float d, float scale) {
-    float y = __fmul_rn((float)q, d);
-    if (scale != 1.0f) y = __fmul_rn(y, scale);
-    return y;
+// N (4 or 8) consecutive bytes starting at the 2-byte aligned shared-memory address p, as N / 4 little-endian words:
+// aligned 32-bit loads from the word that holds p's first byte and a funnel shift by the 0 or 16 bits p sits into
+// it (the last load may reach up to 4 bytes past p + N: the stage buffers are padded for it).
+template <int N>
+__device__ __forceinline__ void ld_bytes_2al(const uint8_t* p, uint32_t* w) {
+    const unsigned a = smem_u32(p), base = a & ~3u, sh = (a & 2u) << 3;
+    uint32_t r[N / 4 + 1];
+#pragma unroll
+    for (int i = 0; i <= N / 4; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r[i]) : "r"(base + 4 * i));
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) w[i] = __funnelshift_r(r[i], r[i + 1], sh);
+}
+
+// Bytes k and k + 1 of w, each an unsigned integer below 256, as the exact floats 2^23 + byte (the byte dropped into
+// the low mantissa bits of 0x4B000000): subtracting 2^23 + bias then gives the signed integer as a float with no
+// rounding and without the int-to-float conversion unit, whose rate (a quarter of the fp32 rate) bounded this kernel.
+__device__ __forceinline__ f2 bytes_to_magic(uint32_t w, int k) {
+    const uint32_t m = 0x4B000000u;
+    return pk2(__uint_as_float(__byte_perm(w, m, 0x7650 + k)), __uint_as_float(__byte_perm(w, m, 0x7651 + k)));
+}
+
+// Decodes the cb blocks staged at sm (block b at sm + b * BB) into o (the row's values from the chunk's first block
+// on): per step a lane takes VPL consecutive values of one block and stores them as one 16-byte vector, so a warp
+// step writes 512 contiguous bytes. Bit for bit (float)q * d (then * scale): the integer is formed exactly, the
+// products are separately rounded two-wide multiplies.
+template <typename OUT, int TYPE>
+__device__ __forceinline__ void embed_decode_chunk(const uint8_t* sm, int cb, OUT* o_chunk, float scale, int lane) {
+    constexpr int BB = TYPE == B200_QT_Q8_0 ? 34 : 18;            // bytes per block
+    constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;                 // values per lane and step: one 16-byte store
+    constexpr int LPB = 32 / VPL;                                 // lanes per block
+    constexpr int BPS = 32 / LPB;                                 // blocks per warp step
+    const int sub = lane % LPB;
+    const f2 scale2 = pk2(scale, scale);
+    for (int bs = 0; bs < cb; bs += BPS) {
+        const int b = bs + lane / LPB;
+        if (b < cb) {
+            const uint8_t* blk = sm + b * BB;
+            const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(blk));
+            const f2 d2 = pk2(d, d);
+            f2 y[VPL / 2];
+            if constexpr (TYPE == B200_QT_Q8_0) {
+                // int8 q as the unsigned byte q + 128: 2^23 + 128 + q, minus 2^23 + 128
+                const f2 off = pk2(8388736.0f, 8388736.0f);
+                uint32_t w[VPL / 4];
+                ld_bytes_2al<VPL>(blk + 2 + sub * VPL, w);
+#pragma unroll
+                for (int i = 0; i < VPL / 4; ++i) {
+                    const uint32_t x = w[i] ^ 0x80808080u;
+                    y[2 * i] = mul2(sub2(bytes_to_magic(x, 0), off), d2);
+                    y[2 * i + 1] = mul2(sub2(bytes_to_magic(x, 2), off), d2);
+                }
+            } else {
+                // values [sub * VPL, sub * VPL + VPL) of the block: the first 16 are low nibbles, the rest high;
+                // nibble - 8 from 2^23 + nibble minus 2^23 + 8
+                const f2 off = pk2(8388616.0f, 8388616.0f);
+                const int v0 = sub * VPL, byte0 = v0 & 15, shift = v0 < 16 ? 0 : 4;
+                uint32_t w[VPL / 4];
+                ld_bytes_2al<VPL>(blk + 2 + byte0, w);
+#pragma unroll
+                for (int i = 0; i < VPL / 4; ++i) {
+                    const uint32_t x = (w[i] >> shift) & 0x0F0F0F0Fu;
+                    y[2 * i] = mul2(sub2(bytes_to_magic(x, 0), off), d2);
+                    y[2 * i + 1] = mul2(sub2(bytes_to_magic(x, 2), off), d2);
+                }
+            }
+            if (scale != 1.0f) {
+#pragma unroll
+                for (int i = 0; i < VPL / 2; ++i) y[i] = mul2(y[i], scale2);
+            }
+            OUT* o = o_chunk + (size_t)b * 32 + sub * VPL;
+            if constexpr (sizeof(OUT) == 4) st_stream(o, Io2<float>::pack(y));
+            else st_stream(o, Io2<__nv_bfloat16>::pack(y));
+        }
+    }
 }
 
 template <typename OUT, int TYPE>
@@ -42,10 +111,8 @@ __global__ void __launch_bounds__(EMBED_WARPS * 32)
 k_embed_rows(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out, int E, long long T,
              float scale, int* bad_row, int vec_ok) {
     constexpr int BB = TYPE == B200_QT_Q8_0 ? 34 : 18;            // bytes per block
-    constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;                 // values per lane and step: one 16-byte store
-    constexpr int LPB = 32 / VPL;                                 // lanes per block
-    constexpr int BPS = 32 / LPB;                                 // blocks per warp step
-    __shared__ __align__(16) uint8_t stage[EMBED_WARPS][EMBED_CHUNK_BLOCKS * BB];
+    constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;                 // values per lane and 16-byte store
+    __shared__ __align__(16) uint8_t stage[EMBED_WARPS][EMBED_CHUNK_BLOCKS * BB + 16];   // (+16: see ld_bytes_2al)
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     uint8_t* sm = stage[wid];
     const int nb = E / 32;
@@ -74,39 +141,103 @@ k_embed_rows(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* t
                     *reinterpret_cast<uint16_t*>(sm + i) = *reinterpret_cast<const uint16_t*>(s + i);
             }
             __syncwarp();
-            for (int bs = 0; bs < cb; bs += BPS) {
-                const int b = bs + lane / LPB, sub = lane % LPB;
-                if (b < cb) {
-                    const uint8_t* blk = sm + b * BB;
-                    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(blk));
-                    float y[VPL];
-                    if constexpr (TYPE == B200_QT_Q8_0) {
+            embed_decode_chunk<OUT, TYPE>(sm, cb, orow + (size_t)b0 * 32, scale, lane);
+        }
+    }
+}
+
+// The same gather with the row fetch overlapped with the decode. A warp owns EMBED_BULK_SLOTS shared-memory slices of
+// about 1.4 KB each and walks its tokens' rows slice by slice: while it decodes one slice, the bulk copies
+// of the next EMBED_BULK_SLOTS - 1 (one instruction each, issued by lane 0, completion counted on the slice's mbarrier)
+// are under way, so a warp always has HBM requests in flight and never idles between "row requested" and "row arrived"
+// as the load -> decode loop of k_embed_rows does. The ids of the warp's next 64 tokens are fetched 32 at a time, one
+// per lane, so that no copy waits for an id load first. Needs a 16-byte aligned table, row_bytes % 16 == 0 and rows of
+// whole 8-block groups (E % 256 == 0: every slice is then a multiple of 16 bytes).
+// A wait that runs out of polls (never seen; it would mean a lost copy) records -1 in *bad_row and the warp stops.
+#define EMBED_BULK_WARPS 8
+#define EMBED_BULK_SLICE_BYTES 1440   // payload of a slice: 40 Q8_0 blocks (a quarter of a 5120-wide row) or 80 Q4_0 blocks
+#define EMBED_BULK_SLOTS 4
+
+template <typename OUT, int TYPE>
+__global__ void __launch_bounds__(EMBED_BULK_WARPS * 32)
+k_embed_rows_bulk(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out, int E, long long T,
+                  float scale, int* bad_row) {
+    constexpr int BB = TYPE == B200_QT_Q8_0 ? 34 : 18;
+    constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;
+    constexpr int NS = EMBED_BULK_SLOTS;
+    constexpr int SB = EMBED_BULK_SLICE_BYTES / BB / 8 * 8;   // blocks per slice, a multiple of 8
+    constexpr int SLOT = SB * BB + 16;                        // a multiple of 16 (+16: see ld_bytes_2al)
+    __shared__ __align__(128) uint8_t stage[EMBED_BULK_WARPS][NS][SLOT];
+    __shared__ __align__(8) unsigned long long bar[EMBED_BULK_WARPS][NS];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int nb = E / 32, nchunks = (nb + SB - 1) / SB;
+    const long long warp0 = (long long)blockIdx.x * EMBED_BULK_WARPS + wid, nwarps = (long long)gridDim.x * EMBED_BULK_WARPS;
+    if (lane < NS) mbar_init(&bar[wid][lane], 1);
+    if (lane == 0) mbar_fence_init();
+    __syncwarp();
+    if (warp0 >= T) return;
+    const long long ntok = (T - warp0 + nwarps - 1) / nwarps;   // this warp's tokens: warp0 + k * nwarps, k < ntok
+    // ids of tokens k in [kb, kb + 32) (cur) and [kb + 32, kb + 64) (nxt), lane j holding the j-th
+    long long kb = 0;
+    auto load_ids = [&](long long k0) { return k0 + lane < ntok ? __ldg(tokens + warp0 + (k0 + lane) * nwarps) : 0; };
+    int cur = load_ids(0), nxt = load_ids(32);
+    auto id_of = [&](long long k) {   // every lane calls it with the same k in [kb, kb + 64)
+        const int a = __shfl_sync(0xffffffffu, cur, (int)(k - kb) & 31), b = __shfl_sync(0xffffffffu, nxt, (int)(k - kb) & 31);
+        return k - kb < 32 ? a : b;
+    };
+    auto start_copy = [&](int tok, int c, int slot) {   // lane 0 only, tok in range
+        const int b0 = c * SB, cb = min(SB, nb - b0);
+        fence_async_smem();
+        bulk_g2s(stage[wid][slot], table + (size_t)tok * row_bytes + (size_t)b0 * BB, (unsigned)(cb * BB), &bar[wid][slot]);
+    };
+    // issue cursor (ik, ic, islot): the next slice to request; it runs NS - 1 slices ahead of the decode cursor
+    long long ik = 0;
+    int ic = 0, islot = 0;
+    auto issue_one = [&]() {   // all lanes (the id comes by shuffle); no-op past the end
+        if (ik >= ntok) return;
+        const int tok = id_of(ik);
+        if (lane == 0 && tok >= 0 && tok < vocab) start_copy(tok, ic, islot);
+        islot = islot + 1 == NS ? 0 : islot + 1;
+        if (++ic == nchunks) { ic = 0; ++ik; }
+    };
 #pragma unroll
-                        for (int k = 0; k < VPL; k += 2) {
-                            const uint16_t two = *reinterpret_cast<const uint16_t*>(blk + 2 + sub * VPL + k);
-                            y[k] = deq((int)(int8_t)(two & 0xff), d, scale);
-                            y[k + 1] = deq((int)(int8_t)(two >> 8), d, scale);
-                        }
-                    } else {
-                        // values [sub * VPL, sub * VPL + VPL) of the block: the first 16 are low nibbles, the rest high
-                        const int v0 = sub * VPL, byte0 = v0 & 15, shift = v0 < 16 ? 0 : 4;
-#pragma unroll
-                        for (int k = 0; k < VPL; k += 2) {
-                            const uint16_t two = *reinterpret_cast<const uint16_t*>(blk + 2 + byte0 + k);
-                            y[k] = deq((int)(((two & 0xff) >> shift) & 15) - 8, d, scale);
-                            y[k + 1] = deq((int)(((two >> 8) >> shift) & 15) - 8, d, scale);
-                        }
-                    }
-                    OUT* o = orow + (size_t)(b0 + b) * 32 + sub * VPL;
-                    if constexpr (sizeof(OUT) == 4) {
-                        st_stream(o, make_uint4(__float_as_uint(y[0]), __float_as_uint(y[1]), __float_as_uint(y[2]),
-                                                __float_as_uint(y[3])));
-                    } else {
-                        st_stream(o, make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]),
-                                                pack_bf16(y[6], y[7])));
-                    }
-                }
+    for (int i = 0; i < NS - 1; ++i) issue_one();
+    unsigned phases = 0u;   // bit s: the parity slice s is waited for next
+    int slot = 0;
+    for (long long k = 0; k < ntok; ++k) {
+        if (k - kb >= 32) {   // the decode cursor leaves the first id batch (the issue cursor is at most a few tokens ahead)
+            kb += 32;
+            cur = nxt;
+            nxt = load_ids(kb + 32);
+        }
+        const long long t = warp0 + k * nwarps;
+        const int tok = id_of(k);
+        const bool valid = tok >= 0 && tok < vocab;
+        OUT* orow = out + (size_t)t * E;
+        if (!valid) {
+            if (lane == 0) atomicMin(bad_row, (int)(t < 0x7fffffff ? t : 0x7ffffffe));
+            for (int c = lane * VPL; c < E; c += 32 * VPL) st_stream(orow + c, make_uint4(0, 0, 0, 0));
+        }
+        for (int c = 0; c < nchunks; ++c) {
+            // the slice decoded in the previous iteration (a __syncwarp ago) is free: request the slice NS - 1 ahead into it
+            issue_one();
+            const int s_now = slot;
+            slot = slot + 1 == NS ? 0 : slot + 1;
+            if (!valid) continue;
+            const int b0 = c * SB, cb = min(SB, nb - b0);
+            // lane 0 polls; the others learn the outcome by shuffle (a warp-wide poll multiplies the shared-memory traffic)
+            int arrived = lane == 0 ? (int)mbar_wait(&bar[wid][s_now], (phases >> s_now) & 1u) : 0;
+            arrived = __shfl_sync(0xffffffffu, arrived, 0);
+            if (!arrived) {
+                if (lane == 0) atomicMin(bad_row, -1);
+                // (the other slices' copies, if in flight, get the same bounded wait before the slices go away)
+                for (int o = 0; o < NS; ++o)
+                    if (o != s_now) (void)mbar_wait(&bar[wid][o], (phases >> o) & 1u);
+                return;
             }
+            phases ^= 1u << s_now;
+            embed_decode_chunk<OUT, TYPE>(stage[wid][s_now], cb, orow + (size_t)b0 * 32, scale, lane);
+            __syncwarp();   // every lane has read the slice
         }
     }
 }

@@ -20,6 +20,7 @@
 #include <mutex>
 
 #include "embed.cuh"
+#include "internal.h"
 
 using namespace b200;
 
@@ -66,7 +67,7 @@ cudaError_t launch(const uint8_t* table, size_t row_bytes, int vocab, const int3
     const long long need = (T + EMBED_WARPS - 1) / EMBED_WARPS, resident = (long long)(per_sm > 0 ? per_sm : 1) * sms;
     k_embed_rows<float, TYPE><<<(unsigned)(need < resident ? need : resident), EMBED_WARPS * 32, 0, stream>>>(
         table, row_bytes, vocab, ids_dev, out, E, T, scale, flag_dev, vec_ok);
-    return cudaGetLastError();
+    return launched();
 }
 
 }  // namespace
@@ -74,6 +75,9 @@ cudaError_t launch(const uint8_t* table, size_t row_bytes, int vocab, const int3
 extern "C" cudaError_t gpu_embed_rows_static_scratch(int type, const void* table, size_t row_bytes, int vocab,
                                                      const int32_t* tokens_host, float* out, int E, long long T,
                                                      float scale, cudaStream_t stream) {
+    if (!lib_ready()) return cudaErrorInvalidDeviceFunction;   // before gpu_ops_init, as every launcher
+    // Q8_0 and Q4_0 tables only (the formats the gather is built and measured for; the other row formats go through
+    // gpu_embed_rows_host_ids with caller-owned scratch)
     const size_t bb = type == B200_QT_Q8_0 ? 34 : type == B200_QT_Q4_0 ? 18 : 0;
     if (!bb || !table || !tokens_host || !out || T <= 0 || E <= 0 || E % 32 != 0 || vocab <= 0 ||
         row_bytes < (size_t)(E / 32) * bb || row_bytes % 2 != 0 || (reinterpret_cast<uintptr_t>(table) & 1u) ||

@@ -153,7 +153,7 @@ b200_gguf* b200_gguf_open(const char* path) {
         e.key = r.str();
         e.type = r.get<uint32_t>();
         e.value_off = r.at;
-        if (r.ok && e.key == "general.alignment" && e.type == 4) {
+        if (r.ok && e.key == "general.alignment" && e.type == 4 && r.need(4)) {   // (a file may end right after the type)
             uint32_t a;
             memcpy(&a, g->map + r.at, 4);
             if (a >= 1 && a <= (1u << 20) && (a & (a - 1)) == 0) g->alignment = a;
@@ -174,8 +174,17 @@ b200_gguf* b200_gguf_open(const char* path) {
         t.offset = r.get<uint64_t>();
         int blck = 0, bytes = 0;
         if (r.ok && type_layout(t.type, &blck, &bytes) && t.ne[0] % blck == 0) {
-            t.row_bytes = (size_t)(t.ne[0] / blck) * bytes;
-            t.nbytes = t.row_bytes * (size_t)t.ne[1] * (size_t)t.ne[2] * (size_t)t.ne[3];
+            // the extents come from the file: a product that wraps would pass the inside-the-file check below with a
+            // small nbytes while ne[] still reports the huge extents, so every step is checked and a wrap fails the open
+            size_t rb = 0, nb = 0;
+            if (__builtin_mul_overflow((size_t)(t.ne[0] / blck), (size_t)bytes, &rb) ||
+                __builtin_mul_overflow(rb, (size_t)t.ne[1], &nb) || __builtin_mul_overflow(nb, (size_t)t.ne[2], &nb) ||
+                __builtin_mul_overflow(nb, (size_t)t.ne[3], &nb)) {
+                r.ok = false;
+                break;
+            }
+            t.row_bytes = rb;
+            t.nbytes = nb;
         }
         if (r.ok) g->tensors.push_back(std::move(t));
     }

@@ -17,13 +17,14 @@ struct b200_host_ctx {
     std::vector<char*> slots;
     std::vector<cudaStream_t> streams;
     char* consts = nullptr;  // gammas, frequency factors, the bad-id flag
+    cudaEvent_t consts_ready = nullptr;   // recorded after a call's constants were queued; every slot stream waits on it
 };
 
 namespace {
 
 constexpr size_t kConstBytes = 1u << 20;
 constexpr size_t kAlign = 256;
-constexpr int kMaxBufs = 4;
+constexpr int kMaxBufs = 12;
 
 inline size_t up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 
@@ -34,8 +35,11 @@ struct RowBufs {
     void* out[kMaxBufs];
     size_t out_bpr[kMaxBufs];
     int n_out = 0;
-    void add_in(const void* p, size_t bpr) { in[n_in] = p; in_bpr[n_in++] = bpr; }
-    void add_out(void* p, size_t bpr) { out[n_out] = p; out_bpr[n_out++] = bpr; }
+    size_t tmp_bpr[kMaxBufs];   // rows that only live on the device between two kernels of a chunk
+    int n_tmp = 0;
+    int add_in(const void* p, size_t bpr) { in[n_in] = p; in_bpr[n_in] = bpr; return n_in++; }
+    int add_out(void* p, size_t bpr) { out[n_out] = p; out_bpr[n_out] = bpr; return n_out++; }
+    int add_tmp(size_t bpr) { tmp_bpr[n_tmp] = bpr; return n_tmp++; }
 };
 
 struct DeviceGuard {
@@ -48,13 +52,24 @@ struct DeviceGuard {
     ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
 };
 
-// launch(dev_in, dev_out, rows, row0, stream) -> cudaError_t
+// launch(dev_in, dev_out, rows, row0, stream[, dev_tmp]) -> cudaError_t
+template <class F>
+auto call_launch(F& launch, void** din, void** dout, void** dtmp, long long rows, long long row0, cudaStream_t st, int)
+    -> decltype(launch(din, dout, rows, row0, st, dtmp)) {
+    return launch(din, dout, rows, row0, st, dtmp);
+}
+template <class F>
+cudaError_t call_launch(F& launch, void** din, void** dout, void**, long long rows, long long row0, cudaStream_t st, long) {
+    return launch(din, dout, rows, row0, st);
+}
+
 template <class F>
 cudaError_t run_rows(b200_host_ctx* ctx, long long T, const RowBufs& io, F launch) {
     size_t per_row = 0;
     for (int i = 0; i < io.n_in; ++i) per_row += io.in_bpr[i];
     for (int i = 0; i < io.n_out; ++i) per_row += io.out_bpr[i];
-    const size_t slack = kAlign * (size_t)(io.n_in + io.n_out);
+    for (int i = 0; i < io.n_tmp; ++i) per_row += io.tmp_bpr[i];
+    const size_t slack = kAlign * (size_t)(io.n_in + io.n_out + io.n_tmp);
     if (per_row == 0 || ctx->slot_bytes <= slack || (ctx->slot_bytes - slack) / per_row == 0) return cudaErrorInvalidValue;
     long long chunk = (long long)((ctx->slot_bytes - slack) / per_row);
     // at least two chunks per slot when the work allows, so the ring actually overlaps
@@ -69,13 +84,16 @@ cudaError_t run_rows(b200_host_ctx* ctx, long long T, const RowBufs& io, F launc
         char* base = ctx->slots[s];
         void* din[kMaxBufs];
         void* dout[kMaxBufs];
+        void* dtmp[kMaxBufs];
         size_t off = 0;
         for (int i = 0; i < io.n_in; ++i) { din[i] = base + off; off += up((size_t)chunk * io.in_bpr[i]); }
         for (int i = 0; i < io.n_out; ++i) { dout[i] = base + off; off += up((size_t)chunk * io.out_bpr[i]); }
+        for (int i = 0; i < io.n_tmp; ++i) { dtmp[i] = base + off; off += up((size_t)chunk * io.tmp_bpr[i]); }
+        if (c < (long long)ctx->slots.size() && ctx->consts_ready) err = cudaStreamWaitEvent(st, ctx->consts_ready, 0);
         for (int i = 0; i < io.n_in && err == cudaSuccess; ++i)
             err = cudaMemcpyAsync(din[i], (const char*)io.in[i] + (size_t)row0 * io.in_bpr[i], (size_t)rows * io.in_bpr[i],
                                   cudaMemcpyHostToDevice, st);
-        if (err == cudaSuccess) err = launch(din, dout, rows, row0, st);
+        if (err == cudaSuccess) err = call_launch(launch, din, dout, dtmp, rows, row0, st, 0);
         for (int i = 0; i < io.n_out && err == cudaSuccess; ++i)
             err = cudaMemcpyAsync((char*)io.out[i] + (size_t)row0 * io.out_bpr[i], dout[i], (size_t)rows * io.out_bpr[i],
                                   cudaMemcpyDeviceToHost, st);
@@ -87,7 +105,9 @@ cudaError_t run_rows(b200_host_ctx* ctx, long long T, const RowBufs& io, F launc
     return err;
 }
 
-// Copies small read-only arrays (gammas and the like) to the context's constant area before the chunks start
+// Copies small read-only arrays (gammas and the like) to the context's constant area before the chunks start: queued
+// on the first slot's stream; done() records the event every slot stream waits on before its first chunk (the slot
+// streams are non-blocking streams, which nothing else orders against these copies).
 struct ConstArea {
     b200_host_ctx* ctx;
     size_t off = 0;
@@ -100,9 +120,13 @@ struct ConstArea {
         if (off + up(bytes) > kConstBytes) { err = cudaErrorInvalidValue; return nullptr; }
         char* d = ctx->consts + off;
         off += up(bytes);
-        const cudaError_t e = cudaMemcpy(d, host, bytes, cudaMemcpyHostToDevice);
+        const cudaError_t e = cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, ctx->streams[0]);
         if (err == cudaSuccess) err = e;
         return reinterpret_cast<const T*>(d);
+    }
+    cudaError_t done() {
+        if (err == cudaSuccess) err = cudaEventRecord(ctx->consts_ready, ctx->streams[0]);
+        return err;
     }
 };
 
@@ -125,6 +149,7 @@ b200_host_ctx* b200_host_ctx_create(size_t slot_bytes, int n_slots) {
         ok = ok && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
         if (ok) ctx->streams.push_back(st);
     }
+    ok = ok && cudaEventCreateWithFlags(&ctx->consts_ready, cudaEventDisableTiming) == cudaSuccess;
     if (!ok) {
         (void)cudaGetLastError();
         b200_host_ctx_destroy(ctx);
@@ -138,6 +163,7 @@ void b200_host_ctx_destroy(b200_host_ctx* ctx) {
     DeviceGuard g(ctx->device);
     for (cudaStream_t st : ctx->streams) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
     for (char* p : ctx->slots) cudaFree(p);
+    if (ctx->consts_ready) cudaEventDestroy(ctx->consts_ready);
     if (ctx->consts) cudaFree(ctx->consts);
     delete ctx;
 }
@@ -149,7 +175,7 @@ cudaError_t b200_host_add_rmsnorm(b200_host_ctx* ctx, int elem, const void* x_in
     DeviceGuard g(ctx->device);
     ConstArea ca(ctx);
     const float* dw = ca.put(w, (size_t)n);
-    if (ca.err != cudaSuccess) return ca.err;
+    if (ca.done() != cudaSuccess) return ca.err;
     const size_t bpr = (size_t)n * elem;
     RowBufs io;
     io.add_in(x_in, bpr);
@@ -194,7 +220,7 @@ cudaError_t b200_host_qk_norm_rope(b200_host_ctx* ctx, int elem, const void* qfu
     const float* dqn = ca.put(q_norm, (size_t)head_dim);
     const float* dkn = ca.put(k_norm, (size_t)head_dim);
     const float* dff = ca.put(freq_factors, (size_t)(n_rot / 2));
-    if (ca.err != cudaSuccess) return ca.err;
+    if (ca.done() != cudaSuccess) return ca.err;
     const size_t qs = (size_t)(gated ? 2 * head_dim : head_dim);
     RowBufs io;
     int iq = -1, ik = -1, ip = -1, oq = -1, ok = -1;
@@ -227,7 +253,7 @@ cudaError_t b200_host_embed_rows(b200_host_ctx* ctx, int elem, int type, const v
     const int int_max = 0x7fffffff;
     ConstArea ca(ctx);
     int* flag = const_cast<int*>(ca.put(&int_max, 1));
-    if (ca.err != cudaSuccess) return ca.err;
+    if (ca.done() != cudaSuccess) return ca.err;
     RowBufs io;
     io.add_in(tokens, sizeof(int32_t));
     io.add_out(out, (size_t)E * elem);
@@ -237,6 +263,79 @@ cudaError_t b200_host_embed_rows(b200_host_ctx* ctx, int elem, int type, const v
                                   scale, flag, st);
         return gpu_embed_rows_bf16(type, table_dev, row_bytes, vocab, (const int32_t*)din[0], (uint16_t*)dout[0], E, rows,
                                    scale, flag, st);
+    });
+}
+
+cudaError_t b200_host_layer_sweep(b200_host_ctx* ctx, const b200_layer_sweep* a) {
+    if (!ctx || !a || (a->elem != 2 && a->elem != 4) || a->T <= 0 || a->E <= 0 || a->FF <= 0 || a->vocab <= 0 ||
+        !a->table_dev || !a->tokens || !a->xn_attn || !a->attn_proj || !a->xn_ffn || !a->gate || !a->up || !a->act ||
+        !a->ffn_proj || !a->x_out || !a->xn_next || a->n_q < 0 || a->n_kv < 0 || a->head_dim <= 0 || a->n_rot < 0 ||
+        a->n_rot > a->head_dim || (a->n_q > 0 && (!a->qfull || !a->q_out)) || (a->n_kv > 0 && (!a->k || !a->k_out)))
+        return cudaErrorInvalidValue;
+    for (long long t = 0; t < a->T; ++t)  // the reference's range check, before any decode (src/qwen_model.cpp:981)
+        if (a->tokens[t] < 0 || a->tokens[t] >= a->vocab) return cudaErrorInvalidValue;
+    DeviceGuard dg(ctx->device);
+    const b200_layer_sweep s = *a;
+    const int elem = s.elem, E = s.E, D = s.head_dim;
+    const int int_max = 0x7fffffff;
+    ConstArea ca(ctx);
+    int* flag = const_cast<int*>(ca.put(&int_max, 1));
+    const float* w1 = ca.put(s.w_attn_norm, (size_t)E);
+    const float* w2 = ca.put(s.w_ffn_norm, (size_t)E);
+    const float* w3 = ca.put(s.w_next_norm, (size_t)E);
+    const float* dqn = ca.put(s.q_norm, (size_t)D);
+    const float* dkn = ca.put(s.k_norm, (size_t)D);
+    const float* dff = ca.put(s.freq_factors, (size_t)(s.n_rot / 2));
+    if (ca.done() != cudaSuccess) return ca.err;
+    const size_t row = (size_t)E * elem, qs = (size_t)(s.gated ? 2 * D : D);
+    RowBufs io;
+    const int i_tok = io.add_in(s.tokens, sizeof(int32_t));
+    const int i_q = s.n_q > 0 ? io.add_in(s.qfull, (size_t)s.n_q * qs * elem) : -1;
+    const int i_k = s.n_kv > 0 ? io.add_in(s.k, (size_t)s.n_kv * D * elem) : -1;
+    const int i_pos = s.positions ? io.add_in(s.positions, sizeof(int)) : -1;
+    const int i_p1 = io.add_in(s.attn_proj, row), i_g = io.add_in(s.gate, (size_t)s.FF * elem),
+              i_u = io.add_in(s.up, (size_t)s.FF * elem), i_p2 = io.add_in(s.ffn_proj, row);
+    const int o_xn1 = io.add_out(s.xn_attn, row);
+    const int o_q = s.n_q > 0 ? io.add_out(s.q_out, (size_t)s.n_q * D * elem) : -1;
+    const int o_k = s.n_kv > 0 ? io.add_out(s.k_out, (size_t)s.n_kv * D * elem) : -1;
+    const int o_xn2 = io.add_out(s.xn_ffn, row), o_act = io.add_out(s.act, (size_t)s.FF * elem),
+              o_x = io.add_out(s.x_out, row), o_xn3 = io.add_out(s.xn_next, row);
+    const int t_x = io.add_tmp(row), t_alt = io.add_tmp(row);   // the residual stream between the kernels of a chunk
+    return run_rows(ctx, s.T, io, [=](void** din, void** dout, long long rows, long long row0, cudaStream_t st, void** tmp) {
+        const int* dp = i_pos >= 0 ? (const int*)din[i_pos] : nullptr;
+        const int p0 = dp ? 0 : s.pos0 + (int)row0;
+        cudaError_t e;
+        if (elem == 4) {
+            typedef float V;
+            e = gpu_embed_rows(s.qtype, s.table_dev, s.row_bytes, s.vocab, (const int32_t*)din[i_tok], (V*)tmp[t_x], E, rows,
+                               s.embd_scale, flag, st);
+            if (e == cudaSuccess) e = gpu_add_rmsnorm_f32((const V*)tmp[t_x], nullptr, nullptr, w1, (V*)dout[o_xn1], E, rows, s.eps, st);
+            if (e == cudaSuccess)
+                e = gpu_qk_norm_rope(i_q >= 0 ? (const V*)din[i_q] : nullptr, i_k >= 0 ? (const V*)din[i_k] : nullptr, dqn, dkn,
+                                     o_q >= 0 ? (V*)dout[o_q] : nullptr, o_k >= 0 ? (V*)dout[o_k] : nullptr, s.n_q, s.n_kv, D,
+                                     s.n_rot, s.rot_pairs, dp, p0, rows, s.freq_base, s.eps, s.gated, s.qk_norm, dff, st);
+            if (e == cudaSuccess)
+                e = gpu_add_rmsnorm_f32((const V*)tmp[t_x], (const V*)din[i_p1], (V*)tmp[t_alt], w2, (V*)dout[o_xn2], E, rows, s.eps, st);
+            if (e == cudaSuccess) e = gpu_swiglu_f32((const V*)din[i_g], (const V*)din[i_u], (V*)dout[o_act], rows * s.FF, st);
+            if (e == cudaSuccess)
+                e = gpu_add_rmsnorm_f32((const V*)tmp[t_alt], (const V*)din[i_p2], (V*)dout[o_x], w3, (V*)dout[o_xn3], E, rows, s.eps, st);
+        } else {
+            typedef uint16_t V;
+            e = gpu_embed_rows_bf16(s.qtype, s.table_dev, s.row_bytes, s.vocab, (const int32_t*)din[i_tok], (V*)tmp[t_x], E,
+                                    rows, s.embd_scale, flag, st);
+            if (e == cudaSuccess) e = gpu_add_rmsnorm_bf16((const V*)tmp[t_x], nullptr, nullptr, w1, (V*)dout[o_xn1], E, rows, s.eps, st);
+            if (e == cudaSuccess)
+                e = gpu_qk_norm_rope_bf16(i_q >= 0 ? (const V*)din[i_q] : nullptr, i_k >= 0 ? (const V*)din[i_k] : nullptr, dqn,
+                                          dkn, o_q >= 0 ? (V*)dout[o_q] : nullptr, o_k >= 0 ? (V*)dout[o_k] : nullptr, s.n_q,
+                                          s.n_kv, D, s.n_rot, s.rot_pairs, dp, p0, rows, s.freq_base, s.eps, s.gated,
+                                          s.qk_norm, dff, st);
+            if (e == cudaSuccess)
+                e = gpu_add_rmsnorm_bf16((const V*)tmp[t_x], (const V*)din[i_p1], (V*)tmp[t_alt], w2, (V*)dout[o_xn2], E, rows, s.eps, st);
+            if (e == cudaSuccess) e = gpu_swiglu_bf16((const V*)din[i_g], (const V*)din[i_u], (V*)dout[o_act], rows * s.FF, st);
+            if (e == cudaSuccess)
+                e = gpu_add_rmsnorm_bf16((const V*)tmp[t_alt], (const V*)din[i_p2], (V*)dout[o_x], w3, (V*)dout[o_xn3], E, rows, s.eps, st);
+        }
+        return e;
     });
 }
 

@@ -11,10 +11,12 @@
 
 #include <atomic>
 #include <cmath>
+#include <mutex>
 #include <stdlib.h>
 #include <type_traits>
 
 #include "embed.cuh"
+#include "internal.h"
 #include "kv_store.cuh"
 #include "moe_group.cuh"
 #include "moe_router.cuh"
@@ -34,26 +36,38 @@ namespace {
 std::atomic<bool> g_ready{false};
 std::atomic<unsigned long long> g_launches{0};
 
+}  // namespace
+
+namespace b200 {
+
+bool lib_ready() { return g_ready.load(std::memory_order_acquire); }
+
+cudaError_t launched() {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError();
+}
+
+}  // namespace b200
+
+namespace {
+
+// SM count of the current device, cached per device (atomics: launchers run on any thread)
 int sm_count() {
-    static int cached[64];
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int next_pow2(int v) { int p = 1; while (p < v) p <<= 1; return p; }
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-inline cudaError_t launched() {
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    return cudaGetLastError();
-}
 
 // Resident CTAs of `block` threads a B200 SM holds when only the thread count limits it
 inline long long resident_ctas(int block) { return (long long)sm_count() * (2048 / block > 0 ? 2048 / block : 1); }
@@ -124,12 +138,14 @@ cudaError_t launch_norm_vec(const NormPlan& p, const IO* x_in, const IO* add, IO
     return launched();
 }
 
-// xh (fp32 rows): the 16-bit side copy of y, written by the producer itself when the row shape takes the trimmed
-// kernel; *xh_done says whether it was (else the caller runs the side kernel).
+// side (fp32 rows): the activation side outputs of y (src/q8_device.h:54-104). Where the row shape takes the trimmed
+// kernel, the kernel writes them itself from the registers that hold y: the 16-bit copy when side->xh is set (8-byte
+// aligned), the int8 formats when side->qK is set (n % 256 == 0, q0 / qK 4-byte aligned). *xh_done / *q8_done say
+// what was written; the caller runs the side kernel over y for the rest.
 template <typename IO, typename WT>
 cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int n, long long T,
-                               float eps, cudaStream_t stream, uint16_t* xh = nullptr, int xh_bf16 = 0,
-                               bool* xh_done = nullptr) {
+                               float eps, cudaStream_t stream, const Q8Side* side = nullptr, bool* xh_done = nullptr,
+                               bool* q8_done = nullptr) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (T <= 0 || n <= 0 || !x_in || !y || (add && (!x_out || x_out == x_in))) return cudaErrorInvalidValue;
     constexpr int VE = Io<IO>::VE;
@@ -139,32 +155,38 @@ cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const W
     if constexpr (std::is_same<WT, float>::value && !std::is_same<IO, __half>::value) {
         // exact fit of whole warps with gammas: the trimmed kernel
         if (vec && p.cta_row && w && p.tpr <= 512 && (n / VE) == p.tpr * p.vpt && (p.vpt == 2 || p.vpt == 4)) {
-#define NORM_FAST2(V, A, M)                                                                    \
-    do {                                                                                       \
-        long long grid = persistent_grid(k_add_rmsnorm_fast<IO, V, A, M>, p.tpr, 0);           \
-        if (grid > T) grid = T;                                                                \
-        k_add_rmsnorm_fast<IO, V, A, M><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps); \
+#define NORM_FAST3(V, A, M, XHV, Q8V, SIDE)                                                          \
+    do {                                                                                             \
+        long long grid = persistent_grid(k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V>, p.tpr, 0);       \
+        if (grid > T) grid = T;                                                                      \
+        k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, SIDE); \
     } while (0)
-#define NORM_FAST(V, A) do { if (p.tpr <= 160) NORM_FAST2(V, A, 160); else NORM_FAST2(V, A, 512); } while (0)
+#define NORM_FAST2(V, A, XHV, Q8V, SIDE)                                                             \
+    do {                                                                                             \
+        if (p.tpr <= 160) NORM_FAST3(V, A, 160, XHV, Q8V, SIDE);                                     \
+        else if (p.tpr <= 320) NORM_FAST3(V, A, 320, XHV, Q8V, SIDE);                                \
+        else NORM_FAST3(V, A, 512, XHV, Q8V, SIDE);                                                  \
+    } while (0)
+#define NORM_FAST(XHV, Q8V, SIDE)                                                                    \
+    do {                                                                                             \
+        if (p.vpt == 4) { if (add) NORM_FAST2(4, true, XHV, Q8V, SIDE); else NORM_FAST2(4, false, XHV, Q8V, SIDE); } \
+        else { if (add) NORM_FAST2(2, true, XHV, Q8V, SIDE); else NORM_FAST2(2, false, XHV, Q8V, SIDE); }            \
+    } while (0)
             if constexpr (std::is_same<IO, float>::value) {
-                if (xh && (reinterpret_cast<uintptr_t>(xh) & 7) == 0) {
-#define NORM_XH2(V, A, M)                                                                             \
-    do {                                                                                              \
-        long long grid = persistent_grid(k_add_rmsnorm_fast<IO, V, A, M, true>, p.tpr, 0);            \
-        if (grid > T) grid = T;                                                                       \
-        k_add_rmsnorm_fast<IO, V, A, M, true><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, xh, xh_bf16); \
-    } while (0)
-#define NORM_XH(V, A) do { if (p.tpr <= 160) NORM_XH2(V, A, 160); else NORM_XH2(V, A, 512); } while (0)
-                    if (p.vpt == 4) { if (add) NORM_XH(4, true); else NORM_XH(4, false); }
-                    else { if (add) NORM_XH(2, true); else NORM_XH(2, false); }
-#undef NORM_XH2
-#undef NORM_XH
-                    if (xh_done) *xh_done = true;
+                const bool do_xh = side && side->xh && (reinterpret_cast<uintptr_t>(side->xh) & 7) == 0;
+                const bool do_q8 = side && side->qK && n % 256 == 0 && n <= 8192 &&
+                                   ((reinterpret_cast<uintptr_t>(side->q0) | reinterpret_cast<uintptr_t>(side->qK)) & 3) == 0;
+                if (do_xh || do_q8) {
+                    if (do_xh && do_q8) NORM_FAST(true, true, *side);
+                    else if (do_q8) NORM_FAST(false, true, *side);
+                    else NORM_FAST(true, false, *side);
+                    if (xh_done) *xh_done = do_xh;
+                    if (q8_done) *q8_done = do_q8;
                     return launched();
                 }
             }
-            if (p.vpt == 4) { if (add) NORM_FAST(4, true); else NORM_FAST(4, false); }
-            else { if (add) NORM_FAST(2, true); else NORM_FAST(2, false); }
+            NORM_FAST(false, false, Q8Side{});
+#undef NORM_FAST3
 #undef NORM_FAST2
 #undef NORM_FAST
             return launched();
@@ -182,9 +204,13 @@ cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const W
     }
 }
 
+inline Q8Side side_of(const qmatvec_q8* q8) {
+    return Q8Side{q8->q0, q8->d0, q8->qK, q8->dK, q8->bsK, q8->s0, q8->xh, q8->xh_bf16};
+}
+
 cudaError_t launch_q8_side(const float* x, long long K, const qmatvec_q8* q8, cudaStream_t stream) {
     if (!q8->qK && !q8->xh) return cudaSuccess;  // nothing wanted (src/q8_device.h:35)
-    Q8Side o = {q8->q0, q8->d0, q8->qK, q8->dK, q8->bsK, q8->s0, q8->xh, q8->xh_bf16};
+    Q8Side o = side_of(q8);
     const long long nblk = (K + 255) / 256, cap = resident_ctas(256) * 8;
     long long grid = (nblk + 7) / 8;   // a warp per block, 8 warps per CTA
     if (grid > cap) grid = cap;
@@ -196,9 +222,10 @@ cudaError_t launch_q8_side(const float* x, long long K, const qmatvec_q8* q8, cu
 
 // ---------------------------------------------------------------- SwiGLU
 
+// side (fp32): as for launch_add_rmsnorm. The int8 formats are fused when n % 32 == 0 and q0 / qK are 4-byte aligned.
 template <typename IO, bool FAST>
-cudaError_t launch_swiglu(const IO* g, const IO* u, IO* out, long long n, cudaStream_t stream, uint16_t* xh = nullptr,
-                          int xh_bf16 = 0, bool* xh_done = nullptr) {
+cudaError_t launch_swiglu(const IO* g, const IO* u, IO* out, long long n, cudaStream_t stream, const Q8Side* side = nullptr,
+                          bool* xh_done = nullptr, bool* q8_done = nullptr) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (n < 0 || (n > 0 && (!g || !u || !out))) return cudaErrorInvalidValue;
     if (n == 0) return cudaSuccess;
@@ -210,8 +237,18 @@ cudaError_t launch_swiglu(const IO* g, const IO* u, IO* out, long long n, cudaSt
         if (grid > cap) grid = cap;
         if (grid < 1) grid = 1;
         if constexpr (std::is_same<IO, float>::value) {
-            if (xh && n % VE == 0 && (reinterpret_cast<uintptr_t>(xh) & 7) == 0) {
-                k_swiglu<IO, FAST, UNROLL, true><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n, xh, xh_bf16);
+            const bool do_xh = side && side->xh && n % VE == 0 && (reinterpret_cast<uintptr_t>(side->xh) & 7) == 0;
+            const bool do_q8 = side && side->qK && n % 32 == 0 &&
+                               ((reinterpret_cast<uintptr_t>(side->q0) | reinterpret_cast<uintptr_t>(side->qK)) & 3) == 0;
+            if (do_q8) {
+                if (do_xh) k_swiglu_q8<UNROLL, true><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n, *side);
+                else k_swiglu_q8<UNROLL, false><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n, *side);
+                if (xh_done) *xh_done = do_xh;
+                if (q8_done) *q8_done = true;
+                return launched();
+            }
+            if (do_xh) {
+                k_swiglu<IO, FAST, UNROLL, true><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n, side->xh, side->xh_bf16);
                 if (xh_done) *xh_done = true;
                 return launched();
             }
@@ -248,12 +285,14 @@ cudaError_t launch_swiglu_rows(const IO* gate, const IO* up, IO* out, long long 
 // Stand-in for a missing gamma in the vector kernel (multiplying by 1.0f leaves every bit alone)
 __device__ float g_ones[1024];
 bool g_ones_ready[64];
+std::mutex g_ones_lock;   // first use on a device may come from several threads at once
 
 const float* ones_vector() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     float* p = nullptr;
     if (cudaGetSymbolAddress((void**)&p, g_ones) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> hold(g_ones_lock);
     if (!g_ones_ready[dev]) {
         float h[1024];
         for (int i = 0; i < 1024; ++i) h[i] = 1.0f;
@@ -284,12 +323,42 @@ struct KvTarget {   // where the K heads go when they are written into the KV ca
     long long kv_bstride;
 };
 
+// Tables of a call whose cos / sin were computed beforehand (gpu_rope_table): [T][n_rot / 2] fp32 each
+struct RopeTables {
+    const float* cos_tab;
+    const float* sin_tab;
+};
+
+cudaError_t launch_rope_table(const int* positions, int pos0, long long T, int n_rot, int rot_pairs, float freq_base,
+                              const float* ff, float* cos_out, float* sin_out, cudaStream_t stream) {
+    if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (T <= 0 || n_rot < 0 || n_rot % 2 != 0 || n_rot / 2 > B200_MAX_ROT_PAIRS || rot_pairs > n_rot / 2 ||
+        (!positions && pos0 < 0) || (n_rot > 0 && (!cos_out || !sin_out)))
+        return cudaErrorInvalidValue;
+    if (n_rot == 0) return cudaSuccess;   // no rotation: no table
+    const int half = n_rot / 2;
+    if (rot_pairs <= 0) rot_pairs = half;
+    const RopeFreq& fr = rope_freq(freq_base, n_rot);
+    const bool fast = !ff && freq_base >= 1.0f;   // every angle below 2^31: the range of the kernel's own sincos
+    const bool vec = half % 4 == 0 && al16(cos_out) && al16(sin_out);
+    const int tpp = 256 / (half / (vec ? 4 : 1));
+    long long grid = (T + tpp - 1) / tpp;
+    const long long cap = resident_ctas(256) * 4;
+    if (grid > cap) grid = cap;
+#define ROPE_TAB(F, P) k_rope_table<F, P><<<(unsigned)grid, 256, 0, stream>>>(positions, pos0, T, half, rot_pairs, ff, cos_out, sin_out, fr)
+    if (fast) { if (vec) ROPE_TAB(true, 4); else ROPE_TAB(true, 1); }
+    else { if (vec) ROPE_TAB(false, 4); else ROPE_TAB(false, 1); }
+#undef ROPE_TAB
+    return launched();
+}
+
 template <typename IO, bool KVC = false>
 cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const float* k_norm, IO* q_out, IO* k_out,
                       int n_q, int n_kv, int D, int n_rot, int rot_pairs, const int* positions, int pos0, long long T,
                       float freq_base, float eps, int gated, int qk_norm, const float* ff, cudaStream_t stream,
-                      KvTarget kv = KvTarget{nullptr, 0, 0, 0}) {
+                      KvTarget kv = KvTarget{nullptr, 0, 0, 0}, const RopeTables* tabs = nullptr) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
+    if (tabs && n_rot > 0 && (!tabs->cos_tab || !tabs->sin_tab)) return cudaErrorInvalidValue;
     if (KVC) {
         if (!kv.cache || n_kv <= 0 || kv.kv_shift < 0 || kv.kv_shift > 30 || kv.kv_stride < n_kv * D || kv.kv_bstride < 0)
             return cudaErrorInvalidValue;
@@ -308,7 +377,11 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     a.n_rot = n_rot; a.rot_pairs = rot_pairs; a.pos0 = pos0; a.do_norm = qk_norm ? 1 : 0;
     a.T = T; a.eps = eps;
     a.k_cache = KVC ? kv.cache : nullptr; a.kv_stride = kv.kv_stride; a.kv_shift = kv.kv_shift; a.kv_bstride = kv.kv_bstride;
-    const RopeFreq& fr = rope_freq(freq_base, n_rot);
+    const bool tab = tabs && n_rot > 0;
+    a.cos_tab = tab ? tabs->cos_tab : nullptr;
+    a.sin_tab = tab ? tabs->sin_tab : nullptr;
+    static const RopeFreq no_freq = {};   // the kernels that read tables take no multipliers
+    const RopeFreq& fr = tab ? no_freq : rope_freq(freq_base, n_rot);
 
     constexpr int VE = Io<IO>::VE;
     const int NV = D / VE;
@@ -340,13 +413,34 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
     // through the general kernel below (a row's bits do not depend on which of the two processed it).
     constexpr int FTT = 4;
     // (no frequency factors and a base >= 1: every angle is then below 2^31, the range of the kernel's own sincos)
-    if (ppt == 1 && qk_norm && !ff && freq_base >= 1.0f && (n_q + n_kv) * tph == block && block <= 384 && T >= 8LL * sm_count() && n_rot > 0 &&
+    const bool trig_ok = tab ? (al16(a.cos_tab) && al16(a.sin_tab)) : (!ff && freq_base >= 1.0f);
+    if (ppt == 1 && qk_norm && trig_ok && (n_q + n_kv) * tph == block && block <= 384 && T >= 8LL * sm_count() && n_rot > 0 &&
         (n_rot / 2) % 4 == 0) {
         const long long tiles = T / FTT;
         const size_t smem = (2 * (size_t)D + 2 * 2 * FTT * (size_t)(n_rot / 2)) * sizeof(float);
         QkArgs m = a;
         m.T = tiles * FTT;
-        if (n_rot == D) {
+        bool done = false;
+        if constexpr (!KVC) {
+            if (tab) {
+#define QK_TAB(TTV, FULLV, MINB, DSV, NRV)                                                                            \
+    do {                                                                                                              \
+        const long long tl = T / TTV;                                                                                 \
+        const size_t sm = (2 * (size_t)D + 2 * 2 * TTV * (size_t)(n_rot / 2)) * sizeof(float);                        \
+        m.T = tl * TTV;                                                                                               \
+        const long long res = persistent_grid(k_qk_norm_rope_fast<IO, TTV, FULLV, false, true, MINB, DSV, NRV>, block, sm); \
+        k_qk_norm_rope_fast<IO, TTV, FULLV, false, true, MINB, DSV, NRV><<<(unsigned)(tl < res ? tl : res), block, sm, stream>>>(m, fr); \
+    } while (0)
+                if (D == 128 && n_rot == 128) QK_TAB(4, true, 2, 128, 128);         // the heads of the dense configurations
+                else if (D == 256 && n_rot == 64) QK_TAB(4, false, 2, 256, 64);    // partial rotary over the first 64 of 256
+                else if (n_rot == D) QK_TAB(4, true, 2, 0, 0);
+                else QK_TAB(4, false, 2, 0, 0);
+#undef QK_TAB
+                done = true;
+            }
+        }
+        if (done) {
+        } else if (n_rot == D) {
             const long long res = persistent_grid(k_qk_norm_rope_fast<IO, FTT, true, KVC>, block, smem);
             k_qk_norm_rope_fast<IO, FTT, true, KVC><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(m, fr);
         } else {
@@ -364,6 +458,7 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
         a.k_out = n_kv ? static_cast<IO*>(a.k_out) + m.T * kin : nullptr;
         if (a.positions) a.positions += m.T;
         else a.pos0 += (int)m.T;
+        if (tab) { a.cos_tab += m.T * (size_t)(n_rot / 2); a.sin_tab += m.T * (size_t)(n_rot / 2); }
         a.T = rest;
         T = rest;
     }
@@ -418,6 +513,26 @@ cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int voca
         K<OUT, TY><<<(unsigned)(need < res ? need : res), EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, \
                                                                                          E, T, scale, bad_row, vec_ok);     \
     } while (0)
+    // Q8_0 / Q4_0 rows the copy engine can fetch whole (16-byte aligned table and row stride, rows of whole 8-block
+    // groups): the kernel that keeps two rows in flight per warp
+    // Q8_0 / Q4_0 rows the copy engine can fetch whole (16-byte aligned table and row stride, rows of whole 8-block
+    // groups) in a batch that gives a resident warp fewer than 8 tokens: the kernel that keeps several slices of a row
+    // in flight per warp (measured on Q4_0 rows of 2560 at 16,384 tokens: 0.84-0.93 of the copy bandwidth against 0.70).
+    // Longer batches take the load -> decode kernel, whose many warps per SM overlap each other's phases (262,144 rows
+    // of 5120: 0.91-0.93 against 0.86-0.88).
+    if ((type == B200_QT_Q8_0 || type == B200_QT_Q4_0) && vec_ok && E % 256 == 0 &&
+        T < 8LL * EMBED_WARPS * resident_ctas(EMBED_WARPS * 32) * 5 / 8) {
+        const long long need_b = (T + EMBED_BULK_WARPS - 1) / EMBED_BULK_WARPS;
+#define EMBED_BULK(TY)                                                                                           \
+    do {                                                                                                         \
+        const long long res = persistent_grid(k_embed_rows_bulk<OUT, TY>, EMBED_BULK_WARPS * 32, 0);             \
+        k_embed_rows_bulk<OUT, TY><<<(unsigned)(need_b < res ? need_b : res), EMBED_BULK_WARPS * 32, 0, stream>>>( \
+            tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row);                                             \
+    } while (0)
+        if (type == B200_QT_Q8_0) EMBED_BULK(B200_QT_Q8_0); else EMBED_BULK(B200_QT_Q4_0);
+#undef EMBED_BULK
+        return launched();
+    }
     switch (type) {
         case B200_QT_Q8_0: EMBED(k_embed_rows, B200_QT_Q8_0); break;
         case B200_QT_Q4_0: EMBED(k_embed_rows, B200_QT_Q4_0); break;
@@ -656,26 +771,31 @@ cudaError_t gpu_add_rmsnorm(const float* x_in, const float* add, float* x_out, c
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (T <= 0 || (q8 && (n % 256 != 0 || (long long)n * T > q8->max_k)) || (add && x_out == x_in))
         return cudaErrorInvalidValue;
-    // the 16-bit copy is written by the norm kernel itself where the row shape allows; what is left (the int8
-    // formats, or the copy for the other shapes) is one more pass over y
-    bool xh_done = false;
-    const cudaError_t e = launch_add_rmsnorm<float, float>(x_in, add, x_out, w, y, n, T, eps, stream,
-                                                           q8 ? (uint16_t*)q8->xh : nullptr, q8 ? q8->xh_bf16 : 0, &xh_done);
+    // the side outputs are written by the norm kernel itself where the row shape allows (one launch); for the other
+    // shapes, what is left is one more pass over y
+    bool xh_done = false, q8_done = false;
+    Q8Side side = {};
+    if (q8) side = side_of(q8);
+    const cudaError_t e = launch_add_rmsnorm<float, float>(x_in, add, x_out, w, y, n, T, eps, stream, q8 ? &side : nullptr,
+                                                           &xh_done, &q8_done);
     if (e != cudaSuccess || !q8) return e;
     qmatvec_q8 rest = *q8;
     if (xh_done) rest.xh = nullptr;
+    if (q8_done) rest.qK = nullptr;
     return launch_q8_side(y, (long long)n * T, &rest, stream);
 }
 
 cudaError_t gpu_swiglu(const float* g, const float* u, float* out, int n, const qmatvec_q8* q8, cudaStream_t stream) {
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (q8 && (n % 32 != 0 || n > q8->max_k)) return cudaErrorInvalidValue;
-    bool xh_done = false;
-    const cudaError_t e = launch_swiglu<float, false>(g, u, out, n, stream, q8 ? (uint16_t*)q8->xh : nullptr,
-                                                      q8 ? q8->xh_bf16 : 0, &xh_done);
+    bool xh_done = false, q8_done = false;
+    Q8Side side = {};
+    if (q8) side = side_of(q8);
+    const cudaError_t e = launch_swiglu<float, false>(g, u, out, n, stream, q8 ? &side : nullptr, &xh_done, &q8_done);
     if (e != cudaSuccess || !q8 || n <= 0) return e;
     qmatvec_q8 rest = *q8;
     if (xh_done) rest.xh = nullptr;
+    if (q8_done) rest.qK = nullptr;
     return launch_q8_side(out, n, &rest, stream);
 }
 
@@ -1031,6 +1151,32 @@ cudaError_t gpu_qk_norm_rope_bf16(const uint16_t* qfull, const uint16_t* k, cons
                                     reinterpret_cast<__nv_bfloat16*>(q_out), reinterpret_cast<__nv_bfloat16*>(k_out),
                                     n_q, n_kv, head_dim, n_rot, rot_pairs, positions, pos0, T, freq_base, eps, gated,
                                     qk_norm, freq_factors, stream);
+}
+
+cudaError_t gpu_rope_table(const int* positions, int pos0, long long T, int n_rot, int rot_pairs, float freq_base,
+                           const float* freq_factors, float* cos_tab, float* sin_tab, cudaStream_t stream) {
+    return launch_rope_table(positions, pos0, T, n_rot, rot_pairs, freq_base, freq_factors, cos_tab, sin_tab, stream);
+}
+
+cudaError_t gpu_qk_norm_rope_tab(const float* qfull, const float* k, const float* q_norm, const float* k_norm,
+                                 float* q_out, float* k_out, int n_q, int n_kv, int head_dim, int n_rot,
+                                 const float* cos_tab, const float* sin_tab, long long T, float eps, int gated,
+                                 int qk_norm, cudaStream_t stream) {
+    const RopeTables tabs = {cos_tab, sin_tab};
+    return launch_qk<float>(qfull, k, q_norm, k_norm, q_out, k_out, n_q, n_kv, head_dim, n_rot, 0, nullptr, 0, T, 1.0f, eps,
+                            gated, qk_norm, nullptr, stream, KvTarget{nullptr, 0, 0, 0}, &tabs);
+}
+
+cudaError_t gpu_qk_norm_rope_tab_bf16(const uint16_t* qfull, const uint16_t* k, const float* q_norm, const float* k_norm,
+                                      uint16_t* q_out, uint16_t* k_out, int n_q, int n_kv, int head_dim, int n_rot,
+                                      const float* cos_tab, const float* sin_tab, long long T, float eps, int gated,
+                                      int qk_norm, cudaStream_t stream) {
+    const RopeTables tabs = {cos_tab, sin_tab};
+    return launch_qk<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(qfull),
+                                    reinterpret_cast<const __nv_bfloat16*>(k), q_norm, k_norm,
+                                    reinterpret_cast<__nv_bfloat16*>(q_out), reinterpret_cast<__nv_bfloat16*>(k_out),
+                                    n_q, n_kv, head_dim, n_rot, 0, nullptr, 0, T, 1.0f, eps, gated, qk_norm, nullptr, stream,
+                                    KvTarget{nullptr, 0, 0, 0}, &tabs);
 }
 
 cudaError_t gpu_qk_norm_rope_kv(const float* qfull, const float* k, const float* q_norm, const float* k_norm, float* q_out,

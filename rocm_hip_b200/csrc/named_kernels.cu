@@ -7,7 +7,8 @@
 //   "rmsnorm"           grid n_tokens, block 32                 src/layernorm.hip:15-45, launched at tests/layernorm_verify.cpp:96
 //   "rope_rotate_half"  grid n_rows, block 32                   src/rope_embedding.hip:18-37, tests/rope_verify.cpp:113
 // The by-value struct of side-output pointers has the layout of the reference's Q8Out (src/q8_device.h:22-31).
-// The module's other twenty names (moe_router ... softcap, src/gpu_ops.cpp:29-48) follow in named_gpu_ops_rest.cuh.
+// The reference's gpu_ops module holds twenty more names (moe_router ... softcap, src/gpu_ops.cpp:29-48) for model
+// families outside this library's path; this image does not provide them.
 // These are compatibility kernels in the reference's launch shapes (which re-read rows or use one warp per row); the
 // library's own launchers (layer_ops.cu) use better-shaped kernels with the same arithmetic: double-precision sums
 // of squares, 1/rms as the CPU reference forms it, products rounded separately. Built into gpu_ops.fatbin.
@@ -119,4 +120,3 @@ extern "C" __global__ void rope_rotate_half(const __half* x, const float* ctab, 
     }
 }
 
-#include "named_gpu_ops_rest.cuh"

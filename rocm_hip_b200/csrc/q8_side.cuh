@@ -90,6 +90,123 @@ __device__ __forceinline__ void q8_block_value(float v, bool active, long long b
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same outputs written by a producer whose threads hold NV finished 16-byte vectors of 4 fp32 values each, the 32
+// lanes of a warp holding 32 consecutive vectors per slot (the row kernels of rmsnorm.cuh, the tiles of swiglu.cuh): a
+// Q8_0 block is 8 neighbouring lanes of a slot, a Q8_K block two neighbouring groups of 32 lanes. Built for the fewest
+// instructions per value (the producers are bound by instruction issue once this is added):
+//   * maxima are taken of the |x| bit patterns (they order like the values): one 32-bit shuffle and one integer
+//     maximum per step, the Q8_0 block's maximum falling out after three steps, the warp's after five;
+//   * which value holds a Q8_K block's maximum (lowest index on ties) and its sign is found without a second
+//     reduction: the few lanes that hold the warp's maximum post index << 1 | sign with a shared-memory atomicMin;
+//   * the IEEE divisions of the rules (127 / amax, amax / 127, -127 / max, 1 / iscale) are batched: a division costs
+//     the warp its ~20 instructions whether one lane or all need it, so lane j (and NV + j) of a group divides for
+//     slot j and the quotients travel by shuffle: 3 division sequences per thread instead of 4 per vector.
+//     (Warp-reduce instructions, redux.sync, were measured 1.7x slower than the shuffle steps they replace.)
+// q8v_phase_a writes the Q8_0 part and leaves, per slot, the maximum |x| bits of the warp's 128 values and the
+// candidate code of the lowest index that has it in the slot's shared-memory cell; after a barrier the caller
+// combines the cells of a block's two halves (q8v_combine) and q8v_phase_b writes the Q8_K part.
+// Same rules and bits as q8_block_value and k_q8_side. NV <= 4.
+
+struct Q8Half { unsigned am, cand; };
+
+__device__ __forceinline__ Q8Half q8v_combine(Q8Half first, Q8Half second) {   // halves in index order
+    Q8Half r;
+    r.am = first.am > second.am ? first.am : second.am;
+    r.cand = first.am > second.am ? first.cand : (second.am > first.am ? second.cand : min(first.cand, second.cand));
+    return r;
+}
+
+// y[j]: slot j's 4 values, elements i[j] .. i[j] + 3 of the flattened vector (i[j] a multiple of 4; the warp's lanes
+// hold i0 + 4 * lane; 32-bit: the reference's launchers bound the vector by an int, src/gpu_ops.cpp:70,82). live[j] false: the vector lies past the end (the 8 lanes of a Q8_0 block are live or dead
+// together); its values count as zeros and nothing is stored for it. cell[j]: the warp's shared-memory cell of slot j.
+template <int NV>
+__device__ __forceinline__ void q8v_phase_a(const float (&y)[NV][4], const unsigned (&i)[NV], const bool (&live)[NV],
+                                            const Q8Side& o, Q8Half* const (&cell)[NV]) {
+    static_assert(NV <= 4, "lanes j and NV + j of an 8-lane group divide for slot j");
+    const int lane = threadIdx.x & 31, r = lane & 7;
+    unsigned am8[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        unsigned ab[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ab[e] = live[j] ? (__float_as_uint(y[j][e]) & 0x7fffffffu) : 0u;
+        unsigned t = max(max(ab[0], ab[1]), max(ab[2], ab[3]));
+        t = max(t, __shfl_xor_sync(0xffffffffu, t, 1));
+        t = max(t, __shfl_xor_sync(0xffffffffu, t, 2));
+        t = max(t, __shfl_xor_sync(0xffffffffu, t, 4));
+        am8[j] = t;
+        t = max(t, __shfl_xor_sync(0xffffffffu, t, 8));
+        t = max(t, __shfl_xor_sync(0xffffffffu, t, 16));
+        if (lane == 0) { cell[j]->am = t; cell[j]->cand = 0xffffffffu; }
+        __syncwarp();
+        const unsigned in_blk = i[j] & 255u;
+        unsigned c = 0xffffffffu;
+#pragma unroll
+        for (int e = 3; e >= 0; --e)
+            if (ab[e] == t) c = ((in_blk + e) << 1) | (__float_as_uint(y[j][e]) >> 31);
+        if (live[j] && c != 0xffffffffu) atomicMin(&cell[j]->cand, c);
+    }
+    // lane j of a group: 127 / amax of slot j; lane NV + j: amax / 127 (both 0 when amax is 0)
+    float am = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (r == j || r == NV + j) am = __uint_as_float(am8[j]);
+    const bool is_id = r < NV;
+    const float quot = (r < 2 * NV && am != 0.0f) ? __fdiv_rn(is_id ? 127.0f : am, is_id ? am : 127.0f) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const float id0 = __shfl_sync(0xffffffffu, quot, (lane & 24) + j);
+        int q[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) q[e] = live[j] ? __float2int_rn(__fmul_rn(y[j][e], id0)) : 0;
+        int sum0 = (q[0] + q[1]) + (q[2] + q[3]);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 4);
+        if (live[j]) {
+            *reinterpret_cast<uint32_t*>(o.q0 + i[j]) =
+                __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+            if (r == NV + j) {   // this lane holds amax / 127 of the block
+                o.d0[i[j] >> 5] = __half2float(__float2half_rn(quot));
+                o.s0[i[j] >> 5] = __float_as_int(__half2float(__float2half_rn(__fmul_rn(quot, (float)sum0))));
+            }
+        }
+    }
+}
+
+// blk[j]: the combined halves of slot j's block. first_half[j]: this warp holds the block's first 128 values.
+template <int NV>
+__device__ __forceinline__ void q8v_phase_b(const float (&y)[NV][4], const unsigned (&i)[NV], const bool (&live)[NV],
+                                            const Q8Side& o, const Q8Half (&blk)[NV], const bool (&first_half)[NV]) {
+    const int lane = threadIdx.x & 31;
+    // lane j: -127 / (the signed value of largest magnitude of slot j's block), then 1 / that
+    unsigned ab = 0u, sg = 0u;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (lane == j) { ab = blk[j].am; sg = blk[j].cand & 1u; }
+    const bool on = lane < NV && ab != 0u;
+    const float isc = on ? __fdiv_rn(-127.0f, __uint_as_float(ab | (sg << 31))) : 0.0f;
+    const float dk = on ? __fdiv_rn(1.0f, isc) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const float iscale = __shfl_sync(0xffffffffu, isc, j);
+        int q[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            q[e] = (live[j] && blk[j].am != 0u) ? min(127, __float2int_rn(__fmul_rn(iscale, y[j][e]))) : 0;
+        int s16 = (q[0] + q[1]) + (q[2] + q[3]);
+        s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
+        s16 += __shfl_xor_sync(0xffffffffu, s16, 2);
+        if (live[j]) {
+            *reinterpret_cast<uint32_t*>(o.qK + i[j]) =
+                __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+            if ((lane & 3) == 0) o.bsK[i[j] >> 4] = s16;
+            if (lane == j && first_half[j]) o.dK[i[j] >> 8] = dk;
+        }
+    }
+}
+
 // The same outputs for a finished vector in memory, at memory speed: one warp per 256-value block, a lane owns 8
 // consecutive values (two 16-byte loads; its int8 results are one 8-byte store per format, its 16-bit copy one 16-byte
 // store), a Q8_0 block is four neighbouring lanes, a Q8_K block the warp, so every reduction is a shuffle. Same rules

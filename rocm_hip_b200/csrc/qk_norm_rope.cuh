@@ -52,6 +52,10 @@ struct QkArgs {
     __half* k_cache;
     int kv_stride, kv_shift;
     long long kv_bstride;
+    // cos / sin of every token's angles computed beforehand (k_rope_table): [T][n_rot / 2] fp32 each, row t = token t,
+    // (1, 0) in the pairs that do not rotate. NULL: the kernel evaluates them itself.
+    const float* cos_tab;
+    const float* sin_tab;
 };
 
 // VE consecutive values of token t's K row, starting at element e of the row (e a multiple of VE), into the cache
@@ -73,6 +77,11 @@ __device__ __forceinline__ void kv_put(const QkArgs& a, long long t, int e, cons
 // multiply-add even when both carry .rn (measured: 26 % of results differ in the last bit), which it never does to
 // the scalar forms.
 __device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, float* hi) {
+#ifdef B200_ROT_WIDE
+    upk2(sub2(mul2(x0, c), mul2(x1, s)), lo[0], lo[1]);
+    upk2(add2(mul2(x0, s), mul2(x1, c)), hi[0], hi[1]);
+    return;
+#endif
     float a0, a1, b0, b1, c0, c1, d0, d1;
     upk2(mul2(x0, c), a0, a1);
     upk2(mul2(x1, s), b0, b1);
@@ -133,7 +142,10 @@ __device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const
     for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
         const int tt = idx / half, i = idx - tt * half;
         float c = 1.0f, s = 0.0f;
-        if (i < a.rot_pairs) {
+        if (!FAST_TRIG && a.cos_tab) {   // uniform: the tables were computed beforehand
+            c = __ldg(a.cos_tab + (size_t)(t0 + tt) * half + i);
+            s = __ldg(a.sin_tab + (size_t)(t0 + tt) * half + i);
+        } else if (i < a.rot_pairs) {
             const int pos = a.positions ? a.positions[t0 + tt] : a.pos0 + (int)(t0 + tt);
             double theta = (double)pos * inv_freq[i];
             if (a.ff) theta /= (double)a.ff[i];
@@ -150,6 +162,23 @@ __device__ __forceinline__ void tokens_cos_sin(float* cos_t, float* sin_t, const
         }
         cos_t[at] = c;
         sin_t[at] = s;
+    }
+}
+
+// The cos / sin rows of `nt` consecutive tokens starting at t0, from the tables in global memory into the
+// chunk-major shared-memory layout of tokens_cos_sin (chunk c of lane l at ((c * chunk_lanes + l) * 4) within the
+// token's row), as 16-byte asynchronous copies spread over the CTA. n_rot / 2 a multiple of 4, tables 16-byte aligned.
+__device__ __forceinline__ void tile_tables_async(float* cos_t, float* sin_t, const QkArgs& a, long long t0, int nt,
+                                                  int chunk_lanes, int ve, int half) {
+    const int cpr = half >> 2, C = ve >> 2;   // chunks per token row, chunks per lane
+    const float* gc = a.cos_tab + (size_t)t0 * half;
+    const float* gs = a.sin_tab + (size_t)t0 * half;
+    for (int idx = threadIdx.x; idx < 2 * nt * cpr; idx += blockDim.x) {
+        const int which = idx >= nt * cpr, r = idx - which * nt * cpr;
+        const int tt = r / cpr, ch = r - tt * cpr;
+        const int l = ch / C, c = ch - l * C;
+        const int at = tt * half + ((c * chunk_lanes + l) << 2);
+        cp_async16((which ? sin_t : cos_t) + at, (which ? gs : gc) + (size_t)r * 4);
     }
 }
 
@@ -314,15 +343,25 @@ k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
 // normalisation on. FULL: n_rot == D, so every thread rotates. The gammas of q and k sit in shared memory next to the
 // tables (read with immediate offsets: no address arithmetic in the token loop).
 // Shared memory: [2 * D floats: q gamma, k gamma][2 passes x (cos, sin) x TT x n_rot / 2 floats].
-template <typename IO, int TT, bool FULL, bool KVC = false>
-__global__ void __launch_bounds__(384, TT <= 2 ? 3 : 2)
+//
+// TAB: the cos / sin of every token come from tables in global memory (a.cos_tab, a.sin_tab: k_rope_table fills them
+// once per forward pass and every layer's call reads them). A tile's 2 * TT * n_rot / 2 floats are fetched into the
+// same shared-memory layout with 16-byte cp.async copies issued one pass ahead, so no trigonometry and no double
+// arithmetic beyond the sum of squares remains in the streaming kernel: it fits 3 to 5 CTAs per SM where the kernel
+// that evaluates sin / cos itself fits 2. MINB: resident CTAs the register budget is held to.
+// DS / NR: head size and rotary width fixed at compile time (0: taken from the arguments), which turns every
+// shared-memory offset of the token loop into an immediate.
+template <typename IO, int TT, bool FULL, bool KVC = false, bool TAB = false, int MINB = (TT <= 2 ? 3 : 2), int DS = 0,
+          int NR = 0>
+__global__ void __launch_bounds__(384, MINB)
 k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
     extern __shared__ __align__(16) float smem_all[];
-    __shared__ double invf[B200_MAX_ROT_PAIRS];
-    stage_inv_freq(invf, fr, a.n_rot >> 1);
-    const int D = a.D, NV = D / VE, tph = NV / 2;
-    const int R = a.n_rot / VE, P = R / 2, half = a.n_rot >> 1;
+    __shared__ double invf[TAB ? 1 : B200_MAX_ROT_PAIRS];
+    const int n_rot = NR ? NR : a.n_rot;
+    if (!TAB) stage_inv_freq(invf, fr, n_rot >> 1);
+    const int D = DS ? DS : a.D, NV = D / VE, tph = NV / 2;
+    const int R = n_rot / VE, P = R / 2, half = n_rot >> 1;
     const int l = threadIdx.x % tph, h = threadIdx.x / tph;
     const bool isq = h < a.n_q;
     const double inv_n = 1.0 / (double)D;
@@ -361,7 +400,10 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     // The tables of a tile are computed at the END of the pass before it (the first tile's here), into the buffer the
     // pass before that used: the double-precision sincos then runs while none of a pass's loaded vectors are live, so
     // its registers do not compete with them (computing the tables between the loads and their use cost 15 %).
-    if ((long long)blockIdx.x < ntiles) tokens_cos_sin<true>(tab, tab + TT * half, a, invf, (long long)blockIdx.x * TT, TT, PL, VE);
+    if ((long long)blockIdx.x < ntiles) {
+        if (TAB) tile_tables_async(tab, tab + TT * half, a, (long long)blockIdx.x * TT, TT, PL, VE, half);
+        else tokens_cos_sin<true>(tab, tab + TT * half, a, invf, (long long)blockIdx.x * TT, TT, PL, VE);
+    }
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, flip ^= 1) {
         const long long t0 = tile * TT;
         const uint4* src = in_base + (size_t)t0 * in_vec;
@@ -374,7 +416,12 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
         }
         float* cos_t = tab + flip * (2 * TT * half);
         float* sin_t = cos_t + TT * half;
-        __syncthreads();   // this tile's tables (written at the end of the previous pass) are complete
+        if (TAB) cp_async_wait_all();   // this thread's copies of this tile's tables have landed
+        __syncthreads();   // this tile's tables (written during the previous pass) are complete
+        if (TAB && tile + gridDim.x < ntiles) {   // the other buffer was last read one pass ago, before this barrier
+            float* ncos = tab + (flip ^ 1) * (2 * TT * half);
+            tile_tables_async(ncos, ncos + TT * half, a, (tile + gridDim.x) * TT, TT, PL, VE, half);
+        }
         const ulonglong2* ct = reinterpret_cast<const ulonglong2*>(cos_t) + l;   // chunk c of token tt: [(tt * half) / 4 + c * PL]
         const ulonglong2* st = reinterpret_cast<const ulonglong2*>(sin_t) + l;
 #pragma unroll
@@ -420,7 +467,7 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                 st_stream(dst + (tt * out_vec + (unsigned)vhi), Io<IO>::pack(fhi));
             }
         }
-        if (tile + gridDim.x < ntiles) {   // the other buffer was last read one pass ago, before this pass's barrier
+        if (!TAB && tile + gridDim.x < ntiles) {   // the other buffer was last read one pass ago, before this pass's barrier
             float* ncos = tab + (flip ^ 1) * (2 * TT * half);
             tokens_cos_sin<true>(ncos, ncos + TT * half, a, invf, (tile + gridDim.x) * TT, TT, PL, VE);
         }
@@ -482,6 +529,58 @@ k_qk_norm_rope_generic(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                 }
             }
             __syncthreads();  // v is rewritten by the next head
+        }
+    }
+}
+
+// The cos / sin tables the TAB kernels read: cos_out / sin_out [T][half] fp32, row t = token t at positions[t] (or
+// pos0 + t), entry i = cos / sin of pos * inv_freq[i] (/ ff[i]) formed and evaluated in double and rounded once, the
+// angle of the CPU reference (src/qwen_ops.cpp:18-19; the tables of tests/rope_verify.cpp:73-81 are built the same
+// way, on the host); pairs at or beyond rot_pairs get (1, 0). A forward pass fills them once and every layer's q/k
+// call reads them, as the reference's rope_rotate_half takes host-built tables (src/rope_embedding.hip:18-37).
+// PER (4 or 1) consecutive pairs per thread, half / PER threads per token, 256 / (half / PER) tokens per CTA pass.
+template <bool FAST_TRIG, int PER>
+__global__ void __launch_bounds__(256)
+k_rope_table(const int* positions, int pos0, long long T, int half, int rot_pairs, const float* ff, float* cos_out,
+             float* sin_out, const __grid_constant__ RopeFreq fr) {
+    __shared__ double invf[B200_MAX_ROT_PAIRS];
+    stage_inv_freq(invf, fr, half);
+    const int L = half / PER, tpp = 256 / L;
+    const int l = threadIdx.x % L, slot = threadIdx.x / L;
+    if (slot >= tpp) return;
+    double f[PER];
+    bool rot[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = l * PER + j;
+        rot[j] = i < rot_pairs;
+        f[j] = invf[i];
+    }
+    for (long long t = (long long)blockIdx.x * tpp + slot; t < T; t += (long long)gridDim.x * tpp) {
+        const int pos = positions ? positions[t] : pos0 + (int)t;
+        float c[PER], s[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            c[j] = 1.0f;
+            s[j] = 0.0f;
+            if (rot[j]) {
+                double theta = (double)pos * f[j];
+                if (ff) theta /= (double)ff[l * PER + j];
+                double ds, dc;
+                if (FAST_TRIG) sincos_cw(theta, &ds, &dc);   // (the launcher guarantees |theta| < 2^31 here)
+                else sincos(theta, &ds, &dc);
+                c[j] = (float)dc;
+                s[j] = (float)ds;
+            }
+        }
+        float* co = cos_out + (size_t)t * half + l * PER;
+        float* so = sin_out + (size_t)t * half + l * PER;
+        if constexpr (PER == 4) {
+            *reinterpret_cast<float4*>(co) = make_float4(c[0], c[1], c[2], c[3]);
+            *reinterpret_cast<float4*>(so) = make_float4(s[0], s[1], s[2], s[3]);
+        } else {
+            co[0] = c[0];
+            so[0] = s[0];
         }
     }
 }

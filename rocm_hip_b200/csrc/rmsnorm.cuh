@@ -24,6 +24,7 @@
 #define B200_RMSNORM_CUH
 
 #include "common.cuh"
+#include "q8_side.cuh"
 
 namespace b200 {
 
@@ -103,15 +104,23 @@ k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int 
 // Values travel as packed fp32 pairs: the add, the two multiplies and the bf16 packing are two-wide instructions,
 // each lane rounded as the scalar instruction would. Same summation order as k_add_rmsnorm is NOT promised: a row
 // width always maps to the same kernel, so a row's bits are still a function of the row alone.
-// MAXT: largest CTA the instance is launched with; small CTAs are held to 96 registers so that four fit an SM.
+// MAXT: largest CTA the instance is launched with (160, 320 or 512 threads); CTAs of up to 160 threads are held to 96
+// registers so that four fit an SM, those of up to 320 to 102 so that two do.
 // XH (fp32 rows only): y is also written rounded to bf16 (xh_bf16) or fp16 into xh, the 16-bit side copy the
 // reference's producers write for their matmul consumers (src/q8_device.h:37-43,58): 2 more bytes per value written
 // instead of a second kernel that reads y again.
-template <typename IO, int VPT, bool HAS_ADD, int MAXT, bool XH = false>
-__global__ void __launch_bounds__(MAXT, MAXT <= 160 ? 4 : 1)
+// Q8 (fp32 rows, n % 256 == 0): y is also quantised into the Q8_0 and Q8_K activation formats from the registers that
+// hold it, as the reference's producers do (src/q8_device.h:54-104, called at src/gpu_ops.hip:55,98): a Q8_0 block is
+// 8 neighbouring lanes of one of the thread's vectors, a Q8_K block the 64 consecutive vectors of two 32-lane groups,
+// whose keys meet in shared memory (one more CTA barrier per row). side: the xh pointer and the int8 outputs.
+template <typename IO, int VPT, bool HAS_ADD, int MAXT, bool XH = false, bool Q8 = false>
+__global__ void __launch_bounds__(MAXT, MAXT <= 160 ? 4 : MAXT <= 320 ? (Q8 ? 3 : 2) : 1)
 k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO* y, int n, long long T, float eps,
-                   uint16_t* xh = nullptr, int xh_bf16 = 0) {
-    static_assert(!XH || sizeof(IO) == 4, "the 16-bit side copy belongs to fp32 rows");
+                   const Q8Side side = Q8Side{}) {
+    static_assert(!(XH || Q8) || sizeof(IO) == 4, "the side outputs belong to fp32 rows");
+    __shared__ Q8Half half_stat[Q8 ? 64 : 1];   // per 128 values of the row (n <= 8192)
+    uint16_t* const xh = side.xh;
+    const int xh_bf16 = side.xh_bf16;
     constexpr int NP = Io2<IO>::NP;
     // fp32 rows: every square goes into a double sum, which makes 1/rms, and with it y, the CPU reference's to the bit.
     // 16-bit rows: a thread's own 16 or 32 squares (each exact in fp32) are summed in two packed fp32 chains and only
@@ -197,6 +206,7 @@ k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO*
         const double tot = cta_sum(s0 + s1, part[flip]);
         const float inv = inv_rms(tot, inv_n, eps);
         const f2 inv2 = pk2(inv, inv);
+        float yq[Q8 ? VPT : 1][4];
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             f2 v[NP];
@@ -205,6 +215,31 @@ k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO*
             for (int k = 0; k < NP; ++k) v[k] = mul2(mul2(v[k], inv2), gam[j][k]);
             st_stream(py + off + j * tpr, Io2<IO>::pack(v));
             if (XH) st_half4(xh + (off + j * tpr + l) * 4, v[0], v[NP > 1 ? 1 : 0], xh_bf16);
+            if constexpr (Q8) {
+                upk2(v[0], yq[j][0], yq[j][1]);
+                upk2(v[1], yq[j][2], yq[j][3]);
+            }
+        }
+        if constexpr (Q8) {
+            unsigned qi[VPT];
+            bool live[VPT], first[VPT];
+            Q8Half blk[VPT];
+            Q8Half* cell[VPT];
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                qi[j] = ((unsigned)off + j * tpr + l) * 4u;
+                live[j] = true;
+                first[j] = (((l + j * tpr) >> 5) & 1) == 0;
+                cell[j] = &half_stat[(l + j * tpr) >> 5];
+            }
+            q8v_phase_a<VPT>(yq, qi, live, side, cell);
+            __syncthreads();   // (the next row's writes to half_stat come after its row-sum barrier)
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int hb = (l + j * tpr) >> 5;
+                blk[j] = q8v_combine(half_stat[hb & ~1], half_stat[hb | 1]);
+            }
+            q8v_phase_b<VPT>(yq, qi, live, side, blk, first);
         }
     }
 }

@@ -15,6 +15,7 @@
 #define B200_SWIGLU_CUH
 
 #include "common.cuh"
+#include "q8_side.cuh"
 
 namespace b200 {
 
@@ -107,6 +108,65 @@ k_swiglu(const IO* g, const IO* u, IO* out, long long n, uint16_t* xh = nullptr,
     if (blockIdx.x == 0 && threadIdx.x < (int)(n - nvec * VE)) {
         const long long i = nvec * VE + threadIdx.x;
         Io<IO>::store1(out + i, silu_mul<FAST>(Io<IO>::load1(g + i), Io<IO>::load1(u + i)));
+    }
+}
+
+// fp32 SwiGLU that also quantises its output into the Q8_0 and Q8_K activation formats (and the 16-bit copy when XH)
+// from the registers that hold it, as the reference's swiglu does (src/gpu_ops.hip:113, src/q8_device.h:54-104): the
+// tile walk of k_swiglu, in which the 256 threads' k-th vectors are 1024 consecutive values = four Q8_K blocks of two
+// warps each; the two warps' keys meet in shared memory (one CTA barrier per tile; the key buffers alternate between
+// tiles, so a tile's writes never meet the previous tile's reads). n % 32 == 0: a last partial Q8_K block gets its Q8_0
+// blocks and an incomplete Q8_K part, as in the reference.
+template <int UNROLL, bool XH>
+__global__ void __launch_bounds__(256)
+k_swiglu_q8(const float* g, const float* u, float* out, long long n, const Q8Side side) {
+    __shared__ Q8Half half_stat[2][UNROLL][8];
+    const long long nvec = n / 4;
+    constexpr int TILE = 256 * UNROLL;
+    const long long ntiles = (nvec + TILE - 1) / TILE;
+    const int warp = threadIdx.x >> 5;
+    int flip = 0;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, flip ^= 1) {
+        const long long v0 = tile * TILE;
+        const uint4* pg = reinterpret_cast<const uint4*>(g) + v0 + threadIdx.x;
+        const uint4* pu = reinterpret_cast<const uint4*>(u) + v0 + threadIdx.x;
+        uint4* po = reinterpret_cast<uint4*>(out) + v0 + threadIdx.x;
+        const int left = (int)(nvec - v0 < TILE ? nvec - v0 : TILE) - (int)threadIdx.x;  // vectors from this thread's first
+        uint4 rg[UNROLL], ru[UNROLL];
+        bool live[UNROLL], first[UNROLL];
+        unsigned qi[UNROLL];
+#pragma unroll
+        for (int k = 0; k < UNROLL; ++k) {
+            live[k] = k * 256 < left;
+            first[k] = (warp & 1) == 0;
+            qi[k] = ((unsigned)v0 + threadIdx.x + k * 256) * 4u;
+            rg[k] = live[k] ? ld_stream(pg + k * 256) : make_uint4(0, 0, 0, 0);
+            ru[k] = live[k] ? ld_stream(pu + k * 256) : make_uint4(0, 0, 0, 0);
+        }
+        float y[UNROLL][4];
+#pragma unroll
+        for (int k = 0; k < UNROLL; ++k) {
+            f2 a[2], b[2];
+            Io2<float>::unpack(rg[k], a);
+            Io2<float>::unpack(ru[k], b);
+            a[0] = silu_mul2<false>(a[0], b[0]);
+            a[1] = silu_mul2<false>(a[1], b[1]);
+            if (live[k]) {
+                st_stream(po + k * 256, Io2<float>::pack(a));
+                if (XH) st_half4(side.xh + qi[k], a[0], a[1], side.xh_bf16);
+            }
+            upk2(a[0], y[k][0], y[k][1]);
+            upk2(a[1], y[k][2], y[k][3]);
+        }
+        Q8Half blk[UNROLL];
+        Q8Half* cell[UNROLL];
+#pragma unroll
+        for (int k = 0; k < UNROLL; ++k) cell[k] = &half_stat[flip][k][warp];
+        q8v_phase_a<UNROLL>(y, qi, live, side, cell);
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < UNROLL; ++k) blk[k] = q8v_combine(half_stat[flip][k][warp & ~1], half_stat[flip][k][warp | 1]);
+        q8v_phase_b<UNROLL>(y, qi, live, side, blk, first);
     }
 }
 

@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_qk_norm_rope_kv", "gpu_attn_prep_f16", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_mamba_conv", "gpu_mamba_scan", "gpu_ple_conv", "gpu_hc_norm", "gpu_hc_lowrank", "gpu_hc_mix", "gpu_ple_gate", "gpu_mtp_concat", "gpu_mamba_gnorm", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_rope_table", "gpu_qk_norm_rope_tab", "gpu_qk_norm_rope_kv", "gpu_attn_prep_f16", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_mamba_conv", "gpu_mamba_scan", "gpu_ple_conv", "gpu_hc_norm", "gpu_hc_lowrank", "gpu_hc_mix", "gpu_ple_gate", "gpu_mtp_concat", "gpu_mamba_gnorm", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "QT_F32", "QT_F16", "QT_BF16", "QT_Q4_1", "QT_Q5_0", "QT_Q5_1", "QT_Q4_K", "QT_Q5_K", "QT_Q6_K",
     "QT_BLOCKS", "qt_row_size", "HostRows", "HostGroup",
 ]
@@ -316,6 +316,24 @@ def gpu_qk_norm_rope(qfull, k, q_norm, k_norm, q_out, k_out, n_q, n_kv, head_dim
               rot_pairs, _ptr(positions), pos0, T, freq_base, eps, gated, qk_norm, _ptr(freq_factors), _stream()))
 
 
+def gpu_rope_table(positions, pos0, T, n_rot, rot_pairs, freq_base, cos_tab, sin_tab, freq_factors=None):
+    """cos / sin tables [T][n_rot / 2] (fp32 CUDA tensors) of the angles gpu_qk_norm_rope would form."""
+    _check("gpu_rope_table",
+           _lib.load().gpu_rope_table(_ptr(positions), pos0, T, n_rot, rot_pairs, freq_base, _ptr(freq_factors),
+                                      _ptr(cos_tab), _ptr(sin_tab), _stream()))
+
+
+def gpu_qk_norm_rope_tab(qfull, k, q_norm, k_norm, q_out, k_out, n_q, n_kv, head_dim, n_rot, cos_tab, sin_tab, T, eps,
+                         gated=0, qk_norm=1):
+    """gpu_qk_norm_rope with the angles' cos / sin read from the tables of gpu_rope_table."""
+    lib = _lib.load()
+    ref = qfull if qfull is not None else k
+    fn = lib.gpu_qk_norm_rope_tab if ref.dtype == torch.float32 else lib.gpu_qk_norm_rope_tab_bf16
+    _check("gpu_qk_norm_rope_tab",
+           fn(_ptr(qfull), _ptr(k), _ptr(q_norm), _ptr(k_norm), _ptr(q_out), _ptr(k_out), n_q, n_kv, head_dim, n_rot,
+              _ptr(cos_tab), _ptr(sin_tab), T, eps, gated, qk_norm, _stream()))
+
+
 def gpu_qk_norm_rope_kv(qfull, k, q_norm, k_norm, q_out, k_cache, kv_stride, kv_shift, kv_bstride, n_q, n_kv, head_dim, n_rot,
                         rot_pairs, positions, pos0, T, freq_base, eps, gated=0, qk_norm=1, freq_factors=None):
     """gpu_qk_norm_rope with the K heads written, rounded to fp16, into the block-major KV cache `k_cache`."""
@@ -417,6 +435,24 @@ class HostRows:
         h = self._h
         _check("b200_host_embed_rows", self._lib.b200_host_embed_rows(
             self._ctx, self._elem(out), qtype, _ptr(table_dev), row_bytes, vocab, h(tokens), h(out), E, T, scale))
+
+
+    def layer_sweep(self, *, qtype, table_dev, row_bytes, vocab, tokens, E, w_attn_norm, w_ffn_norm, w_next_norm, eps,
+                    xn_attn, qfull, k, q_out, k_out, q_norm, k_norm, n_q, n_kv, head_dim, n_rot, freq_base, attn_proj,
+                    xn_ffn, gate, up, FF, act, ffn_proj, x_out, xn_next, T, rot_pairs=0, positions=None, pos0=0, gated=0,
+                    qk_norm=1, freq_factors=None, embd_scale=1.0):
+        """b200_host_layer_sweep: the layer's six ops in one call; rows in host memory, the residual stream stays on
+        the device between the kernels of a chunk."""
+        v = lambda a: self._h(a).value if a is not None else None
+        a = _lib.b200_layer_sweep(
+            elem=self._elem(xn_attn), T=T, qtype=qtype, table_dev=table_dev.data_ptr(), row_bytes=row_bytes, vocab=vocab,
+            tokens=v(tokens), E=E, embd_scale=embd_scale, w_attn_norm=v(w_attn_norm), w_ffn_norm=v(w_ffn_norm),
+            w_next_norm=v(w_next_norm), eps=eps, xn_attn=v(xn_attn), qfull=v(qfull), k=v(k), q_out=v(q_out), k_out=v(k_out),
+            q_norm=v(q_norm), k_norm=v(k_norm), n_q=n_q, n_kv=n_kv, head_dim=head_dim, n_rot=n_rot, rot_pairs=rot_pairs,
+            positions=v(positions), pos0=pos0, freq_base=freq_base, gated=gated, qk_norm=qk_norm,
+            freq_factors=v(freq_factors), attn_proj=v(attn_proj), xn_ffn=v(xn_ffn), gate=v(gate), up=v(up), FF=FF,
+            act=v(act), ffn_proj=v(ffn_proj), x_out=v(x_out), xn_next=v(xn_next))
+        _check("b200_host_layer_sweep", self._lib.b200_host_layer_sweep(self._ctx, C.byref(a)))
 
 
 class HostGroup(HostRows):

@@ -3,6 +3,8 @@ value kind (skipped or read), tensor infos, alignment, data pointers; malformed 
 import ctypes as C
 import os
 
+import struct
+
 import numpy as np
 import pytest
 
@@ -73,6 +75,17 @@ def test_malformed_files_are_refused(tmp_path):
     cases = {"magic": b"GGUX" + raw[4:], "version": raw[:4] + (9).to_bytes(4, "little") + raw[8:],
              "truncated_header": raw[:40], "truncated_data": raw[:-200], "empty": b"",
              "huge_count": raw[:8] + (2**40).to_bytes(8, "little") + raw[16:]}
+    # extents whose byte count wraps around 2^64: 4 * ne0 * ne1 = 2^64 + 4096 for F32 rows of 4 values. The wrapped size
+    # (4096 bytes) would fit the file; the open must fail rather than report a 2^60-row tensor as present.
+    path = str(tmp_path / "wrap_src.gguf")
+    write_gguf(path, [], [("token_embd.weight", 0, (4, 256), np.zeros((256, 4), np.float32))])
+    wrap = bytearray(open(path, "rb").read())
+    at = wrap.index(struct.pack("<QQ", 4, 256))
+    wrap[at + 8:at + 16] = struct.pack("<Q", 2**60 + 256)
+    cases["extent_product_wraps"] = bytes(wrap)
+    # a file that ends right after the key and type of general.alignment (no value bytes to read)
+    head = struct.pack("<IIQQ", 0x46554747, 3, 0, 1) + struct.pack("<Q", 17) + b"general.alignment" + struct.pack("<I", T_U32)
+    cases["alignment_value_missing"] = head
     for name, data in cases.items():
         p = str(tmp_path / (name + ".gguf"))
         open(p, "wb").write(data)

@@ -83,3 +83,52 @@ def test_row_too_large_for_a_slot(ops, hr):
     with pytest.raises(ops.LayerOpError) as e:
         hr.add_rmsnorm(x, None, None, None, x.copy(), 1 << 19, 2, 1e-6)
     assert e.value.code == 1
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_layer_sweep_gives_the_bits_of_the_six_calls(ops, oracle, bf16):
+    """b200_host_layer_sweep keeps the residual stream on the device between the kernels of a chunk; every output
+    row must still be, bit for bit, what the six separate host-buffer calls produce (and the gather the oracle's)."""
+    T, E, nq, nkv, D, FF, vocab = 333, 1024, 16, 8, 128, 3072, 2000
+    h = ops.HostRows(slot_bytes=4 << 20, n_slots=3)    # 17 rows per chunk: many chunks, a ragged last one
+    try:
+        f = lambda name, *shape: synth.normal(5, name, 0, int(np.prod(shape))).reshape(shape)
+        cv = (lambda a: oracle.f32_to_bf16(a).reshape(a.shape)) if bf16 else (lambda a: a)
+        table = synth.q8_0_table(0, "ls.tab", vocab, E)
+        ids = synth.randint(0, "ls.ids", 0, T, 0, vocab).astype(np.int32)
+        q, k = cv(f("ls.q", T, nq * D)), cv(f("ls.k", T, nkv * D))
+        p1, p2, g, u = cv(f("ls.p1", T, E)), cv(f("ls.p2", T, E)), cv(f("ls.g", T, FF)), cv(f("ls.u", T, FF))
+        w1, w2, w3 = (synth.normal(5, n, 0, E, 1.0, 0.1) for n in ("ls.w1", "ls.w2", "ls.w3"))
+        qn, kn = synth.normal(5, "ls.qn", 0, D, 1.0, 0.1), synth.normal(5, "ls.kn", 0, D, 1.0, 0.1)
+        z = lambda *shape: np.zeros(shape, q.dtype)
+        dt = dev(table)
+        # the six calls
+        x, xn1, qo, ko, xa, xn2, act, x3, xn3 = z(T, E), z(T, E), z(T, nq * D), z(T, nkv * D), z(T, E), z(T, E), z(T, FF), z(T, E), z(T, E)
+        h.embed_rows(ops.QT_Q8_0, dt, table.shape[1], vocab, ids, x, E, T)
+        h.add_rmsnorm(x, None, None, w1, xn1, E, T, 1e-6)
+        h.qk_norm_rope(q, k, qn, kn, qo, ko, nq, nkv, D, D, 0, None, 77, T, 1e6, 1e-6)
+        h.add_rmsnorm(x, p1, xa, w2, xn2, E, T, 1e-6)
+        h.swiglu(g, u, act, T, FF)
+        h.add_rmsnorm(xa, p2, x3, w3, xn3, E, T, 1e-6)
+        # one call
+        s_xn1, s_qo, s_ko, s_xn2, s_act, s_x3, s_xn3 = z(T, E), z(T, nq * D), z(T, nkv * D), z(T, E), z(T, FF), z(T, E), z(T, E)
+        h.layer_sweep(qtype=ops.QT_Q8_0, table_dev=dt, row_bytes=table.shape[1], vocab=vocab, tokens=ids, E=E,
+                      w_attn_norm=w1, w_ffn_norm=w2, w_next_norm=w3, eps=1e-6, xn_attn=s_xn1, qfull=q, k=k, q_out=s_qo,
+                      k_out=s_ko, q_norm=qn, k_norm=kn, n_q=nq, n_kv=nkv, head_dim=D, n_rot=D, freq_base=1e6,
+                      attn_proj=p1, xn_ffn=s_xn2, gate=g, up=u, FF=FF, act=s_act, ffn_proj=p2, x_out=s_x3, xn_next=s_xn3,
+                      T=T, pos0=77)
+        for a, b in ((xn1, s_xn1), (qo, s_qo), (ko, s_ko), (xn2, s_xn2), (act, s_act), (x3, s_x3), (xn3, s_xn3)):
+            assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
+        if not bf16:   # and the chain is the oracle's: gather bit-exact, hence x3 = (embed + p1) + p2 exactly
+            _, want = oracle.embed_rows(oracle.Q8_0, table, table.shape[1], vocab, ids, E)
+            assert np.array_equal(s_x3, (want + p1) + p2)
+        ids[7] = -1
+        with pytest.raises(ops.LayerOpError) as e:
+            h.layer_sweep(qtype=ops.QT_Q8_0, table_dev=dt, row_bytes=table.shape[1], vocab=vocab, tokens=ids, E=E,
+                          w_attn_norm=w1, w_ffn_norm=w2, w_next_norm=w3, eps=1e-6, xn_attn=s_xn1, qfull=q, k=k,
+                          q_out=s_qo, k_out=s_ko, q_norm=qn, k_norm=kn, n_q=nq, n_kv=nkv, head_dim=D, n_rot=D,
+                          freq_base=1e6, attn_proj=p1, xn_ffn=s_xn2, gate=g, up=u, FF=FF, act=s_act, ffn_proj=p2,
+                          x_out=s_x3, xn_next=s_xn3, T=T, pos0=77)
+        assert e.value.code == 1
+    finally:
+        h.close()

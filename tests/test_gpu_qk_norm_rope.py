@@ -109,6 +109,78 @@ def test_options(ops, oracle):
     assert run(ops, oracle, 2000, 40, 8, 128, 128, 1e6, pos0=9, inplace=True, bf16=True) <= 1
 
 
+def run_tab(ops, oracle, T, nq, nkv, D, n_rot, base, positions=None, pos0=0, gated=0, rot_pairs=0, ff=None, qk_norm=1,
+            bf16=False, seed=0):
+    """The table route: gpu_rope_table once, then gpu_qk_norm_rope_tab; checked like run()."""
+    qs = 2 * D if gated else D
+    q = synth.normal(seed, "qk.q", 0, T * nq * qs).reshape(T, nq * qs)
+    k = synth.normal(seed, "qk.k", 0, T * nkv * D).reshape(T, nkv * D)
+    qn, kn = synth.normal(seed, "qk.qn", 0, D, 1.0, 0.1), synth.normal(seed, "qk.kn", 0, D, 1.0, 0.1)
+    dt = None
+    if bf16:
+        q, k, dt = oracle.f32_to_bf16(q).reshape(q.shape), oracle.f32_to_bf16(k).reshape(k.shape), torch.bfloat16
+    wq, wk = oracle.qk_norm_rope(q, k, qn, kn, nq, nkv, D, n_rot, rot_pairs, positions, pos0, base, 1e-6, gated=gated,
+                                 ff=ff, do_norm=qk_norm, bf16=bf16)
+    dq, dk = dev(q, dt), dev(k, dt)
+    qo = torch.zeros(T, nq * D, device="cuda", dtype=dq.dtype)
+    ko = torch.zeros(T, nkv * D, device="cuda", dtype=dq.dtype)
+    ct = torch.full((T, max(n_rot // 2, 1)), 7.0, device="cuda")
+    st = torch.full((T, max(n_rot // 2, 1)), 7.0, device="cuda")
+    ops.gpu_rope_table(dev(positions) if positions is not None else None, pos0, T, n_rot, rot_pairs, base, ct, st, dev(ff))
+    ops.gpu_qk_norm_rope_tab(dq, dk, dev(qn), dev(kn), qo, ko, nq, nkv, D, n_rot, ct, st, T, 1e-6, gated, qk_norm)
+    torch.cuda.synchronize()
+    gq, gk = host(qo), host(ko)
+    if bf16:
+        return max(bf16_ulp_dist(gq, wq).max(initial=0), bf16_ulp_dist(gk, wk).max(initial=0))
+    return max(max_rel_rows(gq.reshape(-1, D), wq.reshape(-1, D)), max_rel_rows(gk.reshape(-1, D), wk.reshape(-1, D)))
+
+
+def test_table_route_on_the_config_shapes(ops, oracle):
+    """cos / sin from gpu_rope_table + gpu_qk_norm_rope_tab against the CPU oracle: c1 (fp32), c2 (per-row
+    positions), c3 (gated q, partial rotary, theta 1e7), c5 heads at the far end of a 262,144-token prefill; short
+    batches (general kernel) and long ones (tile kernel with asynchronous table copies, plus its tail tokens)."""
+    assert run_tab(ops, oracle, 2427, 16, 8, 128, 128, 1e6) <= 1e-5
+    pos = synth.randint(0, "c2.pos", 0, 64, 0, 32768).astype(np.int32)
+    assert run_tab(ops, oracle, 64, 16, 8, 128, 128, 1e6, positions=pos, bf16=True) <= 1
+    assert run_tab(ops, oracle, 1500, 16, 4, 256, 64, 1e7, gated=1, bf16=True) <= 1
+    assert run_tab(ops, oracle, 1499, 16, 4, 256, 64, 1e7, gated=1) <= 1e-5
+    assert run_tab(ops, oracle, 1501, 40, 8, 128, 128, 1e6, pos0=262144 - 1501) <= 1e-5
+    assert run_tab(ops, oracle, 1501, 40, 8, 128, 128, 1e6, pos0=262144 - 1501, bf16=True) <= 1
+
+
+def test_table_route_options_and_head_shapes(ops, oracle):
+    """rot_pairs < n_rot / 2, frequency factors, RoPE only, the generic path (96), no rotation at all."""
+    ff = (1.0 + synth.uniform(0, "ff", 0, 64) * 7).astype(np.float32)
+    assert run_tab(ops, oracle, 50, 8, 2, 128, 128, 1e6, rot_pairs=24, pos0=77) <= 1e-5
+    assert run_tab(ops, oracle, 1300, 8, 2, 128, 128, 1e6, rot_pairs=24, pos0=77) <= 1e-5
+    assert run_tab(ops, oracle, 50, 8, 2, 128, 128, 5e5, ff=ff, pos0=4000) <= 1e-5
+    assert run_tab(ops, oracle, 50, 8, 2, 128, 128, 1e6, qk_norm=0, pos0=9) <= 1e-5
+    for D, n_rot in ((64, 64), (512, 512), (512, 128), (96, 32), (128, 20), (256, 0)):
+        for bf16 in (False, True):
+            r = run_tab(ops, oracle, 33, 5, 3, D, n_rot, 1e4, pos0=1000, bf16=bf16, seed=D + n_rot)
+            assert r <= (1 if bf16 else 1e-5), (D, n_rot, bf16, r)
+
+
+def test_table_route_gives_the_bits_of_the_direct_route(ops):
+    """On a long batch both routes evaluate sin / cos with the same routine, so the outputs are identical; the table
+    itself holds (1, 0) beyond rot_pairs."""
+    T, nq, nkv, D = 1400, 8, 2, 128
+    q, k = torch.randn(T, nq * D, device="cuda"), torch.randn(T, nkv * D, device="cuda")
+    w = 1 + 0.1 * torch.randn(D, device="cuda")
+    for dt in (torch.float32, torch.bfloat16):
+        qq, kk = q.to(dt), k.to(dt)
+        a = [torch.empty_like(qq), torch.empty_like(kk)]
+        b = [torch.empty_like(qq), torch.empty_like(kk)]
+        ops.gpu_qk_norm_rope(qq, kk, w, w, a[0], a[1], nq, nkv, D, D, 40, None, 1000, T, 1e6, 1e-6)
+        ct, st = torch.empty(T, D // 2, device="cuda"), torch.empty(T, D // 2, device="cuda")
+        ops.gpu_rope_table(None, 1000, T, D, 40, 1e6, ct, st)
+        ops.gpu_qk_norm_rope_tab(qq, kk, w, w, b[0], b[1], nq, nkv, D, D, ct, st, T, 1e-6)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+        assert bool((ct[:, 40:] == 1).all()) and bool((st[:, 40:] == 0).all())
+    with pytest.raises(ops.LayerOpError):
+        ops.gpu_qk_norm_rope_tab(q, k, w, w, a[0], a[1], nq, nkv, D, D, None, None, T, 1e-6)
+
+
 def test_rope_alone_matches_golden(ops):
     """qk_norm 0 on the reference's own outputs (tests/golden/rope_neox.npz, made by qwen_rope_neox)."""
     import os
