@@ -1,9 +1,11 @@
 #!/usr/bin/env python
-"""Benchmark of the fused layer-op path: one step = one pass of the layer-op sweep over one batch of synthetic rows
-(embedding gather -> RMSNorm -> q/k norm + RoPE -> residual add + RMSNorm -> SwiGLU -> residual add + RMSNorm), in the
-order a layer of the reference's forward pass issues them (src/qwen_model.cpp:980-990, 941-957).
+"""Benchmark of the fused layer-op path. One sweep = one pass of the layer's ops over one batch of synthetic rows
+(embedding gather -> RMSNorm -> cos/sin table -> q/k norm + RoPE -> residual add + RMSNorm -> SwiGLU -> residual add +
+RMSNorm), in the order a layer of the reference's forward pass issues them (src/qwen_model.cpp:980-990, 941-957). One
+step = `sweeps_per_step` sweeps back to back (as many as keep a step near 80 ms whatever the GPU count, so that the
+timed region of K steps is long enough for the clock samples to mean something).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c5|c4|c3|c1] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c5|c4|c3|c2|c1] [--impl reference]
 
 For N > 1 launch one process per GPU with torch.distributed.run; rows are sharded by token, no collective touches
 the data path (torch.distributed only carries the barrier and the max over ranks of the device-timed duration).
@@ -11,7 +13,9 @@ Prints ONE JSON line on rank 0:
   value       token rows per second through the whole sweep, inputs resident in HBM, all ranks together
   kernels     per kernel: rows/s, algorithmic GB/s, fraction of the measured HBM copy peak and of the nominal 8 TB/s
   roofline    the dominant kernel (SwiGLU) against the measured HBM peak
-  e2e         the same sweep through the host-buffer C-ABI calls, host<->device copies inside the timed region
+  configs     the same per-kernel table for the other workloads (c1 .. c4), each kernel launched on cold inputs
+  e2e         the same sweep through the host-buffer C-ABI call, host<->device copies inside the timed region, next to
+              the time the same bytes take as plain copies
   cpu_baseline the reference's CPU functions (or their restatement) on the host cores, on a bounded row sample
 --impl reference times that CPU path alone with all host threads and prints the same line shape.
 """
@@ -53,6 +57,17 @@ def measured_peak():
 
 
 from rocm_hip_b200.sharding import shard  # noqa: E402  (contiguous row range of a rank)
+
+
+def dram_traffic_ratio(kernel):
+    """DRAM bytes per algorithmic byte of a kernel, from the tracked summary of its profiler capture (a small case;
+    every byte is touched once, so traffic grows with the rows). Returns (ratio or None, where it came from)."""
+    p = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        e = json.load(open(p))[kernel]
+        return float(e["dram_bytes"]) / float(e["algorithmic_bytes"]), f"profiles/dram_traffic.json[{kernel}]: {e['capture']}"
+    except Exception:
+        return None, "no capture on file"
 
 
 class ClockSampler:
@@ -176,6 +191,9 @@ class Sweep:
         self.k = big(T, nkv * D)
         self.q_out = torch.empty(T, nq * D, device=device, dtype=self.dt)
         self.k_out = torch.empty(T, nkv * D, device=device, dtype=self.dt)
+        half = wl["n_rot"] // 2
+        self.cos_tab = torch.empty(T, half, device=device)
+        self.sin_tab = torch.empty(T, half, device=device)
         self.qn = (1 + 0.1 * torch.randn(D, device=device, generator=g)).float()
         self.kn = (1 + 0.1 * torch.randn(D, device=device, generator=g)).float()
         self.proj1 = big(T, E)
@@ -188,8 +206,14 @@ class Sweep:
                   T * (4 + self.row_bytes + E * s), T, "token rows"))
         K.append(("rmsnorm", lambda: ops.gpu_add_rmsnorm(self.x, None, self.x, self.w1, self.xn, E, T, eps),
                   T * 2 * E * s + 4 * E, T, "token rows"))
-        K.append(("qk_norm_rope", lambda: ops.gpu_qk_norm_rope(self.q, self.k, self.qn, self.kn, self.q_out, self.k_out, nq, nkv, D,
-                                                               wl["n_rot"], 0, self.positions, self.pos0, T, wl["theta"], eps, gated, 1),
+        # The cos / sin of the tokens' angles are computed once (a forward pass does it once for all its layers; here
+        # once per sweep, its time counted in the step) and the q/k kernel reads them. The table is not algorithmic
+        # traffic of the q/k kernel: its bytes are the head rows in and out.
+        K.append(("rope_table", lambda: ops.gpu_rope_table(self.positions, self.pos0, T, wl["n_rot"], 0, wl["theta"], self.cos_tab,
+                                                            self.sin_tab),
+                  T * 4 * (1 if self.positions is not None else 0) + T * half * 8, T, "token rows"))
+        K.append(("qk_norm_rope", lambda: ops.gpu_qk_norm_rope_tab(self.q, self.k, self.qn, self.kn, self.q_out, self.k_out, nq,
+                                                                   nkv, D, wl["n_rot"], self.cos_tab, self.sin_tab, T, eps, gated, 1),
                   T * ((nq * qs if not gated else nq * D) + nkv * D + (nq + nkv) * D) * s, T * (nq + nkv), "head rows"))
         K.append(("add_rmsnorm_ffn", lambda: ops.gpu_add_rmsnorm(self.x, self.proj1, self.x_alt, self.w2, self.xn, E, T, eps),
                   T * 4 * E * s + 4 * E, T, "token rows"))
@@ -198,8 +222,13 @@ class Sweep:
                   T * 4 * E * s + 4 * E, T, "token rows"))
         self.dominant = "swiglu"
 
-    def step(self, events=None):
+    def step(self, events=None, flush=None):
+        """One sweep. events: per kernel a (start, end) pair recorded around its launch. flush: a tensor larger than L2
+        that is rewritten before every kernel (outside the event pair), for workloads whose tensors would otherwise
+        still sit in the 126 MB L2 from the kernel that produced them."""
         for i, (_, fn, _, _, _) in enumerate(self.kernels):
+            if flush is not None:
+                flush.add_(1)
             if events is not None:
                 events[i][0].record()
             fn()
@@ -210,8 +239,10 @@ class Sweep:
 # ------------------------------------------------------------------------------------------------ host-buffer e2e
 
 class HostSweep:
-    """The same sweep through the host-buffer C-ABI calls: every row input starts in page-locked host memory and every
-    row output ends there, each step."""
+    """The same sweep through the host-buffer C-ABI call (b200_host_layer_sweep; the MoE workload, which has no gather
+    or q/k step, through b200_host_add_rmsnorm + b200_host_swiglu): every true input starts in page-locked host memory
+    and every result ends there, each step; the residual stream between the ops stays on the device, as the
+    reference keeps it in place (s.x / s.x_alt, src/qwen_model.cpp:946-957)."""
 
     def __init__(self, wl, T, row0, table_dev, row_bytes):
         import torch
@@ -223,9 +254,8 @@ class HostSweep:
         g = torch.Generator().manual_seed(4242 + row0)
         pin = lambda *shape, dtype=dt: torch.empty(*shape, dtype=dtype).pin_memory()
         rnd = lambda *shape: pin(*shape).copy_(torch.randn(*shape, generator=g).to(dt))
-        self.host = ops.HostRows(slot_bytes=48 << 20, n_slots=4)
+        self.host = ops.HostRows(slot_bytes=32 << 20, n_slots=6)
         self.w = (1 + 0.1 * torch.randn(E, generator=g)).float()
-        self.h2d = self.d2h = 0
         self.calls = []
         H = self.host
         if wl.get("moe"):
@@ -234,36 +264,60 @@ class HostSweep:
             gg, uu, act = rnd(rows, 512), rnd(rows, 512), pin(rows, 512)
             self.calls.append(lambda: H.add_rmsnorm(x, None, None, self.w, xn, E, T, wl["eps"]))
             self.calls.append(lambda: H.swiglu(gg, uu, act, rows, 512))
-            self.h2d = T * E * s + 2 * rows * 512 * s
-            self.d2h = T * E * s + rows * 512 * s
-            self.keep = (x, xn, gg, uu, act)
-            return
-        nq, nkv, D = wl["n_q"], wl["n_kv"], wl["D"]
-        gated = wl.get("gated", 0)
-        qs = 2 * D if gated else D
-        ids = pin(T, dtype=torch.int32).copy_(torch.randint(0, wl["vocab"], (T,), generator=g, dtype=torch.int32))
-        x, x_alt, xn = pin(T, E), pin(T, E), pin(T, E)
-        q, k = rnd(T, nq * qs), rnd(T, nkv * D)
-        qo, ko = pin(T, nq * D), pin(T, nkv * D)
-        qn = (1 + 0.1 * torch.randn(D, generator=g)).float()
-        kn = (1 + 0.1 * torch.randn(D, generator=g)).float()
-        p1, p2 = rnd(T, E), rnd(T, E)
-        gg, uu, act = rnd(T, FF), rnd(T, FF), pin(T, FF)
-        eps = wl["eps"]
-        C = self.calls
-        C.append(lambda: H.embed_rows(wl["qtype"], table_dev, row_bytes, wl["vocab"], ids, x, E, T))
-        C.append(lambda: H.add_rmsnorm(x, None, None, self.w, xn, E, T, eps))
-        C.append(lambda: H.qk_norm_rope(q, k, qn, kn, qo, ko, nq, nkv, D, wl["n_rot"], 0, None, row0, T, wl["theta"], eps, gated, 1))
-        C.append(lambda: H.add_rmsnorm(x, p1, x_alt, self.w, xn, E, T, eps))
-        C.append(lambda: H.swiglu(gg, uu, act, T, FF))
-        C.append(lambda: H.add_rmsnorm(x_alt, p2, x, self.w, xn, E, T, eps))
-        self.h2d = T * (4 + E * s + (nq * qs + nkv * D) * s + 2 * E * s + 2 * FF * s + 2 * E * s)
-        self.d2h = T * (E * s + E * s + (nq + nkv) * D * s + 2 * E * s + FF * s + 2 * E * s)
-        self.keep = (ids, x, x_alt, xn, q, k, qo, ko, p1, p2, gg, uu, act, qn, kn)
+            self.inputs, self.outputs = [x, gg, uu], [xn, act]
+        else:
+            nq, nkv, D = wl["n_q"], wl["n_kv"], wl["D"]
+            gated = wl.get("gated", 0)
+            qs = 2 * D if gated else D
+            ids = pin(T, dtype=torch.int32).copy_(torch.randint(0, wl["vocab"], (T,), generator=g, dtype=torch.int32))
+            q, k = rnd(T, nq * qs), rnd(T, nkv * D)
+            p1, p2, gg, uu = rnd(T, E), rnd(T, E), rnd(T, FF), rnd(T, FF)
+            xn1, qo, ko, xn2, act, xo, xn3 = pin(T, E), pin(T, nq * D), pin(T, nkv * D), pin(T, E), pin(T, FF), pin(T, E), pin(T, E)
+            qn = (1 + 0.1 * torch.randn(D, generator=g)).float()
+            kn = (1 + 0.1 * torch.randn(D, generator=g)).float()
+            self.calls.append(lambda: H.layer_sweep(
+                qtype=wl["qtype"], table_dev=table_dev, row_bytes=row_bytes, vocab=wl["vocab"], tokens=ids, E=E,
+                w_attn_norm=self.w, w_ffn_norm=self.w, w_next_norm=self.w, eps=wl["eps"], xn_attn=xn1, qfull=q, k=k, q_out=qo,
+                k_out=ko, q_norm=qn, k_norm=kn, n_q=nq, n_kv=nkv, head_dim=D, n_rot=wl["n_rot"], freq_base=wl["theta"],
+                attn_proj=p1, xn_ffn=xn2, gate=gg, up=uu, FF=FF, act=act, ffn_proj=p2, x_out=xo, xn_next=xn3, T=T, pos0=row0,
+                gated=gated))
+            self.inputs, self.outputs = [ids, q, k, p1, p2, gg, uu], [xn1, qo, ko, xn2, act, xo, xn3]
+            self.keep = (qn, kn)
+        self.h2d = sum(t.numel() * t.element_size() for t in self.inputs)
+        self.d2h = sum(t.numel() * t.element_size() for t in self.outputs)
 
     def step(self):
         for c in self.calls:
             c()
+
+    def copy_only_ms(self, steps):
+        """The same bytes as plain copies and nothing else: every input tensor host -> device on one stream, every
+        output tensor device -> host on another, both directions at once. The ceiling the host-buffer call is held to."""
+        import torch
+        dev_in = [torch.empty(t.shape, dtype=t.dtype, device="cuda") for t in self.inputs]
+        dev_out = [torch.empty(t.shape, dtype=t.dtype, device="cuda") for t in self.outputs]
+        up, down = torch.cuda.Stream(), torch.cuda.Stream()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def once():
+            up.wait_stream(torch.cuda.current_stream())
+            down.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(up):
+                for d, h in zip(dev_in, self.inputs):
+                    d.copy_(h, non_blocking=True)
+            with torch.cuda.stream(down):
+                for h, d in zip(self.outputs, dev_out):
+                    h.copy_(d, non_blocking=True)
+            torch.cuda.current_stream().wait_stream(up)
+            torch.cuda.current_stream().wait_stream(down)
+        once()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            once()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
 
 
 # ------------------------------------------------------------------------------------------------ CPU baseline
@@ -382,7 +436,28 @@ def emit(line):
         os.write(_REAL_STDOUT, data)
 
 
+def kernel_table(sw, per_kernel_ms, world, peak):
+    rows = []
+    for (name, _, nbytes, nrows, unit), ms in zip(sw.kernels, per_kernel_ms):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        rows.append({"name": name, "ms": ms, "rows_per_s": nrows * world / (ms * 1e-3), "rows": unit,
+                     "algorithmic_bytes_per_gpu": nbytes, "gbs_per_gpu": gbs, "gbs_all_gpus": gbs * world,
+                     "frac_of_measured_peak": gbs / peak, "frac_of_8tbs": gbs / NOMINAL_HBM_GBS})
+    return rows
+
+
+def sweeps_per_step(wl, T):
+    """Sweeps in one step: as many as bring a step's rows to about the rows of 8 sweeps of the full c5 batch on one
+    GPU (~80 ms of device time), from the rank's row count and row width alone."""
+    per_row = wl["E"] * 8 + wl["FF"] * 3 + (wl["n_q"] + wl["n_kv"]) * wl["D"] * 2
+    return max(1, min(4096, round(8 * 262144 * (5120 * 8 + 17408 * 3 + 48 * 128 * 2) / (T * per_row))))
+
+
 def main():
+    if "--micro" in sys.argv:   # the per-launcher table of the entry points around the sweep (microbench.py)
+        sys.argv.remove("--micro")
+        import microbench
+        return microbench.main()
     claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -395,10 +470,10 @@ def main():
                     help="strong: the configuration's rows are sharded over the GPUs; weak: every GPU gets all of them")
     ap.add_argument("--e2e-rows", type=int, default=16384, help="token rows per rank of the host-buffer measurement")
     ap.add_argument("--cpu-rows", type=int, default=0, help="token rows of the CPU sample (default: calibrated)")
-    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
-                    help="time the step as CUDA-graph replays (auto: when a step is shorter than 1 ms)")
+    ap.add_argument("--sweeps-per-step", type=int, default=0, help="default: chosen from the rank's rows (see sweeps_per_step)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the per-kernel tables of the other workloads")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -417,7 +492,7 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        dist.init_process_group("nccl", device_id=device)   # the harness's barrier and max-reduce only
     assert ops.gpu_ops_init("gpu_ops.co") == 0
 
     def barrier():
@@ -432,44 +507,53 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.tolist()
 
-    T_total = args.tokens or wl["T"]
-    if args.scaling == "strong":
-        lo, hi = shard(T_total, rank, world)
-    else:
-        lo, hi = rank * T_total, (rank + 1) * T_total
-        T_total = T_total * world
-    T = hi - lo
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    peak, peak_src = measured_peak()
+
+    def rank_rows(T_total):
+        if args.scaling == "strong":
+            lo, hi = shard(T_total, rank, world)
+            return lo, hi - lo, T_total
+        return rank * T_total, T_total, T_total * world
+
+    def time_sweeps(sw, steps, reps, flush=None, clocks=None):
+        """Times steps x reps sweeps between two barriers; returns (ms per step, ms per launch of each kernel), max over
+        ranks. Every launch sits between its own pair of events."""
+        nk = len(sw.kernels)
+        ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nk)]
+              for _ in range(steps * reps)]
+        barrier()
+        if clocks:
+            clocks.mark_begin()
+        start.record()
+        for i in range(steps * reps):
+            sw.step(ev[i], flush)
+        end.record()
+        barrier()
+        if clocks:
+            clocks.mark_end()
+        per_kernel = [sum(e[j][0].elapsed_time(e[j][1]) for e in ev) / len(ev) for j in range(nk)]
+        red = max_over_ranks([start.elapsed_time(end) / steps] + per_kernel)
+        return red[0], red[1:]
+
+    # ---- the headline workload
+    lo, T, T_total = rank_rows(args.tokens or wl["T"])
     sw = Sweep(wl, T, lo, device)
     nk = len(sw.kernels)
-    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nk)]
-          for _ in range(args.steps)]
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-
+    reps = args.sweeps_per_step or sweeps_per_step(wl, T)
+    warm = max(args.warmup, 3)
     clocks = ClockSampler(local)
     clocks.start()
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warm):
         sw.step()
     launches0 = ops.launch_count()
-    barrier()
-    clocks.mark_begin()
-    start.record()
-    for i in range(args.steps):
-        sw.step(ev[i])
-    end.record()
-    barrier()
-    clocks.mark_end()
+    ms_step, per_kernel_ms = time_sweeps(sw, args.steps, reps, clocks=clocks)
     clk = clocks.stop()
     launches = ops.launch_count() - launches0
-    ms_total = start.elapsed_time(end)
-    per_kernel_ms = [sum(ev[i][j][0].elapsed_time(ev[i][j][1]) for i in range(args.steps)) / args.steps for j in range(nk)]
-    red = max_over_ranks([ms_total] + per_kernel_ms)
-    ms_step = red[0] / args.steps
-    per_kernel_ms = red[1:]
-    # Latency-bound workloads (a step of a few microseconds of device work per kernel): the six launches of a step are
-    # captured once in a CUDA graph and the step is timed as graph replays, which takes the Python launch overhead out
-    # of the number. The per-kernel figures above stay those of the individual launches.
+    # A sweep of a few microseconds per kernel is bound by launch latency: it is also timed as replays of a CUDA graph
+    # of one sweep, which takes the host's launch cost out; that time becomes the step's.
     graph_ms = None
-    if args.graph == "on" or (args.graph == "auto" and ms_step < 1.0):
+    if ms_step / reps < 1.0:
         g = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -482,39 +566,32 @@ def main():
             g.replay()
         barrier()
         start.record()
-        for _ in range(args.steps):
+        for _ in range(args.steps * reps):
             g.replay()
         end.record()
         barrier()
-        launches += nk * args.steps
+        launches += nk * args.steps * reps
         graph_ms = max_over_ranks([start.elapsed_time(end)])[0] / args.steps
         ms_step = graph_ms
     if not wl.get("moe"):
         assert int(sw.bad.item()) == 2**31 - 1
+    kernels = kernel_table(sw, per_kernel_ms, world, peak)
+    dom = next(k for k in kernels if k["name"] == sw.dominant)
+    ratio, ratio_src = dram_traffic_ratio("swiglu_bf16" if wl["dtype"] == "bf16" else "swiglu_f32")
+    roof = {"kernel": dom["name"], "bound": "hbm", "achieved": dom["gbs_per_gpu"], "peak": peak, "unit": "GB/s",
+            "frac": dom["gbs_per_gpu"] / peak, "traffic": ratio * dom["algorithmic_bytes_per_gpu"] if ratio else None,
+            "traffic_source": ratio_src, "peak_source": f"of {peak_src}",
+            "algorithmic_bytes_per_launch": dom["algorithmic_bytes_per_gpu"], "ms_per_launch": dom["ms"]}
+    cache_note = ("every tensor of a sweep is larger than L2 (126 MB); no flush needed" if T * wl["E"] * sw_bytes(wl) > 126e6
+                  else "tensors near or below the L2 size: warm from the producing kernel, as in a forward pass")
+    table_dev, row_bytes = getattr(sw, "table", None), getattr(sw, "row_bytes", 0)
 
-    peak, peak_src = measured_peak()
-    kernels = []
-    roof = None
-    for (name, _, nbytes, rows, unit), ms in zip(sw.kernels, per_kernel_ms):
-        gbs = nbytes * world / (ms * 1e-3) / 1e9 if args.scaling == "strong" or True else 0
-        per_gpu_gbs = nbytes / (ms * 1e-3) / 1e9
-        kernels.append({"name": name, "ms": ms, "rows_per_s": rows * world / (ms * 1e-3), "rows": unit,
-                        "algorithmic_bytes_per_gpu": nbytes, "gbs_per_gpu": per_gpu_gbs, "gbs_all_gpus": gbs,
-                        "frac_of_measured_peak": per_gpu_gbs / peak, "frac_of_8tbs": per_gpu_gbs / NOMINAL_HBM_GBS})
-        if name == sw.dominant:
-            # DRAM bytes per algorithmic byte of the SwiGLU kernel from one ncu capture at 16,384 tokens
-            # (profiles/step_c5_16k_tokens_full.md: dram read + write = 1673.6 MB for 1711.3 MB algorithmic; the last
-            # writes of a launch are still in L2 when it ends). Traffic grows in proportion to the rows.
-            traffic = 0.978 * nbytes
-            roof = {"kernel": name, "bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s",
-                    "frac": per_gpu_gbs / peak, "traffic": traffic, "peak_source": f"of {peak_src}",
-                    "algorithmic_bytes_per_launch": nbytes, "ms_per_launch": ms}
-
-    # ---- end to end through the host-buffer calls
-    e2e = None
+    # ---- end to end through the host-buffer call
+    e2e, launches_e2e = None, 0
     if not args.no_e2e:
         Te = min(args.e2e_rows, T)
-        hs = HostSweep(wl, Te, lo, getattr(sw, "table", None), getattr(sw, "row_bytes", 0))
+        l0 = ops.launch_count()
+        hs = HostSweep(wl, Te, lo, table_dev, row_bytes)
         for _ in range(2):
             hs.step()
         barrier()
@@ -524,19 +601,71 @@ def main():
         end.record()
         barrier()
         ms_e2e = max_over_ranks([start.elapsed_time(end)])[0] / args.steps
+        launches_e2e = ops.launch_count() - l0
+        barrier()
+        ms_copy = max_over_ranks([hs.copy_only_ms(max(3, args.steps // 2))])[0]
         e2e = {"value": Te * world / (ms_e2e * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": hs.h2d * world,
                "d2h_bytes_per_step": hs.d2h * world, "rows_per_step": Te * world, "ms_per_step": ms_e2e,
-               "what": "every row input copied from page-locked host memory and every row output copied back, each "
-                       "step, through the b200_host_* calls (weights resident on the device)"}
-        launches_e2e = ops.launch_count() - launches0 - launches
+               "gbs_over_pcie": (hs.h2d + hs.d2h) * world / (ms_e2e * 1e-3) / 1e9,
+               "copy_only_ms": ms_copy, "copy_only_rows_per_s": Te * world / (ms_copy * 1e-3),
+               "frac_of_copy_only": ms_copy / ms_e2e,
+               "what": "one b200_host_layer_sweep call per step: every input row copied from page-locked host memory and "
+                       "every result row copied back inside the timed region (weights and the table resident on the "
+                       "device; the residual stream stays on the device between the ops); copy_only = the same bytes as "
+                       "plain copies in both directions at once, max over ranks"}
         hs.host.close()
         del hs
-    else:
-        launches_e2e = 0
+    del sw
+    torch.cuda.empty_cache()
+
+    # ---- the other workloads: per-kernel tables, every launch on cold inputs
+    others = {}
+    if not args.no_other_configs:
+        flush = torch.zeros(96 << 20, device=device, dtype=torch.int32)   # 384 MB, rewritten before every launch
+        for name in sorted(WORKLOADS):
+            if name == args.config:
+                continue
+            w2 = WORKLOADS[name]
+            lo2, T2, T2_total = rank_rows(w2["T"])
+            if T2 <= 0:
+                continue
+            s2 = Sweep(w2, T2, lo2, device)
+            for _ in range(3):
+                s2.step()
+            l0 = ops.launch_count()
+            _, pk = time_sweeps(s2, 5, 4, flush=flush)
+            launches += ops.launch_count() - l0
+            # the whole sweep back to back (warm L2, no events between the launches), as CUDA-graph replays
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                s2.step()
+                with torch.cuda.graph(g, stream=side):
+                    s2.step()
+            torch.cuda.current_stream().wait_stream(side)
+            n_rep = 50
+            for _ in range(3):
+                g.replay()
+            barrier()
+            start.record()
+            for _ in range(n_rep):
+                g.replay()
+            end.record()
+            barrier()
+            launches += len(s2.kernels) * n_rep
+            sweep_ms = max_over_ranks([start.elapsed_time(end)])[0] / n_rep
+            others[name] = {"workload": w2["name"], "dtype": w2["dtype"], "token_rows_total": T2_total, "token_rows_per_gpu": T2,
+                            "sweep_ms_graph_replay": sweep_ms, "rows_per_s": T2_total / (sweep_ms * 1e-3),
+                            "kernels": kernel_table(s2, pk, world, peak),
+                            "timing": "per kernel: CUDA events around single launches, L2 flushed (384 MB rewritten) "
+                                      "before each; sweep: 50 CUDA-graph replays back to back"}
+            del s2, g
+            torch.cuda.empty_cache()
+        del flush
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        del sw
         torch.cuda.empty_cache()
         rows = args.cpu_rows or cpu_sample_rows(wl, 4.0)
         cs, dt = time_cpu(wl, rows, 3, 1)
@@ -550,17 +679,18 @@ def main():
 
     if rank == 0:
         line = {
-            "metric": "layer-op sweep throughput (token rows/s)", "value": T_total / (ms_step * 1e-3), "unit": "rows/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "metric": "layer-op sweep throughput (token rows/s)", "value": T_total * reps / (ms_step * 1e-3), "unit": "rows/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": wl["dtype"],
             "data": "synthetic",
             "config": {"workload": f"{args.config}: {wl['name']}", "token_rows_total": T_total, "token_rows_per_gpu": T,
+                       "sweeps_per_step": reps, "ms_per_sweep": ms_step / reps,
                        "hidden": wl["E"], "ffn": wl["FF"], "heads": [wl["n_q"], wl["n_kv"], wl["D"]],
-                       "parallelism": f"row-sharded x{world}, no collective",
-                       "cache": "every tensor of a step is larger than L2 (126 MB); no flush needed" if T * wl["E"] * sw_bytes(wl) > 126e6
-                       else "working set near L2 size: latency-bound configuration"},
+                       "parallelism": f"row-sharded x{world}, no collective on the data path (NCCL carries only the "
+                                      f"harness's barrier and max-reduce)",
+                       "cache": cache_note},
             "step_timed_as": "cuda graph replay" if graph_ms is not None else "individual launches",
-            "kernels": kernels, "roofline": roof, "e2e": e2e, "cpu_baseline": cpu, "clocks": clk,
+            "kernels": kernels, "roofline": roof, "configs": others, "e2e": e2e, "cpu_baseline": cpu, "clocks": clk,
             "gpu_launches": launches, "gpu_launches_e2e": launches_e2e,
         }
         emit(line)

@@ -2,7 +2,7 @@
 MoE grouping / combine, strided SwiGLU / GEGLU, the Gemma-4 norm chains, KV-cache row writes (FP16, Q8_0, Q4_0, with
 the Hadamard rotation), the 16-bit and int8 side outputs, the soft cap.
 
-    python -m rocm_hip_b200.microbench [--tokens 65536] [--width 4096] [--iters 10] [--only REGEX]
+    python bench.py --micro [--tokens 65536] [--width 4096] [--iters 10] [--only REGEX]      (or: python microbench.py ...)
 
 One line per case: CUDA-event time per launch (after 3 warm-ups; every case streams more bytes than the 126 MB L2
 holds), the ALGORITHMIC bytes of the case (each input read once, each output written once, stated per case below),
@@ -17,7 +17,7 @@ import sys
 
 import torch
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 import rocm_hip_b200 as m  # noqa: E402
@@ -106,13 +106,19 @@ def cases(T, n):
     yield "rmsnorm + bf16 copy (one launch)", lambda: m.gpu_add_rmsnorm(x, None, None, w, o1, n, T, 1e-6, q8=qx), 10 * V
     yield "add+rmsnorm + bf16 copy (one launch)", lambda: m.gpu_add_rmsnorm(x, a, o2, w, o1, n, T, 1e-6, q8=qx), 18 * V
     yield "swiglu + bf16 copy (one launch)", lambda: m.gpu_swiglu(x, a, o1, V, q8=qx), 14 * V
-    yield "rmsnorm + bf16 copy + Q8_0/Q8_K (two launches)", lambda: m.gpu_add_rmsnorm(x, None, None, w, o1, n, T, 1e-6, q8=qa), (10 + 4 + 2.53) * V
+    # int8 formats written by the producer itself (one launch): + 1 (q0) + 1 (qK) + ~0.53 (scales, sums) bytes per value
+    yield "rmsnorm + bf16 copy + Q8_0/Q8_K (one launch)", lambda: m.gpu_add_rmsnorm(x, None, None, w, o1, n, T, 1e-6, q8=qa), (10 + 2.53) * V
+    yield "add+rmsnorm + bf16 copy + Q8_0/Q8_K (one launch)", lambda: m.gpu_add_rmsnorm(x, a, o2, w, o1, n, T, 1e-6, q8=qa), (18 + 2.53) * V
+    yield "swiglu + bf16 copy + Q8_0/Q8_K (one launch)", lambda: m.gpu_swiglu(x, a, o1, V, q8=qa), (14 + 2.53) * V
     # q/k norm + RoPE (bf16, 40 + 8 heads of 128): 2 bytes in and out per value; with the K heads written to the cache
     nq, nkv, D = 40, 8, 128
     qb, kb = R(T, nq * D).bfloat16(), R(T, nkv * D).bfloat16()
     qo, ko = torch.empty_like(qb), torch.empty_like(kb)
     qn, kn = 1 + 0.1 * R(D), 1 + 0.1 * R(D)
     kc = torch.zeros(T * nkv * D, device="cuda", dtype=torch.float16)
+    ct, st2 = torch.empty(T, D // 2, device="cuda"), torch.empty(T, D // 2, device="cuda")
+    yield "rope_table (64 pairs per token)", lambda: m.gpu_rope_table(None, 0, T, D, 0, 1e6, ct, st2), 8 * T * (D // 2)
+    yield "qk_norm_rope_tab (bf16, tables read)", lambda: m.gpu_qk_norm_rope_tab(qb, kb, qn, kn, qo, ko, nq, nkv, D, D, ct, st2, T, 1e-6), 4 * T * (nq + nkv) * D
     yield "qk_norm_rope (bf16)", lambda: m.gpu_qk_norm_rope(qb, kb, qn, kn, qo, ko, nq, nkv, D, D, 0, None, 0, T, 1e6, 1e-6), 4 * T * (nq + nkv) * D
     yield "qk_norm_rope_kv (bf16, K into the fp16 cache)", lambda: m.gpu_qk_norm_rope_kv(qb, kb, qn, kn, qo, kc, nkv * D, 30, 0, nq, nkv, D, D, 0, None, 0, T, 1e6, 1e-6), 4 * T * (nq + nkv) * D
     yield "qk_norm_rope + kv_store_f16 (two launches)", lambda: (m.gpu_qk_norm_rope(qb, kb, qn, kn, qo, ko, nq, nkv, D, D, 0, None, 0, T, 1e6, 1e-6), m.gpu_kv_store_f16(ko, kc, nkv * D, None, 0, T, nkv * D, 30, 0)), 4 * T * (nq + nkv) * D + 4 * T * nkv * D
@@ -138,6 +144,8 @@ def main():
     ap.add_argument("--width", type=int, default=4096, help="row width n (a multiple of 256, at most 4096)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default=None, help="regular expression on the case name")
+    ap.add_argument("--once", action="store_true",
+                    help="launch every selected case exactly once and time nothing (the run a profiler capture wraps)")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     assert m.gpu_ops_init("gpu_ops.co") == 0
@@ -145,6 +153,11 @@ def main():
     print("%-50s %10s %10s %9s %s" % ("case", "us", "MB", "GB/s", "of measured copy peak" if peak else ""))
     for name, fn, nbytes in cases(args.tokens, args.width):
         if args.only and not re.search(args.only, name):
+            continue
+        if args.once:
+            fn()
+            torch.cuda.synchronize()
+            print("%-50s launched once" % name)
             continue
         sec = time_launch(fn, args.iters)
         gbs = nbytes / sec / 1e9

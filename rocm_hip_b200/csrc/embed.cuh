@@ -146,6 +146,42 @@ k_embed_rows(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* t
     }
 }
 
+// The same load -> decode loop with a finer work unit: a warp takes one SLICE of a row (EMBED_SLICE_BYTES of blocks)
+// at a time, and consecutive warps take consecutive slices, so that the warps running at any moment read and write a
+// window of memory several times smaller than with a whole row per warp.
+#define EMBED_SLICE_BYTES 1440
+
+template <typename OUT, int TYPE>
+__global__ void __launch_bounds__(EMBED_WARPS * 32)
+k_embed_rows_sliced(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out, int E, long long T,
+                    float scale, int* bad_row) {
+    constexpr int BB = TYPE == B200_QT_Q8_0 ? 34 : 18;
+    constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;
+    constexpr int SB = EMBED_SLICE_BYTES / BB / 8 * 8;   // blocks per slice, a multiple of 8 (slices stay 16-byte aligned)
+    __shared__ __align__(16) uint8_t stage[EMBED_WARPS][SB * BB + 16];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    uint8_t* sm = stage[wid];
+    const int nb = E / 32, S = (nb + SB - 1) / SB;
+    const long long warp0 = (long long)blockIdx.x * EMBED_WARPS + wid, nwarps = (long long)gridDim.x * EMBED_WARPS;
+    for (long long i = warp0; i < T * S; i += nwarps) {
+        const long long t = i / S;
+        const int b0 = (int)(i - t * S) * SB, cb = min(SB, nb - b0);
+        const int tok = tokens[t];
+        OUT* o = out + (size_t)t * E + (size_t)b0 * 32;
+        if (tok < 0 || tok >= vocab) {
+            if (lane == 0 && b0 == 0) atomicMin(bad_row, (int)(t < 0x7fffffff ? t : 0x7ffffffe));
+            for (int c = lane * VPL; c < cb * 32; c += 32 * VPL) st_stream(o + c, make_uint4(0, 0, 0, 0));
+            continue;
+        }
+        const uint8_t* s = table + (size_t)tok * row_bytes + (size_t)b0 * BB;
+        const int nv = (cb * BB) >> 4;   // whole 16-byte vectors: cb is a multiple of 8
+        __syncwarp();  // the previous slice has been decoded
+        for (int v = lane; v < nv; v += 32) reinterpret_cast<uint4*>(sm)[v] = ld_stream(s + (size_t)v * 16);
+        __syncwarp();
+        embed_decode_chunk<OUT, TYPE>(sm, cb, o, scale, lane);
+    }
+}
+
 // The same gather with the row fetch overlapped with the decode. A warp owns EMBED_BULK_SLOTS shared-memory slices of
 // about 1.4 KB each and walks its tokens' rows slice by slice: while it decodes one slice, the bulk copies
 // of the next EMBED_BULK_SLOTS - 1 (one instruction each, issued by lane 0, completion counted on the slice's mbarrier)

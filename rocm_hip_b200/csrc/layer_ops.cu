@@ -155,11 +155,17 @@ cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const W
     if constexpr (std::is_same<WT, float>::value && !std::is_same<IO, __half>::value) {
         // exact fit of whole warps with gammas: the trimmed kernel
         if (vec && p.cta_row && w && p.tpr <= 512 && (n / VE) == p.tpr * p.vpt && (p.vpt == 2 || p.vpt == 4)) {
+// The residual variant runs one CTA per row (it has no loads in flight across rows, and CTAs that retire and are
+// replaced in row order keep the rows being read and written next to each other in memory: 1.04 of the copy bandwidth
+// on 262,144 rows of 5120 against 0.96 with a grid of resident CTAs walking strided rows). The plain norm keeps the
+// resident grid, whose CTAs fetch their next row while they reduce the current one (0.97 against 0.76).
 #define NORM_FAST3(V, A, M, XHV, Q8V, SIDE)                                                          \
     do {                                                                                             \
-        long long grid = persistent_grid(k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V>, p.tpr, 0);       \
+        const int rpc = (A) ? 1 : 0;                                                                 \
+        long long grid = rpc ? (T + rpc - 1) / rpc : persistent_grid(k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V>, p.tpr, 0); \
         if (grid > T) grid = T;                                                                      \
-        k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, SIDE); \
+        if (grid > INT_MAX) return cudaErrorInvalidValue;                                            \
+        k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, SIDE, rpc); \
     } while (0)
 #define NORM_FAST2(V, A, XHV, Q8V, SIDE)                                                             \
     do {                                                                                             \
@@ -233,7 +239,9 @@ cudaError_t launch_swiglu(const IO* g, const IO* u, IO* out, long long n, cudaSt
     if (al16(g) && al16(u) && al16(out)) {
         const long long nvec = n / VE, per_cta = 256LL * UNROLL;
         long long grid = (nvec + per_cta - 1) / per_cta;
-        const long long cap = resident_ctas(256) * 8;
+        // one tile per CTA: CTAs that retire and are replaced in tile order keep the tiles in flight next to each other
+        // in memory (1.07 of the copy bandwidth on the 27B-shape FFN rows against 1.01 with a capped grid walking tiles)
+        const long long cap = INT_MAX;
         if (grid > cap) grid = cap;
         if (grid < 1) grid = 1;
         if constexpr (std::is_same<IO, float>::value) {
@@ -272,7 +280,7 @@ cudaError_t launch_swiglu_rows(const IO* gate, const IO* up, IO* out, long long 
     constexpr int VE = Io<IO>::VE;
     const bool vec = h % VE == 0 && gs % VE == 0 && us % VE == 0 && al16(gate) && al16(up) && al16(out);
     const long long work = vec ? rows * (h / VE) : rows * (long long)h;
-    const long long cap = resident_ctas(256) * 8;
+    const long long cap = INT_MAX;   // one step per thread, CTAs in row order (as launch_swiglu)
     long long grid = (work + 255) / 256;
     if (grid > cap) grid = cap;
     if (vec) k_swiglu_strided_vec<IO, FAST><<<(unsigned)grid, 256, 0, stream>>>(gate, up, out, rows, h, gs, us);
@@ -513,24 +521,33 @@ cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int voca
         K<OUT, TY><<<(unsigned)(need < res ? need : res), EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, \
                                                                                          E, T, scale, bad_row, vec_ok);     \
     } while (0)
-    // Q8_0 / Q4_0 rows the copy engine can fetch whole (16-byte aligned table and row stride, rows of whole 8-block
-    // groups): the kernel that keeps two rows in flight per warp
-    // Q8_0 / Q4_0 rows the copy engine can fetch whole (16-byte aligned table and row stride, rows of whole 8-block
-    // groups) in a batch that gives a resident warp fewer than 8 tokens: the kernel that keeps several slices of a row
-    // in flight per warp (measured on Q4_0 rows of 2560 at 16,384 tokens: 0.84-0.93 of the copy bandwidth against 0.70).
-    // Longer batches take the load -> decode kernel, whose many warps per SM overlap each other's phases (262,144 rows
-    // of 5120: 0.91-0.93 against 0.86-0.88).
-    if ((type == B200_QT_Q8_0 || type == B200_QT_Q4_0) && vec_ok && E % 256 == 0 &&
-        T < 8LL * EMBED_WARPS * resident_ctas(EMBED_WARPS * 32) * 5 / 8) {
-        const long long need_b = (T + EMBED_BULK_WARPS - 1) / EMBED_BULK_WARPS;
+    // Q8_0 / Q4_0 rows of whole 8-block groups in a 16-byte aligned table (every GGUF token_embd of E % 256 == 0).
+    // Long batches: a warp per slice of a row, one slice per warp, CTAs retiring in slice order, so that what is read
+    // and written at any moment lies close together in memory (262,144 rows of 5120, fraction of the copy bandwidth:
+    // 1.00 against 0.91 for the whole-row kernel with a resident grid; Q4_0 rows of 2560: 0.93 against 0.84). Batches
+    // that give a resident warp fewer than 8 tokens: the kernel that keeps several slices of a row in flight per warp
+    // (16,384 Q4_0 rows of 2560: 0.84-0.93 against 0.70 and 0.82).
+    if ((type == B200_QT_Q8_0 || type == B200_QT_Q4_0) && vec_ok && E % 256 == 0) {
+        if (T < 8LL * EMBED_WARPS * resident_ctas(EMBED_WARPS * 32) * 5 / 8) {
+            const long long need_b = (T + EMBED_BULK_WARPS - 1) / EMBED_BULK_WARPS;
 #define EMBED_BULK(TY)                                                                                           \
     do {                                                                                                         \
         const long long res = persistent_grid(k_embed_rows_bulk<OUT, TY>, EMBED_BULK_WARPS * 32, 0);             \
         k_embed_rows_bulk<OUT, TY><<<(unsigned)(need_b < res ? need_b : res), EMBED_BULK_WARPS * 32, 0, stream>>>( \
             tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row);                                             \
     } while (0)
-        if (type == B200_QT_Q8_0) EMBED_BULK(B200_QT_Q8_0); else EMBED_BULK(B200_QT_Q4_0);
+            if (type == B200_QT_Q8_0) EMBED_BULK(B200_QT_Q8_0); else EMBED_BULK(B200_QT_Q4_0);
 #undef EMBED_BULK
+            return launched();
+        }
+        const int sb = EMBED_SLICE_BYTES / (type == B200_QT_Q8_0 ? 34 : 18) / 8 * 8;   // blocks per slice, as the kernel's
+        const long long slices = T * ((E / 32 + sb - 1) / sb);
+        long long grid = (slices + EMBED_WARPS - 1) / EMBED_WARPS;
+        if (grid > INT_MAX) grid = INT_MAX;
+        if (type == B200_QT_Q8_0)
+            k_embed_rows_sliced<OUT, B200_QT_Q8_0><<<(unsigned)grid, EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row);
+        else
+            k_embed_rows_sliced<OUT, B200_QT_Q4_0><<<(unsigned)grid, EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row);
         return launched();
     }
     switch (type) {

@@ -75,13 +75,9 @@ __device__ __forceinline__ void kv_put(const QkArgs& a, long long t, int e, cons
 // the CPU reference evaluates it (src/qwen_ops.cpp:21-22). The four products are two-wide multiplies; the sums are
 // scalar add.rn / sub.rn because the assembler contracts a two-wide multiply that feeds a two-wide add into a fused
 // multiply-add even when both carry .rn (measured: 26 % of results differ in the last bit), which it never does to
-// the scalar forms.
+// the scalar forms. (Writing the sums as fused multiply-adds by an opaque +1 / -1, which nothing can contract, gives the
+// same bits with fewer instructions, but measured 3 % slower in the table-reading tile kernel.)
 __device__ __forceinline__ void rotate2(f2 x0, f2 x1, f2 c, f2 s, float* lo, float* hi) {
-#ifdef B200_ROT_WIDE
-    upk2(sub2(mul2(x0, c), mul2(x1, s)), lo[0], lo[1]);
-    upk2(add2(mul2(x0, s), mul2(x1, c)), hi[0], hi[1]);
-    return;
-#endif
     float a0, a1, b0, b1, c0, c1, d0, d1;
     upk2(mul2(x0, c), a0, a1);
     upk2(mul2(x1, s), b0, b1);
@@ -396,15 +392,15 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
     __syncthreads();
 
     int flip = 0;
-    const long long ntiles = a.T / TT;
+    const long long ntiles = a.T / TT, tile0 = blockIdx.x, tstride = gridDim.x;
     // The tables of a tile are computed at the END of the pass before it (the first tile's here), into the buffer the
     // pass before that used: the double-precision sincos then runs while none of a pass's loaded vectors are live, so
     // its registers do not compete with them (computing the tables between the loads and their use cost 15 %).
-    if ((long long)blockIdx.x < ntiles) {
-        if (TAB) tile_tables_async(tab, tab + TT * half, a, (long long)blockIdx.x * TT, TT, PL, VE, half);
-        else tokens_cos_sin<true>(tab, tab + TT * half, a, invf, (long long)blockIdx.x * TT, TT, PL, VE);
+    if (tile0 < ntiles) {
+        if (TAB) tile_tables_async(tab, tab + TT * half, a, tile0 * TT, TT, PL, VE, half);
+        else tokens_cos_sin<true>(tab, tab + TT * half, a, invf, tile0 * TT, TT, PL, VE);
     }
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, flip ^= 1) {
+    for (long long tile = tile0; tile < ntiles; tile += tstride, flip ^= 1) {
         const long long t0 = tile * TT;
         const uint4* src = in_base + (size_t)t0 * in_vec;
         uint4* dst = out_base + (size_t)t0 * out_vec;
@@ -418,9 +414,9 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
         float* sin_t = cos_t + TT * half;
         if (TAB) cp_async_wait_all();   // this thread's copies of this tile's tables have landed
         __syncthreads();   // this tile's tables (written during the previous pass) are complete
-        if (TAB && tile + gridDim.x < ntiles) {   // the other buffer was last read one pass ago, before this barrier
+        if (TAB && tile + tstride < ntiles) {   // the other buffer was last read one pass ago, before this barrier
             float* ncos = tab + (flip ^ 1) * (2 * TT * half);
-            tile_tables_async(ncos, ncos + TT * half, a, (tile + gridDim.x) * TT, TT, PL, VE, half);
+            tile_tables_async(ncos, ncos + TT * half, a, (tile + tstride) * TT, TT, PL, VE, half);
         }
         const ulonglong2* ct = reinterpret_cast<const ulonglong2*>(cos_t) + l;   // chunk c of token tt: [(tt * half) / 4 + c * PL]
         const ulonglong2* st = reinterpret_cast<const ulonglong2*>(sin_t) + l;
@@ -467,9 +463,9 @@ k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
                 st_stream(dst + (tt * out_vec + (unsigned)vhi), Io<IO>::pack(fhi));
             }
         }
-        if (!TAB && tile + gridDim.x < ntiles) {   // the other buffer was last read one pass ago, before this pass's barrier
+        if (!TAB && tile + tstride < ntiles) {   // the other buffer was last read one pass ago, before this pass's barrier
             float* ncos = tab + (flip ^ 1) * (2 * TT * half);
-            tokens_cos_sin<true>(ncos, ncos + TT * half, a, invf, (tile + gridDim.x) * TT, TT, PL, VE);
+            tokens_cos_sin<true>(ncos, ncos + TT * half, a, invf, (tile + tstride) * TT, TT, PL, VE);
         }
     }
 }

@@ -116,7 +116,7 @@ k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int 
 template <typename IO, int VPT, bool HAS_ADD, int MAXT, bool XH = false, bool Q8 = false>
 __global__ void __launch_bounds__(MAXT, MAXT <= 160 ? 4 : MAXT <= 320 ? (Q8 ? 3 : 2) : 1)
 k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO* y, int n, long long T, float eps,
-                   const Q8Side side = Q8Side{}) {
+                   const Q8Side side = Q8Side{}, int rows_per_cta = 0) {
     static_assert(!(XH || Q8) || sizeof(IO) == 4, "the side outputs belong to fp32 rows");
     __shared__ Q8Half half_stat[Q8 ? 64 : 1];   // per 128 values of the row (n <= 8192)
     uint16_t* const xh = side.xh;
@@ -148,17 +148,22 @@ k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO*
             gam[j][2 * h + 1] = g.y;
         }
     }
-    size_t off = (size_t)blockIdx.x * row_vecs;
-    const size_t step = (size_t)gridDim.x * row_vecs;
+    // rows_per_cta > 0: CTA b takes the consecutive rows [b * rows_per_cta, (b + 1) * rows_per_cta) and retires (the grid
+    // covers T); 0: the CTAs of a resident grid walk rows b, b + gridDim.x, ...
+    const long long first = rows_per_cta ? (long long)blockIdx.x * rows_per_cta : (long long)blockIdx.x;
+    const long long last = rows_per_cta ? (first + rows_per_cta < T ? first + rows_per_cta : T) : T;
+    const long long rstride = rows_per_cta ? 1 : (long long)gridDim.x;
+    size_t off = (size_t)first * row_vecs;
+    const size_t step = (size_t)rstride * row_vecs;
     int flip = 0;
     // Without the residual a thread holds only VPT vectors, so the next row's loads are issued before this row's
     // reduction (two rows in flight per CTA); with it, x and add already double the bytes in flight.
     uint4 rn[VPT];
-    if (!HAS_ADD && (long long)blockIdx.x < T) {
+    if (!HAS_ADD && first < last) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) rn[j] = ld_stream(px + off + j * tpr);
     }
-    for (long long row = blockIdx.x; row < T; row += gridDim.x, off += step, flip ^= 1) {
+    for (long long row = first; row < last; row += rstride, off += step, flip ^= 1) {
         uint4 rx[VPT], ra[VPT];
         if (HAS_ADD) {
 #pragma unroll
@@ -169,7 +174,7 @@ k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO*
         } else {
 #pragma unroll
             for (int j = 0; j < VPT; ++j) rx[j] = rn[j];
-            if (row + gridDim.x < T) {
+            if (row + rstride < last) {
 #pragma unroll
                 for (int j = 0; j < VPT; ++j) rn[j] = ld_stream(px + off + step + j * tpr);
             }
