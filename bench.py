@@ -2,7 +2,7 @@
 """Benchmark of the fused layer-op path. One sweep = one pass of the layer's ops over one batch of synthetic rows
 (embedding gather -> RMSNorm -> cos/sin table -> q/k norm + RoPE -> residual add + RMSNorm -> SwiGLU -> residual add +
 RMSNorm), in the order a layer of the reference's forward pass issues them (src/qwen_model.cpp:980-990, 941-957). One
-step = `sweeps_per_step` sweeps back to back (as many as keep a step near 80 ms whatever the GPU count, so that the
+step = `sweeps_per_step` sweeps back to back (as many as keep a step near 30 ms whatever the GPU count, so that the
 timed region of K steps is long enough for the clock samples to mean something).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config c5|c4|c3|c2|c1] [--impl reference]
@@ -447,10 +447,11 @@ def kernel_table(sw, per_kernel_ms, world, peak):
 
 
 def sweeps_per_step(wl, T):
-    """Sweeps in one step: as many as bring a step's rows to about the rows of 8 sweeps of the full c5 batch on one
-    GPU (~80 ms of device time), from the rank's row count and row width alone."""
+    """Sweeps in one step: as many as bring a step's rows to about the rows of 3 sweeps of the full c5 batch on one
+    GPU (~30 ms of device time, so that 20 steps time 0.6 s whatever the GPU count), from the rank's row count and
+    row width alone."""
     per_row = wl["E"] * 8 + wl["FF"] * 3 + (wl["n_q"] + wl["n_kv"]) * wl["D"] * 2
-    return max(1, min(4096, round(8 * 262144 * (5120 * 8 + 17408 * 3 + 48 * 128 * 2) / (T * per_row))))
+    return max(1, min(4096, round(3 * 262144 * (5120 * 8 + 17408 * 3 + 48 * 128 * 2) / (T * per_row))))
 
 
 def main():
@@ -461,7 +462,7 @@ def main():
     claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", default="c5", choices=sorted(WORKLOADS))

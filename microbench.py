@@ -51,6 +51,11 @@ def cases(T, n):
     x, a, o1, o2, o3 = R(T, n), R(T, n), R(T, n), R(T, n), R(T, n)
     w, w1, w2, w3 = R(n), R(n), R(n), R(n)
     sc = torch.tensor([0.7], device="cuda")
+    # what the memory system gives plain library kernels at different read : write mixes (the denominators' context)
+    yield "torch copy_ (read 1 : write 1)", lambda: o1.copy_(x), 8 * V
+    yield "torch add (read 2 : write 1)", lambda: torch.add(x, a, out=o1), 12 * V
+    yield "torch sum (read only)", lambda: x.sum(), 4 * V
+    yield "torch zero_ (write only)", lambda: o1.zero_(), 4 * V
     # norm chains: inputs + outputs, 4 bytes each per value
     yield "add_normed", lambda: m.gpu_add_normed(x, a, w, sc, o1, n, T, 1e-6), 12 * V
     yield "gemma_attn_post", lambda: m.gpu_gemma_attn_post(x, a, w, o1, w1, o2, None, None, n, T, 1e-6), 16 * V
