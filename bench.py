@@ -33,7 +33,7 @@ sys.path.insert(0, ROOT)
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
-# Workloads (BASELINE.json configs): row counts and widths. c5 is the headline multi-GPU configuration.
+# Workloads: row counts and widths of the five benchmark configurations. c5 is the headline multi-GPU configuration.
 WORKLOADS = {
     "c5": dict(name="dense-27B-shape layer-op sweep", dtype="bf16", T=262144, E=5120, n_q=40, n_kv=8, D=128,
                n_rot=128, theta=1e6, FF=17408, qtype=8, vocab=151936, eps=1e-6),

@@ -114,7 +114,7 @@ def moe_routing(seed, name, T, n_expert, n_used):
     return ids, order
 
 
-# The five benchmark configurations (row counts and widths; see BASELINE.json)
+# The five benchmark configurations (row counts and widths of the reference's model shapes)
 CONFIGS = {
     "c1_qwen3_0p6b_fp32": dict(dtype="f32", T=2427, E=1024, n_q=16, n_kv=8, D=128, n_rot=128, theta=1e6, FF=3072,
                                qtype=8, vocab=151936, eps=1e-6, positions="range"),

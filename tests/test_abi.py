@@ -11,7 +11,8 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HEADER = os.path.join(ROOT, "include", "b200_layer_ops.h")
-REF = "/root/reference"
+# the reference's source tree: $REF, else a checkout named "reference" beside this repository (as oracle/Makefile)
+REF = os.environ.get("REF", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def declared_functions():

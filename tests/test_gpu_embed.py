@@ -175,3 +175,28 @@ def test_k_formats_need_whole_super_blocks(ops):
     assert e.value.code == 1
     with pytest.raises(ops.LayerOpError):
         ops.gpu_embed_rows(9, t, 64, 16, ids, out, 128, 4, 1.0)                 # ggml id 9 (Q8_1) is not a row format
+
+
+@pytest.mark.parametrize("qt,E", [(8, 2048), (2, 2560), (8, 256)])
+@pytest.mark.parametrize("T", [60, 50000])
+def test_every_batch_length_gives_the_oracle_rows(ops, oracle, qt, E, T):
+    """The launcher picks its kernel from the batch length and the row shape (a few tokens per resident warp: slices
+    of a row in flight as bulk copies; long batches: a warp per slice, one slice per warp; other shapes: whole-row
+    load -> decode). Whatever runs, every row is the oracle's to the bit, in fp32 and rounded once to bf16, and ids
+    out of range give zero rows and the first offending row index."""
+    vocab = 300
+    maker, okind = (synth.q8_0_table, oracle.Q8_0) if qt == 8 else (synth.q4_0_table, oracle.Q4_0)
+    table = maker(21, "len.tab", vocab, E)
+    ids = synth.randint(21, "len.ids", 0, T, 0, vocab).astype(np.int32)
+    _, want = oracle.embed_rows(okind, table, table.shape[1], vocab, ids, E)
+    got, bad = gather(ops, qt, table, vocab, ids, E)
+    assert bad == INT_MAX and np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    got16, bad = gather(ops, qt, table, vocab, ids, E, bf16=True)
+    assert bad == INT_MAX and np.array_equal(got16, oracle.f32_to_bf16(want).reshape(T, E))
+    ids2 = ids.copy()
+    ids2[[T // 3, T - 2]] = [vocab + 7, -1]
+    got, bad = gather(ops, qt, table, vocab, ids2, E)
+    assert bad == T // 3 and not got[T // 3].any() and not got[T - 2].any()
+    keep = np.ones(T, bool)
+    keep[[T // 3, T - 2]] = False
+    assert np.array_equal(got[keep].view(np.uint32), want[keep].view(np.uint32))
