@@ -157,11 +157,13 @@ cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const W
         if (vec && p.cta_row && w && p.tpr <= 512 && (n / VE) == p.tpr * p.vpt && (p.vpt == 2 || p.vpt == 4)) {
 // The residual variant runs one CTA per row (it has no loads in flight across rows, and CTAs that retire and are
 // replaced in row order keep the rows being read and written next to each other in memory: 1.04 of the copy bandwidth
-// on 262,144 rows of 5120 against 0.96 with a grid of resident CTAs walking strided rows). The plain norm keeps the
-// resident grid, whose CTAs fetch their next row while they reduce the current one (0.97 against 0.76).
+// on 262,144 rows of 5120 against 0.96 with a grid of resident CTAs walking strided rows); on narrow rows (two vectors
+// per thread) a CTA takes four consecutive rows and fetches the next while it reduces the current one (16,384 rows of
+// 2560: 0.86 against 0.75). The plain norm keeps the resident grid, whose CTAs fetch their next row while they reduce
+// the current one (0.97 against 0.76).
 #define NORM_FAST3(V, A, M, XHV, Q8V, SIDE)                                                          \
     do {                                                                                             \
-        const int rpc = (A) ? 1 : 0;                                                                 \
+        const int rpc = (A) ? ((V) <= 2 ? 4 : 1) : 0;                                                \
         long long grid = rpc ? (T + rpc - 1) / rpc : persistent_grid(k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V>, p.tpr, 0); \
         if (grid > T) grid = T;                                                                      \
         if (grid > INT_MAX) return cudaErrorInvalidValue;                                            \
@@ -522,13 +524,13 @@ cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int voca
                                                                                          E, T, scale, bad_row, vec_ok);     \
     } while (0)
     // Q8_0 / Q4_0 rows of whole 8-block groups in a 16-byte aligned table (every GGUF token_embd of E % 256 == 0).
-    // Long batches: a warp per slice of a row, one slice per warp, CTAs retiring in slice order, so that what is read
-    // and written at any moment lies close together in memory (262,144 rows of 5120, fraction of the copy bandwidth:
-    // 1.00 against 0.91 for the whole-row kernel with a resident grid; Q4_0 rows of 2560: 0.93 against 0.84). Batches
-    // that give a resident warp fewer than 8 tokens: the kernel that keeps several slices of a row in flight per warp
-    // (16,384 Q4_0 rows of 2560: 0.84-0.93 against 0.70 and 0.82).
+    // From 8192 tokens on: a warp per slice of a row, one slice per warp, CTAs retiring in slice order, so that what is
+    // read and written at any moment lies close together in memory (262,144 rows of 5120, fraction of the copy
+    // bandwidth: 1.00 against 0.91 for the whole-row kernel with a resident grid; Q4_0 rows of 2560: 0.93 against 0.84;
+    // single cold launches of 32,768 rows of 5120: 0.89 against 0.80 for the kernel below). Shorter batches: a resident
+    // grid whose warps keep several slices of a row in flight as bulk copies (2048 rows: 16.7 against 17.8 us).
     if ((type == B200_QT_Q8_0 || type == B200_QT_Q4_0) && vec_ok && E % 256 == 0) {
-        if (T < 8LL * EMBED_WARPS * resident_ctas(EMBED_WARPS * 32) * 5 / 8) {
+        if (T < 8192) {
             const long long need_b = (T + EMBED_BULK_WARPS - 1) / EMBED_BULK_WARPS;
 #define EMBED_BULK(TY)                                                                                           \
     do {                                                                                                         \

@@ -105,7 +105,8 @@ k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int 
 // each lane rounded as the scalar instruction would. Same summation order as k_add_rmsnorm is NOT promised: a row
 // width always maps to the same kernel, so a row's bits are still a function of the row alone.
 // MAXT: largest CTA the instance is launched with (160, 320 or 512 threads); CTAs of up to 160 threads are held to 96
-// registers so that four fit an SM, those of up to 320 to 102 so that two do.
+// registers so that four fit an SM (narrow rows of two vectors per thread to 48 / 80 so that eight / five do: a row of
+// theirs is only 5 KB in flight), those of up to 320 to 102 so that two do.
 // XH (fp32 rows only): y is also written rounded to bf16 (xh_bf16) or fp16 into xh, the 16-bit side copy the
 // reference's producers write for their matmul consumers (src/q8_device.h:37-43,58): 2 more bytes per value written
 // instead of a second kernel that reads y again.
@@ -114,7 +115,7 @@ k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int 
 // 8 neighbouring lanes of one of the thread's vectors, a Q8_K block the 64 consecutive vectors of two 32-lane groups,
 // whose keys meet in shared memory (one more CTA barrier per row). side: the xh pointer and the int8 outputs.
 template <typename IO, int VPT, bool HAS_ADD, int MAXT, bool XH = false, bool Q8 = false>
-__global__ void __launch_bounds__(MAXT, MAXT <= 160 ? 4 : MAXT <= 320 ? (Q8 ? 3 : 2) : 1)
+__global__ void __launch_bounds__(MAXT, MAXT <= 160 ? (VPT <= 2 && !XH && !Q8 ? (HAS_ADD ? 5 : 8) : 4) : MAXT <= 320 ? (Q8 ? 3 : 2) : 1)
 k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO* y, int n, long long T, float eps,
                    const Q8Side side = Q8Side{}, int rows_per_cta = 0) {
     static_assert(!(XH || Q8) || sizeof(IO) == 4, "the side outputs belong to fp32 rows");
@@ -156,16 +157,21 @@ k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO*
     size_t off = (size_t)first * row_vecs;
     const size_t step = (size_t)rstride * row_vecs;
     int flip = 0;
-    // Without the residual a thread holds only VPT vectors, so the next row's loads are issued before this row's
-    // reduction (two rows in flight per CTA); with it, x and add already double the bytes in flight.
-    uint4 rn[VPT];
-    if (!HAS_ADD && first < last) {
+    // Where a thread holds few vectors (no residual, or narrow rows of two vectors per thread) the next row's loads
+    // are issued before this row's reduction (two rows in flight per CTA); with the residual on rows of four vectors
+    // per thread, x and add already double the bytes in flight and a second row would cost an SM its fourth CTA.
+    constexpr bool PREFETCH = !HAS_ADD || VPT <= 2;
+    uint4 rn[PREFETCH ? VPT : 1], rna[PREFETCH && HAS_ADD ? VPT : 1];
+    if (PREFETCH && first < last) {
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) rn[j] = ld_stream(px + off + j * tpr);
+        for (int j = 0; j < VPT; ++j) {
+            rn[j] = ld_stream(px + off + j * tpr);
+            if (HAS_ADD) rna[j] = ld_stream(pa + off + j * tpr);
+        }
     }
     for (long long row = first; row < last; row += rstride, off += step, flip ^= 1) {
         uint4 rx[VPT], ra[VPT];
-        if (HAS_ADD) {
+        if (!PREFETCH) {
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 rx[j] = ld_stream(px + off + j * tpr);
@@ -173,10 +179,16 @@ k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO*
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < VPT; ++j) rx[j] = rn[j];
+            for (int j = 0; j < VPT; ++j) {
+                rx[j] = rn[j];
+                if (HAS_ADD) ra[j] = rna[j];
+            }
             if (row + rstride < last) {
 #pragma unroll
-                for (int j = 0; j < VPT; ++j) rn[j] = ld_stream(px + off + step + j * tpr);
+                for (int j = 0; j < VPT; ++j) {
+                    rn[j] = ld_stream(px + off + step + j * tpr);
+                    if (HAS_ADD) rna[j] = ld_stream(pa + off + step + j * tpr);
+                }
             }
         }
         double s0 = 0.0, s1 = 0.0;
