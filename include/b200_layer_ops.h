@@ -69,7 +69,11 @@ cudaError_t gpu_swiglu(const float* g, const float* u, float* out, int n, const 
  * tile_e / tile_start / tile_n (gpu_moe_max_tiles entries each), *n_tiles of them. n_expert <= 1024. Unlike the
  * reference, the order inside an expert's run is fixed too (ascending pair index). Batches of more than 8192 entries
  * are grouped by three launches over the whole device and need n_segments * n_expert ints of work memory: this entry
- * point takes it from a few slots inside the library, used in turn (see gpu_moe_group_scratch below). */
+ * point takes it from four slots inside the library (4 MiB each, part of the library image on every GPU that loads
+ * it), used in turn: at most four such groupings may be in flight on a device at once, a fifth overlapping call would
+ * share counters with the first; a CUDA-graph capture bakes the slot of its capture-time call into the graph, so
+ * replays may meet other users of that slot. Callers that cannot keep to that pass their own work memory
+ * (gpu_moe_group_scratch below). */
 #ifndef GPU_OPS_H
 static inline int gpu_moe_max_tiles(int T, int n_used, int n_expert, int tile) {
     const int n = T * n_used, bound = n_expert + n / tile;

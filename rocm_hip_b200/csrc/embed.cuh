@@ -6,10 +6,13 @@
 // fused with it; an embedding scale other than 1 is a second, separately rounded multiply (src/qwen_model.cpp:1409).
 //
 // Layout: table rows of E / 32 blocks (34 or 18 bytes each), row t at table + t * row_bytes; inside a row the fp16
-// scale and the payload are only 2-byte aligned. A warp takes one token at a time: it copies the row's bytes into its
-// own shared-memory slice (16-byte loads when the table base and row_bytes allow, else 2-byte loads), then decodes
-// from shared memory so that every global store is a full 16-byte vector and a warp writes 512 contiguous bytes.
-// Traffic per token: 4 (id) + row_bytes + E * s_out, the algorithmic minimum.
+// scale and the payload are only 2-byte aligned. A warp copies a row (or a slice of one) into its own shared-memory
+// slice, then decodes from shared memory so that every global store is a full 16-byte vector and a warp writes 512
+// contiguous bytes. Traffic per token: 4 (id) + row_bytes + E * s_out, the algorithmic minimum.
+// Three kernels share the decoder (embed_decode_chunk): k_embed_rows_sliced (long batches: a warp per 1.4 KB slice,
+// one slice per warp, CTAs retiring in slice order), k_embed_rows_bulk (short batches: a resident grid whose warps
+// keep four slices in flight as bulk copies), k_embed_rows (any alignment and E % 32 == 0: whole row per warp,
+// 16-byte loads when the table base and row_bytes allow, else 2-byte loads). The launcher picks by shape and length.
 // An id outside [0, vocab) never touches the table: its output row is zero-filled and the smallest offending row
 // index is recorded in *bad_row (initialised to INT_MAX by the launcher's caller) for the host to turn into an error.
 

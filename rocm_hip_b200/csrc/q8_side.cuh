@@ -7,8 +7,10 @@
 //          q = min(127, rint(iscale * x)), d = 1 / iscale, plus the sum of every 16 q
 // The int8 outputs are written only when qK is set (then q0, d0, s0, dK, bsK are all expected), xh only when set.
 // A last partial 256-value block (n a multiple of 32 only) gets its Q8_0 part and an incomplete Q8_K part, as in the
-// reference. Two forms: q8_block_value, one value per thread of a 256-thread group (the reference's shape, for a
-// kernel that has the value in a register), and k_q8_side, a warp per block over a vector in memory.
+// reference. Three forms: q8_block_value, one value per thread of a 256-thread group (the reference's shape, used by
+// the by-name kernels); q8v_phase_a / q8v_phase_b, for a producer whose threads hold 16-byte vectors of the finished
+// output (the norm and SwiGLU kernels write the side outputs themselves with it: one launch); and k_q8_side, a warp
+// per block over a vector in memory (for the producers that cannot).
 
 #ifndef B200_Q8_SIDE_CUH
 #define B200_Q8_SIDE_CUH

@@ -11,12 +11,13 @@
 // values is NV = D / VE 16-byte vectors, owned by NV / (2 PPT) threads. Each thread owns PPT pairs of vectors; a
 // rotating thread owns the vector of a rotation pair's low half and the vector of its high half, so the rotation
 // needs no exchange, the row is read once and written once (2 D s bytes per head), and the sum of squares is a
-// shuffle reduction inside the head's lanes. A tile's cos / sin (n_rot / 2 each per token) are computed once, in
-// double, into shared memory and shared by all heads.
-// Three kernels: k_qk_norm_rope_fast (long batches of the usual shapes: everything static, gammas and tables in
-// bank-conflict-free shared-memory layouts, the next tile's tables computed at the end of a pass, its own sincos);
-// k_qk_norm_rope (any vectorisable shape, any batch length, frequency factors); k_qk_norm_rope_generic (any head
-// size and alignment, scalar).
+// shuffle reduction inside the head's lanes. A tile's cos / sin (n_rot / 2 each per token) sit in shared memory,
+// shared by all heads: computed there once, in double, or (table route) copied there from the tables k_rope_table
+// filled once for the whole forward pass.
+// Four kernels: k_qk_norm_rope_fast (long batches of the usual shapes: everything static, gammas and tables in
+// bank-conflict-free shared-memory layouts; TAB: the next tile's tables fetched by cp.async one pass ahead, else
+// computed at the end of a pass with its own sincos); k_qk_norm_rope (any vectorisable shape, any batch length,
+// frequency factors); k_qk_norm_rope_generic (any head size and alignment, scalar); k_rope_table.
 
 #ifndef B200_QK_NORM_ROPE_CUH
 #define B200_QK_NORM_ROPE_CUH

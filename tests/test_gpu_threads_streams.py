@@ -52,3 +52,43 @@ def test_concurrent_threads_on_their_own_streams(ops):
     for b in (0, 1, 2, 3):
         for key in want[b]:
             assert torch.equal(want[b][key], got[b][key]), (b, key)
+
+
+def test_moe_group_work_memory_slots_with_three_callers(ops):
+    """gpu_moe_group without a scratch argument takes its work memory from four slots inside the library, used in
+    turn: up to four long groupings may be in flight on a device at once. Three threads, each on its own stream and
+    each waiting for its call before the next, stay inside that limit and must all get the single-thread result."""
+    E_, U, rows = 64, 4, 9000
+    g = torch.Generator(device="cuda").manual_seed(6)
+    ids = [torch.randint(0, E_, (rows, U), device="cuda", dtype=torch.int32, generator=g) for _ in range(3)]
+    torch.cuda.synchronize()
+
+    def group(i, stream):
+        res = None
+        with torch.cuda.stream(stream):
+            for _ in range(10):
+                m = ids[i].numel()
+                tok, pair = (torch.empty(m, dtype=torch.int32, device="cuda") for _ in range(2))
+                mt = ops.gpu_moe_max_tiles(rows, U, E_, 64)
+                ntl, te, ts, tn = (torch.zeros(kk, dtype=torch.int32, device="cuda") for kk in (1, mt, mt, mt))
+                ops.gpu_moe_group(ids[i], rows, U, E_, 64, tok, pair, ntl, te, ts, tn)      # the library's own slots
+                stream.synchronize()
+                res = (tok, pair, ntl, te, ts, tn)
+        return res
+
+    want = [group(i, torch.cuda.Stream()) for i in range(3)]
+    got = [None] * 3
+
+    def run(i):
+        got[i] = group(i, torch.cuda.Stream())
+    threads = [threading.Thread(target=run, args=(i,)) for i in range(3)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for i in range(3):
+        n_tiles = int(want[i][2].item())
+        assert int(got[i][2].item()) == n_tiles
+        assert torch.equal(want[i][0], got[i][0]) and torch.equal(want[i][1], got[i][1])
+        for k in (3, 4, 5):
+            assert torch.equal(want[i][k][:n_tiles], got[i][k][:n_tiles])
