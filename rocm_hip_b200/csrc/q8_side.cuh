@@ -156,6 +156,11 @@ __device__ __forceinline__ void q8v_phase_a(const float (&y)[NV][4], const unsig
         if (r == j || r == NV + j) am = __uint_as_float(am8[j]);
     const bool is_id = r < NV;
     const float quot = (r < 2 * NV && am != 0.0f) ? __fdiv_rn(is_id ? 127.0f : am, is_id ? am : 127.0f) : 0.0f;
+    // lane NV + j of a group writes slot j's scale and scaled sum: its own slot-j values pick the block (same 32-value
+    // block for all 8 lanes), and the writes are issued once, after the loop, instead of once per slot
+    int my_sum = 0;
+    unsigned my_i = 0u;
+    bool my_live = false;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         const float id0 = __shfl_sync(0xffffffffu, quot, (lane & 24) + j);
@@ -166,14 +171,14 @@ __device__ __forceinline__ void q8v_phase_a(const float (&y)[NV][4], const unsig
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 4);
-        if (live[j]) {
+        if (live[j])
             *reinterpret_cast<uint32_t*>(o.q0 + i[j]) =
                 __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
-            if (r == NV + j) {   // this lane holds amax / 127 of the block
-                o.d0[i[j] >> 5] = __half2float(__float2half_rn(quot));
-                o.s0[i[j] >> 5] = __float_as_int(__half2float(__float2half_rn(__fmul_rn(quot, (float)sum0))));
-            }
-        }
+        if (r == NV + j) { my_sum = sum0; my_i = i[j]; my_live = live[j]; }
+    }
+    if (my_live) {   // (only lanes NV .. 2 NV - 1 of a group: this lane holds amax / 127 of its block in quot)
+        o.d0[my_i >> 5] = __half2float(__float2half_rn(quot));
+        o.s0[my_i >> 5] = __float_as_int(__half2float(__float2half_rn(__fmul_rn(quot, (float)my_sum))));
     }
 }
 
