@@ -244,7 +244,7 @@ class HostSweep:
     and every result ends there, each step; the residual stream between the ops stays on the device, as the
     reference keeps it in place (s.x / s.x_alt, src/qwen_model.cpp:946-957)."""
 
-    def __init__(self, wl, T, row0, table_dev, row_bytes):
+    def __init__(self, wl, T, row0, table_dev, row_bytes, slot_bytes=256 << 20, n_slots=4):
         import torch
         import rocm_hip_b200 as ops
         self.wl, self.T, self.ops = wl, T, ops
@@ -254,7 +254,7 @@ class HostSweep:
         g = torch.Generator().manual_seed(4242 + row0)
         pin = lambda *shape, dtype=dt: torch.empty(*shape, dtype=dtype).pin_memory()
         rnd = lambda *shape: pin(*shape).copy_(torch.randn(*shape, generator=g).to(dt))
-        self.host = ops.HostRows(slot_bytes=32 << 20, n_slots=6)
+        self.host = ops.HostRows(slot_bytes=slot_bytes, n_slots=n_slots)
         self.w = (1 + 0.1 * torch.randn(E, generator=g)).float()
         self.calls = []
         H = self.host

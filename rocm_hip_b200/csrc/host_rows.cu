@@ -71,15 +71,30 @@ cudaError_t run_rows(b200_host_ctx* ctx, long long T, const RowBufs& io, F launc
     for (int i = 0; i < io.n_tmp; ++i) per_row += io.tmp_bpr[i];
     const size_t slack = kAlign * (size_t)(io.n_in + io.n_out + io.n_tmp);
     if (per_row == 0 || ctx->slot_bytes <= slack || (ctx->slot_bytes - slack) / per_row == 0) return cudaErrorInvalidValue;
-    long long chunk = (long long)((ctx->slot_bytes - slack) / per_row);
-    // at least two chunks per slot when the work allows, so the ring actually overlaps
-    const long long want = (T + 2 * (long long)ctx->slots.size() - 1) / (2 * (long long)ctx->slots.size());
-    if (chunk > want && want >= 64) chunk = want;
+    const long long cap = (long long)((ctx->slot_bytes - slack) / per_row);   // rows a slot holds
+    // Chunk sizes: the first chunk's copy in and the last chunk's copy out are not overlapped by anything, so the
+    // chunks start small, double up to what a slot holds and halve again towards the end; in between, large chunks
+    // keep the count of copies and launches (a fixed cost of some tens of microseconds per chunk) low.
+    std::vector<long long> sizes;
+    {
+        const long long r0 = cap / 16 > 64 ? cap / 16 : (cap < 64 ? cap : 64);
+        std::vector<long long> ramp;
+        long long left = T, step = r0;
+        while (step < cap && left > 4 * step) { ramp.push_back(step); left -= 2 * step; step *= 2; }
+        long long mid = step < cap ? step : cap;
+        // at least two chunks per slot when the work allows, so the ring actually overlaps
+        const long long want = (left + 2 * (long long)ctx->slots.size() - 1) / (2 * (long long)ctx->slots.size());
+        if (mid > want && want >= 64) mid = want;
+        sizes = ramp;
+        for (; left > 0; left -= mid) sizes.push_back(left < mid ? left : mid);
+        sizes.insert(sizes.end(), ramp.rbegin(), ramp.rend());
+    }
+    const long long chunk = cap;   // the slot's layout is that of its largest chunk
     cudaError_t err = cudaSuccess;
-    long long c = 0;
-    for (long long row0 = 0; row0 < T && err == cudaSuccess; row0 += chunk, ++c) {
-        const long long rows = T - row0 < chunk ? T - row0 : chunk;
-        const size_t s = (size_t)(c % (long long)ctx->slots.size());
+    long long row0 = 0;
+    for (size_t c = 0; c < sizes.size() && err == cudaSuccess; row0 += sizes[c], ++c) {
+        const long long rows = sizes[c];
+        const size_t s = c % ctx->slots.size();
         cudaStream_t st = ctx->streams[s];
         char* base = ctx->slots[s];
         void* din[kMaxBufs];
@@ -89,7 +104,7 @@ cudaError_t run_rows(b200_host_ctx* ctx, long long T, const RowBufs& io, F launc
         for (int i = 0; i < io.n_in; ++i) { din[i] = base + off; off += up((size_t)chunk * io.in_bpr[i]); }
         for (int i = 0; i < io.n_out; ++i) { dout[i] = base + off; off += up((size_t)chunk * io.out_bpr[i]); }
         for (int i = 0; i < io.n_tmp; ++i) { dtmp[i] = base + off; off += up((size_t)chunk * io.tmp_bpr[i]); }
-        if (c < (long long)ctx->slots.size() && ctx->consts_ready) err = cudaStreamWaitEvent(st, ctx->consts_ready, 0);
+        if (c < ctx->slots.size() && ctx->consts_ready) err = cudaStreamWaitEvent(st, ctx->consts_ready, 0);
         for (int i = 0; i < io.n_in && err == cudaSuccess; ++i)
             err = cudaMemcpyAsync(din[i], (const char*)io.in[i] + (size_t)row0 * io.in_bpr[i], (size_t)rows * io.in_bpr[i],
                                   cudaMemcpyHostToDevice, st);
