@@ -636,6 +636,26 @@ def main():
             l0 = ops.launch_count()
             _, pk = time_sweeps(s2, 5, 4, flush=flush)
             launches += ops.launch_count() - l0
+            # What a launch of this length can reach at all: a plain device copy (torch's copy kernel) of each kernel's
+            # algorithmic bytes, half read and half written, timed the same way (one launch between two events, L2
+            # flushed before it). Launch ramp and tail weigh the same on it.
+            copies = []
+            for (_, _, nbytes, _, _) in s2.kernels:
+                a_ = torch.empty(max(nbytes // 2, 16), device=device, dtype=torch.uint8)
+                b_ = torch.empty_like(a_)
+                ts = []
+                for i in range(8):
+                    flush.add_(1)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    b_.copy_(a_)
+                    e1.record()
+                    e1.synchronize()
+                    if i >= 3:
+                        ts.append(e0.elapsed_time(e1))
+                copies.append(sum(ts) / len(ts))
+                del a_, b_
+            copies = max_over_ranks(copies)
             # the whole sweep back to back (warm L2, no events between the launches), as CUDA-graph replays
             g = torch.cuda.CUDAGraph()
             side = torch.cuda.Stream()
@@ -660,7 +680,11 @@ def main():
                             "sweep_ms_graph_replay": sweep_ms, "rows_per_s": T2_total / (sweep_ms * 1e-3),
                             "kernels": kernel_table(s2, pk, world, peak),
                             "timing": "per kernel: CUDA events around single launches, L2 flushed (384 MB rewritten) "
-                                      "before each; sweep: 50 CUDA-graph replays back to back"}
+                                      "before each; sweep: 50 CUDA-graph replays back to back; same_bytes_copy_ms: a plain "
+                                      "device copy of the kernel's algorithmic bytes timed the same way"}
+            for krow, cms in zip(others[name]["kernels"], copies):
+                krow["same_bytes_copy_ms"] = cms
+                krow["frac_of_same_bytes_copy"] = cms / krow["ms"]
             del s2, g
             torch.cuda.empty_cache()
         del flush
