@@ -453,7 +453,9 @@ cudaError_t b200_host_group_embed_rows(b200_host_group* grp, int elem, int type,
 
 /* From a GGUF file to a device-resident table. The reference maps the file and lets kernels read weights in place
  * from unified memory (src/gguf_mmap.h:15-17; QuantWeight::row, src/inference_internal.h:33-40); here the mapping is
- * the source of one upload. A reader of the container layout only (GGUF version 2 / 3; no split files). Tensor byte
+ * the source of one upload. A reader of the container layout only (GGUF version 2 / 3). A split model
+ * (<prefix>-00001-of-0000N.gguf, split.count in its metadata) is opened by its first file, as the reference does
+ * (src/gguf_mmap.h:92-95): the tensors of all N files form one table, each file has its own mapping. Tensor byte
  * sizes are known for the row formats gpu_embed_rows decodes: F32 (0), F16 (1), Q4_0 (2), Q4_1 (3), Q5_0 (6), Q5_1 (7),
  * Q8_0 (8), Q4_K (12), Q5_K (13), Q6_K (14), BF16 (30); tensors of other types are listed with nbytes 0 and cannot be
  * uploaded. b200_gguf_open returns NULL for a missing, truncated or malformed file. */
@@ -463,7 +465,9 @@ void b200_gguf_close(b200_gguf* g);
 long long b200_gguf_n_tensors(const b200_gguf* g);
 unsigned b200_gguf_version(const b200_gguf* g);
 size_t b200_gguf_alignment(const b200_gguf* g);      /* general.alignment, default 32 */
-size_t b200_gguf_data_offset(const b200_gguf* g);    /* file offset of the data section */
+size_t b200_gguf_data_offset(const b200_gguf* g);    /* file offset of the data section (of the first file) */
+int b200_gguf_n_files(const b200_gguf* g);           /* 1, or the files of a split model */
+int b200_gguf_tensor_file(const b200_gguf* g, int idx);   /* which of them holds tensor idx (0: the one opened), or -1 */
 int b200_gguf_find_tensor(const b200_gguf* g, const char* name);   /* index, or -1 */
 /* Any out pointer may be NULL. ne: 4 extents (1 beyond n_dims); row_bytes: bytes of ne[0] values (qt_row_size);
  * host_data: the tensor's bytes inside the read-only mapping (valid until b200_gguf_close). Returns 0, or -1. */

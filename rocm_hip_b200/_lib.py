@@ -115,6 +115,8 @@ SIGNATURES = {
     "b200_gguf_version": (C.c_uint, [_p]),
     "b200_gguf_alignment": (_sz, [_p]),
     "b200_gguf_data_offset": (_sz, [_p]),
+    "b200_gguf_n_files": (_i, [_p]),
+    "b200_gguf_tensor_file": (_i, [_p, _i]),
     "b200_gguf_find_tensor": (_i, [_p, C.c_char_p]),
     "b200_gguf_tensor_info": (_i, [_p, _i, C.POINTER(C.c_char_p), C.POINTER(_i), C.POINTER(_i), C.POINTER(_ll * 4),
                                    C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_p)]),

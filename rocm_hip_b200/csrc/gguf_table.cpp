@@ -3,7 +3,9 @@
 // (src/gguf_mmap.h:15-17,92-100; QuantWeight, src/inference_internal.h:33-40); on B200 the table has to live in HBM,
 // so the mapping is the source of one upload. This is a reader of the public GGUF container layout (version 2 / 3:
 // header, typed key-value pairs, tensor infos, aligned data section), written for this one job; it is not the
-// reference's parser (no split files, no tokenizer arrays, no staging).
+// reference's parser (no tokenizer arrays, no staging). A split model (<prefix>-00001-of-0000N.gguf, opened by its
+// first file, as src/gguf_mmap.cpp:384-437 does) is read as one tensor table over N mappings; metadata comes from the
+// first file.
 //
 // Every read is bounds-checked against the file size: a truncated or malformed file makes b200_gguf_open fail
 // instead of faulting later.
@@ -11,6 +13,7 @@
 #include "b200_layer_ops.h"
 
 #include <fcntl.h>
+#include <stdio.h>
 #include <string.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -26,8 +29,9 @@ struct TensorInfo {
     std::string name;
     int type = -1, n_dims = 0;
     long long ne[4] = {1, 1, 1, 1};
-    uint64_t offset = 0;   // from the start of the data section
+    uint64_t offset = 0;   // from the start of the data section of its file
     size_t row_bytes = 0, nbytes = 0;
+    int part = 0;          // the file of a split model that holds it (0: the one opened)
 };
 
 struct KvEntry {
@@ -109,45 +113,51 @@ struct Reader {
 
 }  // namespace
 
-struct b200_gguf {
+struct FilePart {
     int fd = -1;
     const uint8_t* map = nullptr;
-    size_t size = 0;
-    uint32_t version = 0;
-    size_t alignment = 32, data_off = 0;
-    std::vector<TensorInfo> tensors;
-    std::vector<KvEntry> kv;
+    size_t size = 0, data_off = 0;
 };
 
-extern "C" {
+struct b200_gguf {
+    std::vector<FilePart> parts;   // one mapping per file of a split model
+    uint32_t version = 0;
+    size_t alignment = 32;
+    std::vector<TensorInfo> tensors;
+    std::vector<KvEntry> kv;       // of the first file
+    const uint8_t* data(const TensorInfo& t) const { return parts[(size_t)t.part].map + parts[(size_t)t.part].data_off + t.offset; }
+};
 
-void b200_gguf_close(b200_gguf* g) {
-    if (!g) return;
-    if (g->map) munmap(const_cast<uint8_t*>(g->map), g->size);
-    if (g->fd >= 0) close(g->fd);
-    delete g;
+namespace {
+
+constexpr int kMaxSplits = 64;   // the reference's limit (src/gguf_mmap.cpp:122)
+
+void close_part(FilePart& f) {
+    if (f.map) munmap(const_cast<uint8_t*>(f.map), f.size);
+    if (f.fd >= 0) close(f.fd);
+    f = FilePart();
 }
 
-b200_gguf* b200_gguf_open(const char* path) {
-    if (!path) return nullptr;
-    b200_gguf* g = new (std::nothrow) b200_gguf;
-    if (!g) return nullptr;
+// Maps one file and reads its header: the key-value entries into kv, the tensor infos (marked with part) appended to
+// tensors. alignment: in / out (a file's own general.alignment places its data section). false: missing, truncated or
+// malformed.
+bool read_file(const char* path, int part, FilePart& f, uint32_t* version, size_t* alignment, std::vector<KvEntry>& kv,
+               std::vector<TensorInfo>& tensors) {
     struct stat st;
-    g->fd = open(path, O_RDONLY);
-    if (g->fd < 0 || fstat(g->fd, &st) != 0 || st.st_size < 24) { b200_gguf_close(g); return nullptr; }
-    g->size = (size_t)st.st_size;
-    void* m = mmap(nullptr, g->size, PROT_READ, MAP_PRIVATE, g->fd, 0);
-    if (m == MAP_FAILED) { b200_gguf_close(g); return nullptr; }
-    g->map = (const uint8_t*)m;
+    f.fd = open(path, O_RDONLY);
+    if (f.fd < 0 || fstat(f.fd, &st) != 0 || st.st_size < 24) return false;
+    f.size = (size_t)st.st_size;
+    void* m = mmap(nullptr, f.size, PROT_READ, MAP_PRIVATE, f.fd, 0);
+    if (m == MAP_FAILED) return false;
+    f.map = (const uint8_t*)m;
 
-    Reader r{g->map, g->size};
+    Reader r{f.map, f.size};
     const uint32_t magic = r.get<uint32_t>();
-    g->version = r.get<uint32_t>();
+    *version = r.get<uint32_t>();
     const uint64_t n_tensors = r.get<uint64_t>(), n_kv = r.get<uint64_t>();
-    if (!r.ok || magic != 0x46554747u || g->version < 2 || g->version > 3 || n_tensors > (1u << 24) || n_kv > (1u << 24)) {
-        b200_gguf_close(g);
-        return nullptr;
-    }
+    if (!r.ok || magic != 0x46554747u || *version < 2 || *version > 3 || n_tensors > (1u << 24) || n_kv > (1u << 24))
+        return false;
+    size_t align = 32;
     for (uint64_t i = 0; i < n_kv && r.ok; ++i) {
         KvEntry e;
         e.key = r.str();
@@ -155,14 +165,16 @@ b200_gguf* b200_gguf_open(const char* path) {
         e.value_off = r.at;
         if (r.ok && e.key == "general.alignment" && e.type == 4 && r.need(4)) {   // (a file may end right after the type)
             uint32_t a;
-            memcpy(&a, g->map + r.at, 4);
-            if (a >= 1 && a <= (1u << 20) && (a & (a - 1)) == 0) g->alignment = a;
+            memcpy(&a, f.map + r.at, 4);
+            if (a >= 1 && a <= (1u << 20) && (a & (a - 1)) == 0) align = a;
         }
         r.skip_value(e.type);
-        if (r.ok) g->kv.push_back(std::move(e));
+        if (r.ok) kv.push_back(std::move(e));
     }
+    const size_t first = tensors.size();
     for (uint64_t i = 0; i < n_tensors && r.ok; ++i) {
         TensorInfo t;
+        t.part = part;
         t.name = r.str();
         t.n_dims = (int)r.get<uint32_t>();
         if (t.n_dims < 1 || t.n_dims > 4) { r.ok = false; break; }
@@ -186,22 +198,93 @@ b200_gguf* b200_gguf_open(const char* path) {
             t.row_bytes = rb;
             t.nbytes = nb;
         }
-        if (r.ok) g->tensors.push_back(std::move(t));
+        if (r.ok) tensors.push_back(std::move(t));
     }
-    if (!r.ok) { b200_gguf_close(g); return nullptr; }
-    g->data_off = (r.at + g->alignment - 1) / g->alignment * g->alignment;
-    for (const TensorInfo& t : g->tensors)   // a tensor of a known type must lie inside the file
-        if (t.nbytes && (g->data_off > g->size || t.offset > g->size - g->data_off || t.nbytes > g->size - g->data_off - t.offset)) {
+    if (!r.ok) return false;
+    f.data_off = (r.at + align - 1) / align * align;
+    for (size_t i = first; i < tensors.size(); ++i) {   // a tensor of a known type must lie inside its file
+        const TensorInfo& t = tensors[i];
+        if (t.nbytes && (f.data_off > f.size || t.offset > f.size - f.data_off || t.nbytes > f.size - f.data_off - t.offset))
+            return false;
+    }
+    *alignment = align;
+    return true;
+}
+
+// An integer key-value entry of any integer type (split.count and split.no are 16-bit in files llama.cpp writes)
+long long kv_int_or(const std::vector<KvEntry>& kv, const uint8_t* map, const char* key, long long def) {
+    for (const KvEntry& e : kv) {
+        if (e.key != key) continue;
+        const uint8_t* p = map + e.value_off;
+        switch (e.type) {
+            case 0: return *p;
+            case 1: return (int8_t)*p;
+            case 2: { uint16_t v; memcpy(&v, p, 2); return v; }
+            case 3: { int16_t v; memcpy(&v, p, 2); return v; }
+            case 4: { uint32_t v; memcpy(&v, p, 4); return v; }
+            case 5: { int32_t v; memcpy(&v, p, 4); return v; }
+            case 10: { uint64_t v; memcpy(&v, p, 8); return (long long)v; }
+            case 11: { int64_t v; memcpy(&v, p, 8); return v; }
+            default: return def;
+        }
+    }
+    return def;
+}
+
+}  // namespace
+
+extern "C" {
+
+void b200_gguf_close(b200_gguf* g) {
+    if (!g) return;
+    for (FilePart& f : g->parts) close_part(f);
+    delete g;
+}
+
+b200_gguf* b200_gguf_open(const char* path) {
+    if (!path) return nullptr;
+    b200_gguf* g = new (std::nothrow) b200_gguf;
+    if (!g) return nullptr;
+    g->parts.emplace_back();
+    if (!read_file(path, 0, g->parts[0], &g->version, &g->alignment, g->kv, g->tensors)) { b200_gguf_close(g); return nullptr; }
+    // a split model: the other files are named after the first (src/gguf_mmap.cpp:389-410), each must say which one it is
+    const long long count = kv_int_or(g->kv, g->parts[0].map, "split.count", 1);
+    if (count > 1) {
+        char suffix[40];
+        snprintf(suffix, sizeof(suffix), "-00001-of-%05d.gguf", (int)count);
+        const std::string first(path);
+        const size_t sl = strlen(suffix);
+        if (count > kMaxSplits || first.size() < sl || first.compare(first.size() - sl, sl, suffix) != 0) {
             b200_gguf_close(g);
             return nullptr;
         }
+        g->parts.reserve((size_t)count);
+        for (int i = 1; i < (int)count; ++i) {
+            char tail[40];
+            snprintf(tail, sizeof(tail), "-%05d-of-%05d.gguf", i + 1, (int)count);
+            const std::string part = first.substr(0, first.size() - sl) + tail;
+            g->parts.emplace_back();
+            std::vector<KvEntry> kv;
+            uint32_t version = 0;
+            size_t alignment = 32;
+            if (!read_file(part.c_str(), i, g->parts.back(), &version, &alignment, kv, g->tensors) ||
+                kv_int_or(kv, g->parts.back().map, "split.no", -1) != i) {
+                b200_gguf_close(g);
+                return nullptr;
+            }
+        }
+    }
     return g;
 }
 
 long long b200_gguf_n_tensors(const b200_gguf* g) { return g ? (long long)g->tensors.size() : 0; }
 unsigned b200_gguf_version(const b200_gguf* g) { return g ? g->version : 0; }
 size_t b200_gguf_alignment(const b200_gguf* g) { return g ? g->alignment : 0; }
-size_t b200_gguf_data_offset(const b200_gguf* g) { return g ? g->data_off : 0; }
+size_t b200_gguf_data_offset(const b200_gguf* g) { return g ? g->parts[0].data_off : 0; }
+int b200_gguf_n_files(const b200_gguf* g) { return g ? (int)g->parts.size() : 0; }
+int b200_gguf_tensor_file(const b200_gguf* g, int idx) {
+    return g && idx >= 0 && (size_t)idx < g->tensors.size() ? g->tensors[(size_t)idx].part : -1;
+}
 
 int b200_gguf_find_tensor(const b200_gguf* g, const char* name) {
     if (!g || !name) return -1;
@@ -220,7 +303,7 @@ int b200_gguf_tensor_info(const b200_gguf* g, int idx, const char** name, int* t
     if (ne) for (int d = 0; d < 4; ++d) ne[d] = t.ne[d];
     if (row_bytes) *row_bytes = t.row_bytes;
     if (nbytes) *nbytes = t.nbytes;
-    if (host_data) *host_data = t.nbytes ? g->map + g->data_off + t.offset : nullptr;
+    if (host_data) *host_data = t.nbytes ? g->data(t) : nullptr;
     return 0;
 }
 
@@ -234,14 +317,14 @@ static const KvEntry* find_kv(const b200_gguf* g, const char* key, uint32_t type
 int b200_gguf_kv_u32(const b200_gguf* g, const char* key, uint32_t* out) {
     const KvEntry* e = find_kv(g, key, 4);
     if (!e || !out) return -1;
-    memcpy(out, g->map + e->value_off, 4);
+    memcpy(out, g->parts[0].map + e->value_off, 4);
     return 0;
 }
 
 int b200_gguf_kv_f32(const b200_gguf* g, const char* key, float* out) {
     const KvEntry* e = find_kv(g, key, 6);
     if (!e || !out) return -1;
-    memcpy(out, g->map + e->value_off, 4);
+    memcpy(out, g->parts[0].map + e->value_off, 4);
     return 0;
 }
 
@@ -250,10 +333,10 @@ long long b200_gguf_kv_str(const b200_gguf* g, const char* key, char* buf, size_
     const KvEntry* e = find_kv(g, key, 8);
     if (!e) return -1;
     uint64_t n;
-    memcpy(&n, g->map + e->value_off, 8);
+    memcpy(&n, g->parts[0].map + e->value_off, 8);
     if (buf && cap) {
         const size_t c = n < cap - 1 ? (size_t)n : cap - 1;
-        memcpy(buf, g->map + e->value_off + 8, c);
+        memcpy(buf, g->parts[0].map + e->value_off + 8, c);
         buf[c] = 0;
     }
     return (long long)n;
@@ -266,7 +349,7 @@ cudaError_t b200_gguf_upload_tensor(const b200_gguf* g, int idx, void** dev_ptr,
     void* d = nullptr;
     cudaError_t e = cudaMalloc(&d, t.nbytes);
     if (e != cudaSuccess) return e;
-    e = cudaMemcpyAsync(d, g->map + g->data_off + t.offset, t.nbytes, cudaMemcpyHostToDevice, stream);
+    e = cudaMemcpyAsync(d, g->data(t), t.nbytes, cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) { cudaFree(d); return e; }
     *dev_ptr = d;
     return cudaSuccess;

@@ -3,7 +3,7 @@ import struct
 
 import numpy as np
 
-T_U32, T_F32, T_STR, T_ARR = 4, 6, 8, 9
+T_U16, T_U32, T_F32, T_STR, T_ARR = 2, 4, 6, 8, 9
 
 
 def _s(b):
@@ -18,6 +18,8 @@ def write_gguf(path, kv, tensors, alignment=32, version=3):
         out += _s(key) + struct.pack("<I", t)
         if t == T_U32:
             out += struct.pack("<I", v)
+        elif t == T_U16:
+            out += struct.pack("<H", v)
         elif t == T_F32:
             out += struct.pack("<f", v)
         elif t == T_STR:

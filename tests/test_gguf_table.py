@@ -8,7 +8,7 @@ import struct
 import numpy as np
 import pytest
 
-from gguf_writer import T_ARR, T_F32, T_STR, T_U32, write_gguf
+from gguf_writer import T_ARR, T_F32, T_STR, T_U16, T_U32, write_gguf
 from rocm_hip_b200 import _lib, synth
 
 
@@ -94,19 +94,29 @@ def test_malformed_files_are_refused(tmp_path):
 
 
 @pytest.mark.gpu
-def test_upload_and_gather(tmp_path, ops, oracle):
-    """File -> device table -> gpu_embed_rows: the rows decode to what the CPU decoder makes of the file's bytes."""
+@pytest.mark.parametrize("split", [False, True])
+def test_upload_and_gather(tmp_path, ops, oracle, split):
+    """File -> device table -> gpu_embed_rows: the rows decode to what the CPU decoder makes of the file's bytes; also
+    with the table in the second file of a split model."""
     import torch
     lib = _lib.load()
     vocab, E, T = 1000, 1024, 500
     q8 = synth.q8_0_table(1, "gg.up", vocab, E)
-    path = str(tmp_path / "up.gguf")
-    write_gguf(path, [("general.architecture", T_STR, "qwen3")], [("pad.weight", 0, (7,), np.zeros(7, np.float32)),
-                                                                    ("token_embd.weight", 8, (E, vocab), q8)])
+    arch = ("general.architecture", T_STR, "qwen3")
+    pad, table = ("pad.weight", 0, (7,), np.zeros(7, np.float32)), ("token_embd.weight", 8, (E, vocab), q8)
+    if split:
+        path = str(tmp_path / "up-00001-of-00002.gguf")
+        write_gguf(path, [arch, ("split.no", T_U16, 0), ("split.count", T_U16, 2)], [pad])
+        write_gguf(str(tmp_path / "up-00002-of-00002.gguf"), [arch, ("split.no", T_U16, 1), ("split.count", T_U16, 2)],
+                   [("other.weight", 0, (5,), np.ones(5, np.float32)), table], alignment=64)
+    else:
+        path = str(tmp_path / "up.gguf")
+        write_gguf(path, [arch], [pad, table])
     g = lib.b200_gguf_open(path.encode())
     assert g
     try:
         i = lib.b200_gguf_find_tensor(g, b"token_embd.weight")
+        assert lib.b200_gguf_n_files(g) == (2 if split else 1) and lib.b200_gguf_tensor_file(g, i) == (1 if split else 0)
         _, typ, _, ne, rb, nb, _ = info(lib, g, i)
         dptr = C.c_void_p()
         assert lib.b200_gguf_upload_tensor(g, i, C.byref(dptr), None) == 0 and dptr.value
