@@ -107,7 +107,8 @@ def test_upload_and_gather(tmp_path, ops, oracle, split):
     if split:
         path = str(tmp_path / "up-00001-of-00002.gguf")
         write_gguf(path, [arch, ("split.no", T_U16, 0), ("split.count", T_U16, 2)], [pad])
-        write_gguf(str(tmp_path / "up-00002-of-00002.gguf"), [arch, ("split.no", T_U16, 1), ("split.count", T_U16, 2)],
+        write_gguf(str(tmp_path / "up-00002-of-00002.gguf"),
+                   [arch, ("general.alignment", T_U32, 64), ("split.no", T_U16, 1), ("split.count", T_U16, 2)],
                    [("other.weight", 0, (5,), np.ones(5, np.float32)), table], alignment=64)
     else:
         path = str(tmp_path / "up.gguf")
