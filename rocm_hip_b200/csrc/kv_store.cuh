@@ -87,38 +87,19 @@ __device__ __forceinline__ void wht8(float (&x)[8], int N, float* xchg) {
     for (int e = 0; e < 8; ++e) x[e] = __fmul_rn(x[e], r);
 }
 
-// out = the transform of x in blocks of N, rows of any length that is a multiple of N (total values a multiple of N)
-template <typename IO>
-__global__ void __launch_bounds__(256)
-k_hadamard_rot(const IO* x, IO* out, long long n_total, int N) {
-    __shared__ float xchg[8 * 256];
-    const long long total = n_total / 8;
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i - threadIdx.x % 32 < total; i += stride) {
-        float v[8];
-        const bool live = i < total;
-        if (live) {
-            if (sizeof(IO) == 4) {
-                Io<float>::unpack(ld_stream(reinterpret_cast<const float*>(x) + i * 8), v);
-                Io<float>::unpack(ld_stream(reinterpret_cast<const float*>(x) + i * 8 + 4), v + 4);
-            } else {
-                Io<__nv_bfloat16>::unpack(ld_stream(reinterpret_cast<const __nv_bfloat16*>(x) + i * 8), v);
-            }
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = 0.0f;
-        }
-        wht8(v, N, xchg);
-        if (live) {
-            if (sizeof(IO) == 4) {
-                st_stream(reinterpret_cast<float*>(out) + i * 8, Io<float>::pack(v));
-                st_stream(reinterpret_cast<float*>(out) + i * 8 + 4, Io<float>::pack(v + 4));
-            } else {
-                st_stream(reinterpret_cast<__nv_bfloat16*>(out) + i * 8, Io<__nv_bfloat16>::pack(v));
-            }
-        }
-    }
-}
+// The quantisers' float -> int conversions without the conversion unit (a quarter-rate pipe that these kernels keep
+// busiest): for |t| < 2^22 the sum t + 1.5 * 2^23, rounded to nearest even, holds rint(t) in its low mantissa bits
+// (two's complement), exactly what __float2int_rn gives; for 0 <= u < 2^23 the sum u + 2^23 rounded DOWN holds
+// floor(u) = (int)u. The products of a block of finite values lie within [-127.001, 127.001] and [0.49, 16.51]. A
+// block with a non-finite value, or with a scale too small to invert in fp32, stores unspecified (in-range) bytes: the
+// C conversion of an infinite product is undefined, so there is nothing to match there.
+__device__ __forceinline__ uint32_t rint_low_bits(float t) { return __float_as_uint(__fadd_rn(t, 12582912.0f)); }
+__device__ __forceinline__ uint32_t floor_low_bits(float u) { return __float_as_uint(__fadd_rd(u, 8388608.0f)); }
+
+// Q4_0's scale source: the value of largest magnitude, the positive one on a +- tie (src/attention.hip:169-171), from
+// the block's largest and smallest value: the largest if it is at least as far from zero as the smallest, else the
+// smallest. (A block of zeros: max(+0, -0) is +0 whatever the order, as in the reference's max over the candidates.)
+__device__ __forceinline__ float q4_0_extreme(float vmax, float vmin) { return vmax >= -vmin ? vmax : vmin; }
 
 // Quantised cache rows (src/attention.hip:44-50, kvq_store :159-178): a row holds d_row values and then one fp16 scale
 // per 32 values; d_row = kv_stride * 32 / 17 (Q8_0) or kv_stride * 32 / 9 (Q4_0), kv_stride still in fp16 units.
@@ -167,17 +148,21 @@ k_kv_store_q(const IO* src, __half* cache, int n_vals, const int* positions, int
         for (int j = 0; j < U; ++j) {
             const long long i = i0 + j * stride;
             const bool live = i < total;
-            float amax = 0.0f;
+            // the block's extremes over its four lanes: Q8_0 needs the largest magnitude, Q4_0 the largest and the
+            // smallest value (q4_0_extreme)
+            float amax = 0.0f, vmax = x[j][0], vmin = x[j][0];
+            if (KQ == 1) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(x[j][e]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            float m = -INFINITY;
-            if (KQ == 2) {
+                for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(x[j][e]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            } else {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(x[j][e]) == amax ? x[j][e] : -INFINITY);
-                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                for (int e = 1; e < 8; ++e) { vmax = fmaxf(vmax, x[j][e]); vmin = fminf(vmin, x[j][e]); }
+                vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1));
+                vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, 1));
+                vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 2));
+                vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, 2));
             }
             if (!live) continue;
             const long long t = i / opr;
@@ -189,20 +174,18 @@ k_kv_store_q(const IO* src, __half* cache, int n_vals, const int* positions, int
                 const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
                 uint32_t w[2] = {0u, 0u};
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int q = d != 0.0f ? __float2int_rn(__fmul_rn(x[j][e], id)) : 0;
-                    w[e >> 2] |= (uint32_t)(q & 0xff) << (8 * (e & 3));
-                }
+                for (int e = 0; e < 8; ++e)
+                    w[e >> 2] |= (rint_low_bits(__fmul_rn(x[j][e], id)) & 0xffu) << (8 * (e & 3));
                 *reinterpret_cast<uint2*>(row + o * 8) = make_uint2(w[0], w[1]);
                 if ((o & 3) == 0) reinterpret_cast<__half*>(row + d_row)[o >> 2] = __float2half_rn(d);
             } else {
-                const float d = __fdiv_rn(m, -8.0f);
+                const float d = __fdiv_rn(q4_0_extreme(vmax, vmin), -8.0f);
                 const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
                 uint32_t w = 0u;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const int n = min(15, (int)(d != 0.0f ? __fadd_rn(__fmul_rn(x[j][e], id), 8.5f) : 8.0f));
-                    w |= (uint32_t)n << (8 * (e & 3) + 4 * (e >> 2));     // value e: byte e % 4, high nibble for e >= 4
+                    const uint32_t n = floor_low_bits(fminf(__fadd_rn(__fmul_rn(x[j][e], id), 8.5f), 15.5f)) & 0xfu;
+                    w |= n << (8 * (e & 3) + 4 * (e >> 2));     // value e: byte e % 4, high nibble for e >= 4
                 }
                 *reinterpret_cast<uint32_t*>(row + o * 4) = w;
                 if ((o & 3) == 0) reinterpret_cast<__half*>(row + d_row / 2)[o >> 2] = __float2half_rn(d);
@@ -211,12 +194,148 @@ k_kv_store_q(const IO* src, __half* cache, int n_vals, const int* positions, int
     }
 }
 
+// One Q8_0 block (values, scale) from 32 finished values of a lane. Returns d.
+__device__ __forceinline__ float q8_0_block_words(const float (&x)[32], uint32_t (&w)[8]) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) amax = fmaxf(amax, fabsf(x[e]));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        w[j] = 0u;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) w[j] |= (rint_low_bits(__fmul_rn(x[4 * j + e], id)) & 0xffu) << (8 * e);
+    }
+    return d;
+}
+
+// One Q4_0 block from 32 finished values of a lane: word j holds values 8 j .. 8 j + 7, byte k = value k (low nibble)
+// and k + 4 (high). Returns d. (d == 0: id = 0, every value stores floor(8.5) = 8, as the reference's 8.0f.)
+__device__ __forceinline__ float q4_0_block_words(const float (&x)[32], uint32_t (&w)[4]) {
+    float vmax = x[0], vmin = x[0];
+#pragma unroll
+    for (int e = 1; e < 32; ++e) { vmax = fmaxf(vmax, x[e]); vmin = fminf(vmin, x[e]); }
+    const float d = __fdiv_rn(q4_0_extreme(vmax, vmin), -8.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        w[j] = 0u;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const uint32_t n = floor_low_bits(fminf(__fadd_rn(__fmul_rn(x[8 * j + e], id), 8.5f), 15.5f)) & 0xfu;
+            w[j] |= n << (8 * (e & 3) + 4 * (e >> 2));
+        }
+    }
+    return d;
+}
+
+// The 32 blocks (of 32 values) a warp owns in one step, from global memory into the lanes: lane l gets block l in
+// x[0..31]. The warp reads its 4 KB (fp32) or 2 KB (16-bit) as consecutive 16-byte chunks, lane after lane, parks
+// them in its 4 KB of shared memory and each lane picks its block's chunks up from there. Chunk c of the span belongs
+// to lane c / CB (CB chunks per block) and is stored at chunk index c ^ s(owner), s chosen so that both the 8 lanes of
+// a store phase and the 8 lanes of a load phase hit 8 different 16-byte bank groups. Blocks at or beyond n_live
+// (counted from the warp's first block) read as zeros.
+template <typename IO>
+__device__ __forceinline__ void warp_blocks_load(const IO* src, long long first_block, long long n_live, float (&x)[32],
+                                                 uint4* tile) {
+    constexpr int CB = sizeof(IO) == 4 ? 8 : 4;   // 16-byte chunks per block
+    const int lane = threadIdx.x & 31;
+    const uint4* g = reinterpret_cast<const uint4*>(src) + first_block * CB;
+    uint4 v[CB];
+#pragma unroll
+    for (int j = 0; j < CB; ++j) {
+        const int c = lane + 32 * j;
+        v[j] = (c / CB) < n_live ? ld_stream(g + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int j = 0; j < CB; ++j) {
+        const int c = lane + 32 * j, owner = c / CB;
+        tile[c ^ (CB == 8 ? (owner & 7) : ((owner >> 1) & 3))] = v[j];
+    }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < CB; ++k) {
+        const uint4 r = tile[(CB * lane + k) ^ (CB == 8 ? (lane & 7) : ((lane >> 1) & 3))];
+        if (sizeof(IO) == 4) Io<float>::unpack(r, x + 4 * k);
+        else Io<__nv_bfloat16>::unpack(r, x + 8 * k);
+    }
+    __syncwarp();   // the tile is written again on the next step
+}
+
+// The way back: lane l's finished block, packed as CB chunks, through the same swizzled tile into consecutive chunks
+// of global memory.
+template <typename IO>
+__device__ __forceinline__ void warp_blocks_store(IO* dst, long long first_block, long long n_live, const float (&x)[32],
+                                                  uint4* tile) {
+    constexpr int CB = sizeof(IO) == 4 ? 8 : 4;
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int k = 0; k < CB; ++k) {
+        uint4 r;
+        if (sizeof(IO) == 4) r = Io<float>::pack(x + 4 * k);
+        else r = Io<__nv_bfloat16>::pack(x + 8 * k);
+        tile[(CB * lane + k) ^ (CB == 8 ? (lane & 7) : ((lane >> 1) & 3))] = r;
+    }
+    __syncwarp();
+    uint4* g = reinterpret_cast<uint4*>(dst) + first_block * CB;
+#pragma unroll
+    for (int j = 0; j < CB; ++j) {
+        const int c = lane + 32 * j, owner = c / CB;
+        const uint4 v = tile[c ^ (CB == 8 ? (owner & 7) : ((owner >> 1) & 3))];
+        if (owner < n_live) st_stream(g + c, v);
+    }
+    __syncwarp();
+}
+
+// The transform of wht8 on a lane's whole block of 32 values: stages 1 .. 16 inside the lane, stages 32 .. N / 2 one
+// shuffle per value between the N / 32 neighbouring lanes of a rotation block. Same operations in the same order per
+// value as the reference's butterflies (src/attention.hip:251-263), so the same bits.
+__device__ __forceinline__ void wht32(float (&x)[32], int N) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+        float y[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) y[e] = (e & s) ? __fsub_rn(x[e ^ s], x[e]) : __fadd_rn(x[e], x[e ^ s]);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) x[e] = y[e];
+    }
+    for (int s = 1; s < N / 32; s <<= 1) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+            const float y = __shfl_xor_sync(0xffffffffu, x[e], s);
+            x[e] = (lane & s) ? __fsub_rn(y, x[e]) : __fadd_rn(x[e], y);
+        }
+    }
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn((float)N));
+#pragma unroll
+    for (int e = 0; e < 32; ++e) x[e] = __fmul_rn(x[e], r);
+}
+
+// out = the transform of x in blocks of N (64 .. 512): a lane per 32 values, global memory read and written as the
+// warp's consecutive chunks (warp_blocks_load / _store). n_total a multiple of N.
+template <typename IO>
+__global__ void __launch_bounds__(128)
+k_hadamard_rot32(const IO* x, IO* out, long long n_total, int N) {
+    __shared__ uint4 tiles[4][256];
+    const int lane = threadIdx.x & 31;
+    const long long nblk = n_total / 32, stride = (long long)gridDim.x * blockDim.x;
+    for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b - lane < nblk; b += stride) {
+        float v[32];
+        warp_blocks_load<IO>(x, b - lane, nblk - (b - lane), v, tiles[threadIdx.x >> 5]);
+        wht32(v, N);
+        warp_blocks_store<IO>(out, b - lane, nblk - (b - lane), v, tiles[threadIdx.x >> 5]);
+    }
+}
+
 // The same rows with a lane owning a whole 32-value block (128 or 64 bytes read through L1, 32 or 16 bytes written as
-// 16-byte vectors): the block maximum needs no shuffle, and a rotation block of rot values is rot / 32 neighbouring
+// 16-byte vectors; fetching the warp's span as consecutive chunks and handing the blocks out through shared memory
+// measured 0.41 against 0.57 rotated and 0.53 against 0.98 for 16-bit Q8_0 rows: L1 serves a lane's run well): the block maximum needs no shuffle, and a rotation block of rot values is rot / 32 neighbouring
 // lanes, so only the stages from 32 up cross lanes (two shuffles per value at rot = 128 where the 8-per-lane form
 // needs four). Same operations in the same order per value, so the same bits. Needs rows that start on 16 bytes. The
 // launcher uses it for rotated rows and for 16-bit sources, where it is the faster of the two.
-template <typename IO, int KQ, bool ROT>
+template <typename IO, int KQ, bool ROT, bool COAL = false>
 __global__ void __launch_bounds__(128)
 k_kv_store_q32(const IO* src, __half* cache, int n_vals, const int* positions, int pos0, long long T, int kv_stride,
                int kv_shift, long long kv_bstride, int rot) {
@@ -226,7 +345,10 @@ k_kv_store_q32(const IO* src, __half* cache, int n_vals, const int* positions, i
     for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b - lane < nblk; b += stride) {
         const bool live = b < nblk;
         float x[32];
-        if (live) {
+        if (COAL) {
+            __shared__ uint4 tiles[COAL ? 4 : 1][COAL ? 256 : 1];
+            warp_blocks_load<IO>(src, b - lane, nblk - (b - lane), x, tiles[threadIdx.x >> 5]);
+        } else if (live) {
             if (sizeof(IO) == 4) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) Io<float>::unpack(__ldg(reinterpret_cast<const uint4*>(src) + b * 8 + j), x + 4 * j);
@@ -239,67 +361,22 @@ k_kv_store_q32(const IO* src, __half* cache, int n_vals, const int* positions, i
 #pragma unroll
             for (int e = 0; e < 32; ++e) x[e] = 0.0f;
         }
-        if (ROT) {
-#pragma unroll
-            for (int s = 1; s < 32; s <<= 1) {
-                float y[32];
-#pragma unroll
-                for (int e = 0; e < 32; ++e) y[e] = (e & s) ? __fsub_rn(x[e ^ s], x[e]) : __fadd_rn(x[e], x[e ^ s]);
-#pragma unroll
-                for (int e = 0; e < 32; ++e) x[e] = y[e];
-            }
-            for (int s = 1; s < rot / 32; s <<= 1) {
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const float y = __shfl_xor_sync(0xffffffffu, x[e], s);
-                    x[e] = (lane & s) ? __fsub_rn(y, x[e]) : __fadd_rn(x[e], y);
-                }
-            }
-            const float r = __fdiv_rn(1.0f, __fsqrt_rn((float)rot));
-#pragma unroll
-            for (int e = 0; e < 32; ++e) x[e] = __fmul_rn(x[e], r);
-        }
+        if (ROT) wht32(x, rot);
         if (!live) continue;
-        float amax = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 32; ++e) amax = fmaxf(amax, fabsf(x[e]));
         const long long t = b / bpr;
         const int blk = (int)(b - t * bpr);
         const int pos = positions ? positions[t] : pos0 + (int)t;
         uint8_t* row = reinterpret_cast<uint8_t*>(cache + kv_row(pos, kv_stride, kv_shift, kv_bstride));
         if (KQ == 1) {
-            const float d = __fdiv_rn(amax, 127.0f);
-            const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
             uint32_t w[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                w[j] = 0u;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int q = d != 0.0f ? __float2int_rn(__fmul_rn(x[4 * j + e], id)) : 0;
-                    w[j] |= (uint32_t)(q & 0xff) << (8 * e);
-                }
-            }
+            const float d = q8_0_block_words(x, w);
             uint4* o = reinterpret_cast<uint4*>(row + blk * 32);
             o[0] = make_uint4(w[0], w[1], w[2], w[3]);
             o[1] = make_uint4(w[4], w[5], w[6], w[7]);
             reinterpret_cast<__half*>(row + d_row)[blk] = __float2half_rn(d);
         } else {
-            float m = -INFINITY;
-#pragma unroll
-            for (int e = 0; e < 32; ++e) m = fmaxf(m, fabsf(x[e]) == amax ? x[e] : -INFINITY);
-            const float d = __fdiv_rn(m, -8.0f);
-            const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
             uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {   // word j: values 8 j .. 8 j + 7, byte k = value k (low) and k + 4 (high)
-                w[j] = 0u;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int n = min(15, (int)(d != 0.0f ? __fadd_rn(__fmul_rn(x[8 * j + e], id), 8.5f) : 8.0f));
-                    w[j] |= (uint32_t)n << (8 * (e & 3) + 4 * (e >> 2));
-                }
-            }
+            const float d = q4_0_block_words(x, w);
             *reinterpret_cast<uint4*>(row + blk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
             reinterpret_cast<__half*>(row + d_row / 2)[blk] = __float2half_rn(d);
         }

@@ -611,15 +611,17 @@ cudaError_t launch_kv_store_q(const IO* src, void* cache, int n_vals, const int*
     if (grid > cap) grid = cap;
     __half* c = reinterpret_cast<__half*>(cache);
     {   // Rotated rows and 16-bit sources take the block-per-lane kernel (measured on 262,144 x 1,024 values, fraction of
-        // the copy bandwidth, 8-per-lane -> block-per-lane: bf16 Q8_0 0.68 -> 0.99, bf16 Q4_0 0.47 -> 0.74, rotated fp32
-        // 0.52 -> 0.58 and 0.43 -> 0.57); fp32 sources without rotation stay on the 8-per-lane one (0.96 / 0.84 against
+        // the copy bandwidth, 8-per-lane -> block-per-lane: bf16 Q8_0 0.68 -> 1.03, bf16 Q4_0 0.47 -> 0.91, rotated fp32
+        // 0.52 -> 0.75 and 0.43 -> 0.67); fp32 sources without rotation stay on the 8-per-lane one (0.96 / 0.90 against
         // 0.79 / 0.75: a lane's 128-byte run costs the fp32 loads their sector efficiency)
         const bool ok32 = kv_stride % 8 == 0 && kv_bstride % 8 == 0 && al16(cache);
         if (ok32 && (rot || sizeof(IO) == 2)) {
             const long long nblk = T * (n_vals / 32), cap32 = resident_ctas(128) * 8;
             long long g32 = (nblk + 127) / 128;
             if (g32 > cap32) g32 = cap32;
-#define KVQ32(KQ, R) k_kv_store_q32<IO, KQ, R><<<(unsigned)g32, 128, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, rot)
+            // (rotated fp32 rows fetch the warp's span as consecutive chunks: 0.58 -> 0.75 and 0.54 -> 0.67; for 16-bit
+            // sources the lanes' own 64-byte runs are faster, 1.03 / 0.91 against 0.94 / 0.82)
+#define KVQ32(KQ, R) k_kv_store_q32<IO, KQ, R, (R && sizeof(IO) == 4)><<<(unsigned)g32, 128, 0, stream>>>(src, c, n_vals, positions, pos0, T, kv_stride, kv_shift, kv_bstride, rot)
             if (kv_quant == 1) { if (rot) KVQ32(1, true); else KVQ32(1, false); }
             else { if (rot) KVQ32(2, true); else KVQ32(2, false); }
 #undef KVQ32
@@ -638,10 +640,12 @@ cudaError_t launch_hadamard(const IO* x, IO* out, long long rows, int D, int N, 
     if (!g_ready.load(std::memory_order_acquire)) return cudaErrorInvalidDeviceFunction;
     if (!x || !out || rows <= 0 || D <= 0 || (N != 64 && N != 128 && N != 256 && N != 512) || D % N != 0 || !al16(x) || !al16(out))
         return cudaErrorInvalidValue;
-    const long long total = rows * D, cap = resident_ctas(256) * 8;
-    long long grid = (total / 8 + 255) / 256;
+    // a lane per 32 values, the warp's span read and written as consecutive chunks (measured against 8 values per lane
+    // with one more shuffle stage: blocks of 128 0.82 -> 0.97 of the copy bandwidth, blocks of 512 0.70 -> 0.85)
+    const long long total = rows * D, cap = resident_ctas(128) * 8;
+    long long grid = (total / 32 + 127) / 128;
     if (grid > cap) grid = cap;
-    k_hadamard_rot<IO><<<(unsigned)grid, 256, 0, stream>>>(x, out, total, N);
+    k_hadamard_rot32<IO><<<(unsigned)grid, 128, 0, stream>>>(x, out, total, N);
     return launched();
 }
 
