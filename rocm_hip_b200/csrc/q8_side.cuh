@@ -19,6 +19,14 @@
 
 namespace b200 {
 
+// rint(t) (ties to even, as __float2int_rn) for |t| < 2^22: the sum t + 1.5 * 2^23 holds it in its low mantissa bits
+// (two's complement), so the conversion is one add on the fp32 pipe instead of an instruction of the quarter-rate
+// conversion unit, which these quantisers otherwise keep busiest. The quantisers' products are within +-127.5 for
+// finite values; a vector with a non-finite value gets unspecified int8 values (the C conversion of an infinite
+// product is undefined, so there is nothing to match there).
+__device__ __forceinline__ int rint_small(float t) { return (int)__float_as_uint(__fadd_rn(t, 12582912.0f)) - 0x4B400000; }
+
+
 struct Q8Side {
     int8_t* q0;
     float* d0;
@@ -166,7 +174,7 @@ __device__ __forceinline__ void q8v_phase_a(const float (&y)[NV][4], const unsig
         const float id0 = __shfl_sync(0xffffffffu, quot, (lane & 24) + j);
         int q[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) q[e] = live[j] ? __float2int_rn(__fmul_rn(y[j][e], id0)) : 0;
+        for (int e = 0; e < 4; ++e) q[e] = live[j] ? rint_small(__fmul_rn(y[j][e], id0)) : 0;
         int sum0 = (q[0] + q[1]) + (q[2] + q[3]);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
@@ -200,8 +208,8 @@ __device__ __forceinline__ void q8v_phase_b(const float (&y)[NV][4], const unsig
         const float iscale = __shfl_sync(0xffffffffu, isc, j);
         int q[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-            q[e] = (live[j] && blk[j].am != 0u) ? min(127, __float2int_rn(__fmul_rn(iscale, y[j][e]))) : 0;
+        for (int e = 0; e < 4; ++e)   // min(127, rint(t)) = rint(min(t, 127))
+            q[e] = (live[j] && blk[j].am != 0u) ? rint_small(fminf(__fmul_rn(iscale, y[j][e]), 127.0f)) : 0;
         int s16 = (q[0] + q[1]) + (q[2] + q[3]);
         s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
         s16 += __shfl_xor_sync(0xffffffffu, s16, 2);
@@ -264,7 +272,7 @@ k_q8_side(const float* x, long long K, Q8Side o) {
         const float id0 = am != 0.0f ? __fdiv_rn(127.0f, am) : 0.0f;
         int q[8], sum0 = 0;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { q[e] = __float2int_rn(__fmul_rn(v[e], id0)); sum0 += q[e]; }
+        for (int e = 0; e < 8; ++e) { q[e] = rint_small(__fmul_rn(v[e], id0)); sum0 += q[e]; }
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
         if (active) {
@@ -294,7 +302,7 @@ k_q8_side(const float* x, long long K, Q8Side o) {
         if (ba != 0.0f) {
             iscale = __fdiv_rn(-127.0f, bv);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { q[e] = min(127, __float2int_rn(__fmul_rn(iscale, v[e]))); s8 += q[e]; }
+            for (int e = 0; e < 8; ++e) { q[e] = rint_small(fminf(__fmul_rn(iscale, v[e]), 127.0f)); s8 += q[e]; }
         } else {
 #pragma unroll
             for (int e = 0; e < 8; ++e) q[e] = 0;
