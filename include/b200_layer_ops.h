@@ -249,6 +249,19 @@ cudaError_t gpu_qk_norm_rope_kv_bf16(const uint16_t* qfull, const uint16_t* k, c
                                      int pos0, long long T, float freq_base, float eps, int gated, int qk_norm,
                                      const float* freq_factors, cudaStream_t stream);
 
+/* The two combined: cos / sin from the tables of gpu_rope_table (row t = token t), K into the FP16 cache at row
+ * positions[t] (or pos0 + t). The same bits as gpu_qk_norm_rope_kv given the same angles. */
+cudaError_t gpu_qk_norm_rope_tab_kv(const float* qfull, const float* k, const float* q_norm, const float* k_norm,
+                                    float* q_out, uint16_t* k_cache, int kv_stride, int kv_shift, long long kv_bstride,
+                                    int n_q, int n_kv, int head_dim, int n_rot, const float* cos_tab, const float* sin_tab,
+                                    const int* positions, int pos0, long long T, float eps, int gated, int qk_norm,
+                                    cudaStream_t stream);
+cudaError_t gpu_qk_norm_rope_tab_kv_bf16(const uint16_t* qfull, const uint16_t* k, const float* q_norm, const float* k_norm,
+                                         uint16_t* q_out, uint16_t* k_cache, int kv_stride, int kv_shift,
+                                         long long kv_bstride, int n_q, int n_kv, int head_dim, int n_rot,
+                                         const float* cos_tab, const float* sin_tab, const int* positions, int pos0,
+                                         long long T, float eps, int gated, int qk_norm, cudaStream_t stream);
+
 /* The whole first stage of the reference's attention for an FP16 cache (attn_prep, src/attention.hip:266-300, without
  * biases, V norm and interleaved pairs): gpu_qk_norm_rope_kv for q and K, then the V rows (v [T][n_kv * head_dim]) into
  * V; two launches on `stream`. K and V are the layer's row 0 of the two halves of the cache. */

@@ -126,6 +126,7 @@ def cases(T, n):
     yield "qk_norm_rope_tab (bf16, tables read)", lambda: m.gpu_qk_norm_rope_tab(qb, kb, qn, kn, qo, ko, nq, nkv, D, D, ct, st2, T, 1e-6), 4 * T * (nq + nkv) * D
     yield "qk_norm_rope (bf16)", lambda: m.gpu_qk_norm_rope(qb, kb, qn, kn, qo, ko, nq, nkv, D, D, 0, None, 0, T, 1e6, 1e-6), 4 * T * (nq + nkv) * D
     yield "qk_norm_rope_kv (bf16, K into the fp16 cache)", lambda: m.gpu_qk_norm_rope_kv(qb, kb, qn, kn, qo, kc, nkv * D, 30, 0, nq, nkv, D, D, 0, None, 0, T, 1e6, 1e-6), 4 * T * (nq + nkv) * D
+    yield "qk_norm_rope_tab_kv (bf16, tables read, K into the fp16 cache)", lambda: m.gpu_qk_norm_rope_tab_kv(qb, kb, qn, kn, qo, kc, nkv * D, 30, 0, nq, nkv, D, D, ct, st2, None, 0, T, 1e-6), 4 * T * (nq + nkv) * D
     yield "qk_norm_rope + kv_store_f16 (two launches)", lambda: (m.gpu_qk_norm_rope(qb, kb, qn, kn, qo, ko, nq, nkv, D, D, 0, None, 0, T, 1e6, 1e-6), m.gpu_kv_store_f16(ko, kc, nkv * D, None, 0, T, nkv * D, 30, 0)), 4 * T * (nq + nkv) * D + 4 * T * nkv * D
     # KV rows: 1024 values per token row (8 heads x 128), 4 T rows
     nv, Tk = 1024, 4 * T

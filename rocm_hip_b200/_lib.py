@@ -81,6 +81,8 @@ SIGNATURES = {
     "gpu_rope_table": (_i, [_p, _i, _ll, _i, _i, _f, _p, _p, _p, _p]),
     "gpu_qk_norm_rope_tab": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _ll, _f, _i, _i, _p]),
     "gpu_qk_norm_rope_tab_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p, _ll, _f, _i, _i, _p]),
+    "gpu_qk_norm_rope_tab_kv": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _p, _p, _p, _i, _ll, _f, _i, _i, _p]),
+    "gpu_qk_norm_rope_tab_kv_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _p, _p, _p, _i, _ll, _f, _i, _i, _p]),
     "gpu_qk_norm_rope_kv": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_qk_norm_rope_kv_bf16": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),
     "gpu_attn_prep_f16": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _ll, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p, _p]),

@@ -431,15 +431,15 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
         QkArgs m = a;
         m.T = tiles * FTT;
         bool done = false;
-        if constexpr (!KVC) {
+        {
             if (tab) {
 #define QK_TAB(TTV, FULLV, MINB, DSV, NRV)                                                                            \
     do {                                                                                                              \
         const long long tl = T / TTV;                                                                                 \
         const size_t sm = (2 * (size_t)D + 2 * 2 * TTV * (size_t)(n_rot / 2)) * sizeof(float);                        \
         m.T = tl * TTV;                                                                                               \
-        const long long res = persistent_grid(k_qk_norm_rope_fast<IO, TTV, FULLV, false, true, MINB, DSV, NRV>, block, sm); \
-        k_qk_norm_rope_fast<IO, TTV, FULLV, false, true, MINB, DSV, NRV><<<(unsigned)(tl < res ? tl : res), block, sm, stream>>>(m, fr); \
+        const long long res = persistent_grid(k_qk_norm_rope_fast<IO, TTV, FULLV, KVC, true, MINB, DSV, NRV>, block, sm); \
+        k_qk_norm_rope_fast<IO, TTV, FULLV, KVC, true, MINB, DSV, NRV><<<(unsigned)(tl < res ? tl : res), block, sm, stream>>>(m, fr); \
     } while (0)
                 if (D == 128 && n_rot == 128) QK_TAB(4, true, 2, 128, 128);         // the heads of the dense configurations
                 else if (D == 256 && n_rot == 64) QK_TAB(4, false, 2, 256, 64);    // partial rotary over the first 64 of 256
@@ -1200,6 +1200,31 @@ cudaError_t gpu_qk_norm_rope_tab_bf16(const uint16_t* qfull, const uint16_t* k, 
                                     reinterpret_cast<__nv_bfloat16*>(q_out), reinterpret_cast<__nv_bfloat16*>(k_out),
                                     n_q, n_kv, head_dim, n_rot, 0, nullptr, 0, T, 1.0f, eps, gated, qk_norm, nullptr, stream,
                                     KvTarget{nullptr, 0, 0, 0}, &tabs);
+}
+
+cudaError_t gpu_qk_norm_rope_tab_kv(const float* qfull, const float* k, const float* q_norm, const float* k_norm,
+                                    float* q_out, uint16_t* k_cache, int kv_stride, int kv_shift, long long kv_bstride,
+                                    int n_q, int n_kv, int head_dim, int n_rot, const float* cos_tab, const float* sin_tab,
+                                    const int* positions, int pos0, long long T, float eps, int gated, int qk_norm,
+                                    cudaStream_t stream) {
+    const RopeTables tabs = {cos_tab, sin_tab};
+    return launch_qk<float, true>(qfull, k, q_norm, k_norm, q_out, nullptr, n_q, n_kv, head_dim, n_rot, 0, positions, pos0, T,
+                                  1.0f, eps, gated, qk_norm, nullptr, stream,
+                                  KvTarget{reinterpret_cast<__half*>(k_cache), kv_stride, kv_shift, kv_bstride}, &tabs);
+}
+
+cudaError_t gpu_qk_norm_rope_tab_kv_bf16(const uint16_t* qfull, const uint16_t* k, const float* q_norm, const float* k_norm,
+                                         uint16_t* q_out, uint16_t* k_cache, int kv_stride, int kv_shift,
+                                         long long kv_bstride, int n_q, int n_kv, int head_dim, int n_rot,
+                                         const float* cos_tab, const float* sin_tab, const int* positions, int pos0,
+                                         long long T, float eps, int gated, int qk_norm, cudaStream_t stream) {
+    const RopeTables tabs = {cos_tab, sin_tab};
+    return launch_qk<__nv_bfloat16, true>(reinterpret_cast<const __nv_bfloat16*>(qfull),
+                                          reinterpret_cast<const __nv_bfloat16*>(k), q_norm, k_norm,
+                                          reinterpret_cast<__nv_bfloat16*>(q_out), nullptr, n_q, n_kv, head_dim, n_rot, 0,
+                                          positions, pos0, T, 1.0f, eps, gated, qk_norm, nullptr, stream,
+                                          KvTarget{reinterpret_cast<__half*>(k_cache), kv_stride, kv_shift, kv_bstride},
+                                          &tabs);
 }
 
 cudaError_t gpu_qk_norm_rope_kv(const float* qfull, const float* k, const float* q_norm, const float* k_norm, float* q_out,

@@ -13,7 +13,7 @@ from . import _lib
 
 __all__ = [
     "LayerOpError", "gpu_ops_init", "gpu_ops_free", "gpu_add_rmsnorm", "gpu_swiglu", "gpu_swiglu_rows",
-    "gpu_qk_norm_rope", "gpu_rope_table", "gpu_qk_norm_rope_tab", "gpu_qk_norm_rope_kv", "gpu_attn_prep_f16", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_mamba_conv", "gpu_mamba_scan", "gpu_ple_conv", "gpu_hc_norm", "gpu_hc_lowrank", "gpu_hc_mix", "gpu_ple_gate", "gpu_mtp_concat", "gpu_mamba_gnorm", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
+    "gpu_qk_norm_rope", "gpu_rope_table", "gpu_qk_norm_rope_tab", "gpu_qk_norm_rope_tab_kv", "gpu_qk_norm_rope_kv", "gpu_attn_prep_f16", "gpu_embed_rows", "gpu_moe_group", "gpu_moe_group_scratch_ints", "gpu_moe_max_tiles", "gpu_kv_store_f16", "gpu_kv_store_q", "gpu_hadamard_rot", "gpu_add_normed", "gpu_gemma_attn_post", "gpu_geglu", "gpu_softcap", "gpu_gemma_ffn_post", "gpu_moe_combine", "gpu_moe_router", "gpu_moe_router_sigmoid", "gpu_relu2", "gpu_mamba_conv", "gpu_mamba_scan", "gpu_ple_conv", "gpu_hc_norm", "gpu_hc_lowrank", "gpu_hc_mix", "gpu_ple_gate", "gpu_mtp_concat", "gpu_mamba_gnorm", "gpu_rmsnorm_f16", "gpu_rope_rotate_half_f16", "launch_count", "Q8Buffers",
     "QT_Q4_0", "QT_Q8_0", "QT_F32", "QT_F16", "QT_BF16", "QT_Q4_1", "QT_Q5_0", "QT_Q5_1", "QT_Q4_K", "QT_Q5_K", "QT_Q6_K",
     "QT_BLOCKS", "qt_row_size", "HostRows", "HostGroup",
 ]
@@ -343,6 +343,18 @@ def gpu_qk_norm_rope_kv(qfull, k, q_norm, k_norm, q_out, k_cache, kv_stride, kv_
            fn(_ptr(qfull), _ptr(k), _ptr(q_norm), _ptr(k_norm), _ptr(q_out), _ptr(k_cache), kv_stride, kv_shift, kv_bstride,
               n_q, n_kv, head_dim, n_rot, rot_pairs, _ptr(positions), pos0, T, freq_base, eps, gated, qk_norm,
               _ptr(freq_factors), _stream()))
+
+
+def gpu_qk_norm_rope_tab_kv(qfull, k, q_norm, k_norm, q_out, k_cache, kv_stride, kv_shift, kv_bstride, n_q, n_kv, head_dim,
+                            n_rot, cos_tab, sin_tab, positions, pos0, T, eps, gated=0, qk_norm=1):
+    """gpu_qk_norm_rope_kv with the cos / sin read from the tables of gpu_rope_table; positions / pos0 still name the
+    cache rows."""
+    lib = _lib.load()
+    fn = lib.gpu_qk_norm_rope_tab_kv if k.dtype == torch.float32 else lib.gpu_qk_norm_rope_tab_kv_bf16
+    _check("gpu_qk_norm_rope_tab_kv",
+           fn(_ptr(qfull), _ptr(k), _ptr(q_norm), _ptr(k_norm), _ptr(q_out), _ptr(k_cache), kv_stride, kv_shift, kv_bstride,
+              n_q, n_kv, head_dim, n_rot, _ptr(cos_tab), _ptr(sin_tab), _ptr(positions), pos0, T, eps, gated, qk_norm,
+              _stream()))
 
 
 def gpu_attn_prep_f16(qfull, k, v, q_norm, k_norm, q_out, K, V, kv_stride, kv_shift, kv_bstride, n_q, n_kv, head_dim, n_rot,

@@ -230,6 +230,14 @@ def test_k_heads_straight_into_the_cache(ops, oracle, T, nq, nkv, D, n_rot, kv_s
     assert touched >= T * d_kv - 8 and int((c_fused == -3.0).sum()) >= size - T * d_kv     # only the T rows were written
     with pytest.raises(ops.LayerOpError):
         ops.gpu_qk_norm_rope_kv(q, k, qn, kn, q2, c_fused, d_kv - 8, kv_shift, bstride, nq, nkv, D, n_rot, 0, pos, pos0, T, 1e6, 1e-6)
+    # the same with the cos / sin read from tables filled once: the same bits in q and in the cache
+    ct, st = torch.empty(T, n_rot // 2, device="cuda"), torch.empty(T, n_rot // 2, device="cuda")
+    c_tab, q3 = fill.clone(), torch.empty_like(q)
+    ops.gpu_rope_table(pos, pos0, T, n_rot, 0, 1e6, ct, st)
+    ops.gpu_qk_norm_rope_tab_kv(q, k, qn, kn, q3, c_tab, d_kv, kv_shift, bstride, nq, nkv, D, n_rot, ct, st, pos, pos0, T, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(q3.view(torch.int16 if bf16 else torch.int32), q2.view(torch.int16 if bf16 else torch.int32))
+    assert torch.equal(c_tab.view(torch.int16), c_fused.view(torch.int16))
 
 
 def test_attn_prep_f16_in_one_call(ops, oracle):
