@@ -254,6 +254,17 @@ __device__ __forceinline__ float gamma1(const WT* w, int c) {
     else return Io<WT>::load1(w + c);
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// First statement of the kernels a layer runs back to back. griddepcontrol.wait returns once the kernel before this
+// one in the stream has completed and its writes are visible (at once if this kernel was launched the plain way);
+// launch_dependents then lets the kernel after this one begin its own launch while this one runs, so that its CTAs
+// are resident and waiting when this one's last CTAs retire: the launch latency between two short kernels (a decode
+// step's are a few microseconds each) is hidden. Nothing is read or written before the wait, so no ordering changes.
+__device__ __forceinline__ void pdl_entry() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- reductions
 
 // Sum over the `width` lanes (a power of two <= 32) of an aligned lane group; every lane of the group gets the total.

@@ -113,6 +113,7 @@ template <typename OUT, int TYPE>
 __global__ void __launch_bounds__(EMBED_WARPS * 32)
 k_embed_rows(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out, int E, long long T,
              float scale, int* bad_row, int vec_ok) {
+    pdl_entry();
     constexpr int BB = TYPE == B200_QT_Q8_0 ? 34 : 18;            // bytes per block
     constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;                 // values per lane and 16-byte store
     __shared__ __align__(16) uint8_t stage[EMBED_WARPS][EMBED_CHUNK_BLOCKS * BB + 16];   // (+16: see ld_bytes_2al)
@@ -158,6 +159,7 @@ template <typename OUT, int TYPE>
 __global__ void __launch_bounds__(EMBED_WARPS * 32)
 k_embed_rows_sliced(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out, int E, long long T,
                     float scale, int* bad_row) {
+    pdl_entry();
     constexpr int BB = TYPE == B200_QT_Q8_0 ? 34 : 18;
     constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;
     constexpr int SB = EMBED_SLICE_BYTES / BB / 8 * 8;   // blocks per slice, a multiple of 8 (slices stay 16-byte aligned)
@@ -201,6 +203,7 @@ template <typename OUT, int TYPE>
 __global__ void __launch_bounds__(EMBED_BULK_WARPS * 32)
 k_embed_rows_bulk(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out, int E, long long T,
                   float scale, int* bad_row) {
+    pdl_entry();
     constexpr int BB = TYPE == B200_QT_Q8_0 ? 34 : 18;
     constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;
     constexpr int NS = EMBED_BULK_SLOTS;
@@ -404,6 +407,7 @@ template <typename OUT, int TYPE>
 __global__ void __launch_bounds__(EMBED_WARPS * 32)
 k_embed_rows_any(const uint8_t* table, size_t row_bytes, int vocab, const int32_t* tokens, OUT* out, int E, long long T,
                  float scale, int* bad_row, int vec_ok) {
+    pdl_entry();
     using F = RowFormat<TYPE>;
     constexpr int VPL = sizeof(OUT) == 4 ? 4 : 8;
     __shared__ __align__(16) uint8_t stage[EMBED_WARPS][EMBED_CHUNK_BLOCKS * 34];

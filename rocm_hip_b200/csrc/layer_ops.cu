@@ -96,6 +96,24 @@ long long persistent_grid(K kernel, int block, size_t smem) {
     return (long long)per_sm * sm_count();
 }
 
+// Launch with programmatic stream serialisation allowed: the kernels launched this way start with pdl_entry(), so
+// they may be scheduled while the kernel before them in the stream drains (see common.cuh). A failed launch leaves its
+// error for launched() to return.
+template <typename... KA, typename... A>
+inline void launch_pdl(void (*kernel)(KA...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KA>(args)...);
+}
+
 // ---------------------------------------------------------------- residual add + RMSNorm
 
 // How a row of nvec 16-byte vectors is spread over threads. A function of the row alone: the summation order of a
@@ -123,7 +141,7 @@ cudaError_t launch_norm_vec(const NormPlan& p, const IO* x_in, const IO* add, IO
     if (p.cta_row) {
         const long long res = persistent_grid(k_add_rmsnorm<IO, WT, VPT, true>, p.tpr, 0);
         const long long grid = T < res ? T : res;
-        k_add_rmsnorm<IO, WT, VPT, true><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, p.tpr);
+        launch_pdl((k_add_rmsnorm<IO, WT, VPT, true>), (unsigned)grid, p.tpr, 0, stream, x_in, add, x_out, w, y, n, T, eps, p.tpr);
     } else {
         // several rows per CTA; with few rows, fewer per CTA so that the rows spread over the SMs
         int rows = 256 / p.tpr;
@@ -133,7 +151,7 @@ cudaError_t launch_norm_vec(const NormPlan& p, const IO* x_in, const IO* add, IO
         long long grid = (T + rpp - 1) / rpp;
         const long long res = persistent_grid(k_add_rmsnorm<IO, WT, VPT, false>, block, 0);
         if (grid > res) grid = res;
-        k_add_rmsnorm<IO, WT, VPT, false><<<(unsigned)grid, block, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, p.tpr);
+        launch_pdl((k_add_rmsnorm<IO, WT, VPT, false>), (unsigned)grid, block, 0, stream, x_in, add, x_out, w, y, n, T, eps, p.tpr);
     }
     return launched();
 }
@@ -167,7 +185,7 @@ cudaError_t launch_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const W
         long long grid = rpc ? (T + rpc - 1) / rpc : persistent_grid(k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V>, p.tpr, 0); \
         if (grid > T) grid = T;                                                                      \
         if (grid > INT_MAX) return cudaErrorInvalidValue;                                            \
-        k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V><<<(unsigned)grid, p.tpr, 0, stream>>>(x_in, add, x_out, w, y, n, T, eps, SIDE, rpc); \
+        launch_pdl((k_add_rmsnorm_fast<IO, V, A, M, XHV, Q8V>), (unsigned)grid, p.tpr, 0, stream, x_in, add, x_out, w, y, n, T, eps, SIDE, rpc); \
     } while (0)
 #define NORM_FAST2(V, A, XHV, Q8V, SIDE)                                                             \
     do {                                                                                             \
@@ -251,19 +269,19 @@ cudaError_t launch_swiglu(const IO* g, const IO* u, IO* out, long long n, cudaSt
             const bool do_q8 = side && side->qK && n % 32 == 0 &&
                                ((reinterpret_cast<uintptr_t>(side->q0) | reinterpret_cast<uintptr_t>(side->qK)) & 3) == 0;
             if (do_q8) {
-                if (do_xh) k_swiglu_q8<UNROLL, true><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n, *side);
-                else k_swiglu_q8<UNROLL, false><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n, *side);
+                if (do_xh) launch_pdl((k_swiglu_q8<UNROLL, true>), (unsigned)grid, 256, 0, stream, g, u, out, n, *side);
+                else launch_pdl((k_swiglu_q8<UNROLL, false>), (unsigned)grid, 256, 0, stream, g, u, out, n, *side);
                 if (xh_done) *xh_done = do_xh;
                 if (q8_done) *q8_done = true;
                 return launched();
             }
             if (do_xh) {
-                k_swiglu<IO, FAST, UNROLL, true><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n, side->xh, side->xh_bf16);
+                launch_pdl((k_swiglu<IO, FAST, UNROLL, true>), (unsigned)grid, 256, 0, stream, g, u, out, n, side->xh, side->xh_bf16);
                 if (xh_done) *xh_done = true;
                 return launched();
             }
         }
-        k_swiglu<IO, FAST, UNROLL><<<(unsigned)grid, 256, 0, stream>>>(g, u, out, n);
+        launch_pdl((k_swiglu<IO, FAST, UNROLL>), (unsigned)grid, 256, 0, stream, g, u, out, n, nullptr, 0);
     } else {
         const long long cap = resident_ctas(256) * 8;
         long long grid = (n + 255) / 256;
@@ -355,7 +373,7 @@ cudaError_t launch_rope_table(const int* positions, int pos0, long long T, int n
     long long grid = (T + tpp - 1) / tpp;
     const long long cap = resident_ctas(256) * 4;
     if (grid > cap) grid = cap;
-#define ROPE_TAB(F, P) k_rope_table<F, P><<<(unsigned)grid, 256, 0, stream>>>(positions, pos0, T, half, rot_pairs, ff, cos_out, sin_out, fr)
+#define ROPE_TAB(F, P) launch_pdl((k_rope_table<F, P>), (unsigned)grid, 256, 0, stream, positions, pos0, T, half, rot_pairs, ff, cos_out, sin_out, fr)
     if (fast) { if (vec) ROPE_TAB(true, 4); else ROPE_TAB(true, 1); }
     else { if (vec) ROPE_TAB(false, 4); else ROPE_TAB(false, 1); }
 #undef ROPE_TAB
@@ -439,7 +457,7 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
         const size_t sm = (2 * (size_t)D + 2 * 2 * TTV * (size_t)(n_rot / 2)) * sizeof(float);                        \
         m.T = tl * TTV;                                                                                               \
         const long long res = persistent_grid(k_qk_norm_rope_fast<IO, TTV, FULLV, KVC, true, MINB, DSV, NRV>, block, sm); \
-        k_qk_norm_rope_fast<IO, TTV, FULLV, KVC, true, MINB, DSV, NRV><<<(unsigned)(tl < res ? tl : res), block, sm, stream>>>(m, fr); \
+        launch_pdl((k_qk_norm_rope_fast<IO, TTV, FULLV, KVC, true, MINB, DSV, NRV>), (unsigned)(tl < res ? tl : res), block, sm, stream, m, fr); \
     } while (0)
                 if (D == 128 && n_rot == 128) QK_TAB(4, true, 2, 128, 128);         // the heads of the dense configurations
                 else if (D == 256 && n_rot == 64) QK_TAB(4, false, 2, 256, 64);    // partial rotary over the first 64 of 256
@@ -452,10 +470,10 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
         if (done) {
         } else if (n_rot == D) {
             const long long res = persistent_grid(k_qk_norm_rope_fast<IO, FTT, true, KVC>, block, smem);
-            k_qk_norm_rope_fast<IO, FTT, true, KVC><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(m, fr);
+            launch_pdl((k_qk_norm_rope_fast<IO, FTT, true, KVC>), (unsigned)(tiles < res ? tiles : res), block, smem, stream, m, fr);
         } else {
             const long long res = persistent_grid(k_qk_norm_rope_fast<IO, FTT, false, KVC>, block, smem);
-            k_qk_norm_rope_fast<IO, FTT, false, KVC><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(m, fr);
+            launch_pdl((k_qk_norm_rope_fast<IO, FTT, false, KVC>), (unsigned)(tiles < res ? tiles : res), block, smem, stream, m, fr);
         }
         const cudaError_t e = launched();
         const long long rest = T - m.T;
@@ -481,7 +499,7 @@ cudaError_t launch_qk(const IO* qfull, const IO* k, const float* q_norm, const f
 #define QK_LAUNCH(P, TTV)                                                                  \
     do {                                                                                   \
         const long long res = persistent_grid(k_qk_norm_rope<IO, P, TTV, KVC>, block, smem);    \
-        k_qk_norm_rope<IO, P, TTV, KVC><<<(unsigned)(tiles < res ? tiles : res), block, smem, stream>>>(a, fr); \
+        launch_pdl((k_qk_norm_rope<IO, P, TTV, KVC>), (unsigned)(tiles < res ? tiles : res), block, smem, stream, a, fr); \
     } while (0)
     if (ppt == 1 && tt == 4) QK_LAUNCH(1, 4);
     else if (ppt == 1) QK_LAUNCH(1, 1);
@@ -520,7 +538,7 @@ cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int voca
 #define EMBED(K, TY)                                                                                             \
     do {                                                                                                         \
         const long long res = persistent_grid(K<OUT, TY>, EMBED_WARPS * 32, 0);                                  \
-        K<OUT, TY><<<(unsigned)(need < res ? need : res), EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, \
+        launch_pdl((K<OUT, TY>), (unsigned)(need < res ? need : res), EMBED_WARPS * 32, 0, stream, tb, row_bytes, vocab, tokens, out, \
                                                                                          E, T, scale, bad_row, vec_ok);     \
     } while (0)
     // Q8_0 / Q4_0 rows of whole 8-block groups in a 16-byte aligned table (every GGUF token_embd of E % 256 == 0).
@@ -535,7 +553,7 @@ cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int voca
 #define EMBED_BULK(TY)                                                                                           \
     do {                                                                                                         \
         const long long res = persistent_grid(k_embed_rows_bulk<OUT, TY>, EMBED_BULK_WARPS * 32, 0);             \
-        k_embed_rows_bulk<OUT, TY><<<(unsigned)(need_b < res ? need_b : res), EMBED_BULK_WARPS * 32, 0, stream>>>( \
+        launch_pdl((k_embed_rows_bulk<OUT, TY>), (unsigned)(need_b < res ? need_b : res), EMBED_BULK_WARPS * 32, 0, stream,  \
             tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row);                                             \
     } while (0)
             if (type == B200_QT_Q8_0) EMBED_BULK(B200_QT_Q8_0); else EMBED_BULK(B200_QT_Q4_0);
@@ -547,9 +565,9 @@ cudaError_t launch_embed(int type, const void* table, size_t row_bytes, int voca
         long long grid = (slices + EMBED_WARPS - 1) / EMBED_WARPS;
         if (grid > INT_MAX) grid = INT_MAX;
         if (type == B200_QT_Q8_0)
-            k_embed_rows_sliced<OUT, B200_QT_Q8_0><<<(unsigned)grid, EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row);
+            launch_pdl((k_embed_rows_sliced<OUT, B200_QT_Q8_0>), (unsigned)grid, EMBED_WARPS * 32, 0, stream, tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row);
         else
-            k_embed_rows_sliced<OUT, B200_QT_Q4_0><<<(unsigned)grid, EMBED_WARPS * 32, 0, stream>>>(tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row);
+            launch_pdl((k_embed_rows_sliced<OUT, B200_QT_Q4_0>), (unsigned)grid, EMBED_WARPS * 32, 0, stream, tb, row_bytes, vocab, tokens, out, E, T, scale, bad_row);
         return launched();
     }
     switch (type) {

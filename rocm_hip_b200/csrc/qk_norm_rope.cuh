@@ -195,6 +195,7 @@ __device__ __forceinline__ void stage_inv_freq(double* dst, const RopeFreq& fr, 
 template <typename IO, int PPT, int TT, bool KVC = false>
 __global__ void __launch_bounds__(384, 2)
 k_qk_norm_rope(const QkArgs a, const __grid_constant__ RopeFreq fr) {
+    pdl_entry();
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
     extern __shared__ __align__(16) float tab_all[];
     __shared__ double invf[B200_MAX_ROT_PAIRS];
@@ -352,6 +353,7 @@ template <typename IO, int TT, bool FULL, bool KVC = false, bool TAB = false, in
           int NR = 0>
 __global__ void __launch_bounds__(384, MINB)
 k_qk_norm_rope_fast(const QkArgs a, const __grid_constant__ RopeFreq fr) {
+    pdl_entry();
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
     extern __shared__ __align__(16) float smem_all[];
     __shared__ double invf[TAB ? 1 : B200_MAX_ROT_PAIRS];
@@ -540,6 +542,7 @@ template <bool FAST_TRIG, int PER>
 __global__ void __launch_bounds__(256)
 k_rope_table(const int* positions, int pos0, long long T, int half, int rot_pairs, const float* ff, float* cos_out,
              float* sin_out, const __grid_constant__ RopeFreq fr) {
+    pdl_entry();
     __shared__ double invf[B200_MAX_ROT_PAIRS];
     stage_inv_freq(invf, fr, half);
     const int L = half / PER, tpp = 256 / L;

@@ -33,6 +33,7 @@ namespace b200 {
 template <typename IO, typename WT, int VPT, bool CTA_ROW>
 __global__ void __launch_bounds__(CTA_ROW ? 1024 : 256)
 k_add_rmsnorm(const IO* x_in, const IO* add, IO* x_out, const WT* w, IO* y, int n, long long T, float eps, int tpr) {
+    pdl_entry();
     constexpr int VE = Io<IO>::VE;
     __shared__ double part[2][32];
     const int nvec = n / VE;
@@ -118,6 +119,7 @@ template <typename IO, int VPT, bool HAS_ADD, int MAXT, bool XH = false, bool Q8
 __global__ void __launch_bounds__(MAXT, MAXT <= 160 ? (VPT <= 2 && !XH && !Q8 ? (HAS_ADD ? 5 : 8) : 4) : MAXT <= 320 ? (Q8 ? 3 : 2) : 1)
 k_add_rmsnorm_fast(const IO* x_in, const IO* add, IO* x_out, const float* w, IO* y, int n, long long T, float eps,
                    const Q8Side side = Q8Side{}, int rows_per_cta = 0) {
+    pdl_entry();
     static_assert(!(XH || Q8) || sizeof(IO) == 4, "the side outputs belong to fp32 rows");
     __shared__ Q8Half half_stat[Q8 ? 64 : 1];   // per 128 values of the row (n <= 8192)
     uint16_t* const xh = side.xh;

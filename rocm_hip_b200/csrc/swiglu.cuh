@@ -61,6 +61,7 @@ __device__ __forceinline__ f2 silu_mul2(f2 g, f2 u) {
 template <typename IO, bool FAST, int UNROLL, bool XH = false>
 __global__ void __launch_bounds__(256)
 k_swiglu(const IO* g, const IO* u, IO* out, long long n, uint16_t* xh = nullptr, int xh_bf16 = 0) {
+    pdl_entry();
     static_assert(!XH || sizeof(IO) == 4, "the 16-bit side copy belongs to fp32 rows");
     constexpr int VE = Io<IO>::VE, NP = VE / 2;
     const long long nvec = n / VE;
@@ -120,6 +121,7 @@ k_swiglu(const IO* g, const IO* u, IO* out, long long n, uint16_t* xh = nullptr,
 template <int UNROLL, bool XH>
 __global__ void __launch_bounds__(256)
 k_swiglu_q8(const float* g, const float* u, float* out, long long n, const Q8Side side) {
+    pdl_entry();
     __shared__ Q8Half half_stat[2][UNROLL][8];
     const long long nvec = n / 4;
     constexpr int TILE = 256 * UNROLL;
