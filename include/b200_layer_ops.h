@@ -376,6 +376,10 @@ cudaError_t gpu_rope_rotate_half_f16(const uint16_t* x, const float* ctab, const
  * time per context. Row pointers are host memory; the embedding table is device memory (a weight, uploaded once).
  * Errors: cudaErrorInvalidValue for bad arguments or a row too large for a slot, else the first CUDA error met. */
 typedef struct b200_host_ctx b200_host_ctx;
+/* How a call cuts T rows into chunks for a ring of n_slots slots of slot_rows rows each (small chunks first and last,
+ * so that little time goes to the copy in that nothing overlaps and to the last copy out; large ones in between).
+ * Writes up to max_sizes chunk sizes and returns their count. Host logic only: no device is touched. */
+int b200_host_chunk_plan(long long T, long long slot_rows, int n_slots, long long* sizes, int max_sizes);
 b200_host_ctx* b200_host_ctx_create(size_t slot_bytes, int n_slots);   /* NULL on failure */
 void b200_host_ctx_destroy(b200_host_ctx* ctx);
 

@@ -63,6 +63,27 @@ cudaError_t call_launch(F& launch, void** din, void** dout, void**, long long ro
     return launch(din, dout, rows, row0, st);
 }
 
+// Chunk sizes for T rows through a ring of n_slots slots that hold cap rows each. The first chunk's copy in and the
+// last chunk's copy out are not overlapped by anything, so the chunks start small (1/16 of a slot, at least 64 rows),
+// double up to what a slot holds and halve again towards the end; in between, large chunks keep the count of copies
+// and launches (a fixed cost of some tens of microseconds per chunk) low, but stay small enough for two chunks per
+// slot when the work allows, so that the ring actually overlaps.
+std::vector<long long> chunk_plan(long long T, long long cap, long long n_slots) {
+    std::vector<long long> sizes;
+    if (T <= 0 || cap <= 0 || n_slots <= 0) return sizes;
+    const long long r0 = cap / 16 > 64 ? cap / 16 : (cap < 64 ? cap : 64);
+    std::vector<long long> ramp;
+    long long left = T, step = r0;
+    while (step < cap && left > 4 * step) { ramp.push_back(step); left -= 2 * step; step *= 2; }
+    long long mid = step < cap ? step : cap;
+    const long long want = (left + 2 * n_slots - 1) / (2 * n_slots);
+    if (mid > want && want >= 64) mid = want;
+    sizes = ramp;
+    for (; left > 0; left -= mid) sizes.push_back(left < mid ? left : mid);
+    sizes.insert(sizes.end(), ramp.rbegin(), ramp.rend());
+    return sizes;
+}
+
 template <class F>
 cudaError_t run_rows(b200_host_ctx* ctx, long long T, const RowBufs& io, F launch) {
     size_t per_row = 0;
@@ -72,23 +93,7 @@ cudaError_t run_rows(b200_host_ctx* ctx, long long T, const RowBufs& io, F launc
     const size_t slack = kAlign * (size_t)(io.n_in + io.n_out + io.n_tmp);
     if (per_row == 0 || ctx->slot_bytes <= slack || (ctx->slot_bytes - slack) / per_row == 0) return cudaErrorInvalidValue;
     const long long cap = (long long)((ctx->slot_bytes - slack) / per_row);   // rows a slot holds
-    // Chunk sizes: the first chunk's copy in and the last chunk's copy out are not overlapped by anything, so the
-    // chunks start small, double up to what a slot holds and halve again towards the end; in between, large chunks
-    // keep the count of copies and launches (a fixed cost of some tens of microseconds per chunk) low.
-    std::vector<long long> sizes;
-    {
-        const long long r0 = cap / 16 > 64 ? cap / 16 : (cap < 64 ? cap : 64);
-        std::vector<long long> ramp;
-        long long left = T, step = r0;
-        while (step < cap && left > 4 * step) { ramp.push_back(step); left -= 2 * step; step *= 2; }
-        long long mid = step < cap ? step : cap;
-        // at least two chunks per slot when the work allows, so the ring actually overlaps
-        const long long want = (left + 2 * (long long)ctx->slots.size() - 1) / (2 * (long long)ctx->slots.size());
-        if (mid > want && want >= 64) mid = want;
-        sizes = ramp;
-        for (; left > 0; left -= mid) sizes.push_back(left < mid ? left : mid);
-        sizes.insert(sizes.end(), ramp.rbegin(), ramp.rend());
-    }
+    const std::vector<long long> sizes = chunk_plan(T, cap, (long long)ctx->slots.size());
     const long long chunk = cap;   // the slot's layout is that of its largest chunk
     cudaError_t err = cudaSuccess;
     long long row0 = 0;
@@ -148,6 +153,12 @@ struct ConstArea {
 }  // namespace
 
 extern "C" {
+
+int b200_host_chunk_plan(long long T, long long slot_rows, int n_slots, long long* sizes, int max_sizes) {
+    const std::vector<long long> plan = chunk_plan(T, slot_rows, n_slots);
+    for (size_t i = 0; i < plan.size() && (int)i < max_sizes; ++i) sizes[i] = plan[i];
+    return (int)plan.size();
+}
 
 b200_host_ctx* b200_host_ctx_create(size_t slot_bytes, int n_slots) {
     if (slot_bytes < (1u << 16) || n_slots < 1 || n_slots > 16) return nullptr;
