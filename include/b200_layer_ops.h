@@ -465,6 +465,9 @@ cudaError_t b200_host_group_qk_norm_rope(b200_host_group* grp, int elem, const v
 cudaError_t b200_host_group_embed_rows(b200_host_group* grp, int elem, int type, const void* const* tables_dev,
                                        size_t row_bytes, int vocab, const int32_t* tokens, void* out, int E, long long T,
                                        float scale);
+/* b200_host_layer_sweep over the group's devices: device g runs rows [T g / G, T (g + 1) / G) with its own table
+ * tables_dev[g] (args->table_dev is not used); positions, or pos0 + the range's first row, follow the rows. */
+cudaError_t b200_host_group_layer_sweep(b200_host_group* grp, const b200_layer_sweep* args, const void* const* tables_dev);
 
 /* ------------------------------------------------------------------------------------------------ Part 4 */
 

@@ -111,6 +111,7 @@ SIGNATURES = {
     "b200_host_group_swiglu": (_i, [_p, _i, _p, _p, _p, _ll, _i]),
     "b200_host_group_qk_norm_rope": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _ll, _f, _f, _i, _i, _p]),
     "b200_host_group_embed_rows": (_i, [_p, _i, _i, _p, _sz, _i, _p, _p, _i, _ll, _f]),
+    "b200_host_group_layer_sweep": (_i, [_p, _p, _p]),
     "b200_host_chunk_plan": (_i, [_ll, _ll, _i, C.POINTER(_ll), _i]),
     "b200_gguf_open": (_p, [C.c_char_p]),
     "b200_gguf_close": (None, [_p]),

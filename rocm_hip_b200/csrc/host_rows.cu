@@ -483,4 +483,35 @@ cudaError_t b200_host_group_embed_rows(b200_host_group* grp, int elem, int type,
     });
 }
 
+cudaError_t b200_host_group_layer_sweep(b200_host_group* grp, const b200_layer_sweep* a, const void* const* tables_dev) {
+    if (!grp || !a || !tables_dev || a->T <= 0 || !a->tokens || (a->elem != 2 && a->elem != 4)) return cudaErrorInvalidValue;
+    for (long long t = 0; t < a->T; ++t)   // refuse before any device starts (src/qwen_model.cpp:981)
+        if (a->tokens[t] < 0 || a->tokens[t] >= a->vocab) return cudaErrorInvalidValue;
+    const b200_layer_sweep all = *a;
+    return for_each_device(grp, all.T, [=](b200_host_ctx* c, int g, long long lo, long long rows) {
+        b200_layer_sweep s = all;
+        const size_t e = (size_t)s.elem, row = (size_t)s.E * e, D = (size_t)s.head_dim;
+        const size_t qin = (size_t)s.n_q * (s.gated ? 2 : 1) * D * e, kin = (size_t)s.n_kv * D * e, ff = (size_t)s.FF * e;
+        s.T = rows;
+        s.table_dev = tables_dev[g];
+        s.tokens = all.tokens + lo;
+        s.xn_attn = at(all.xn_attn, lo * row);
+        s.qfull = at(all.qfull, lo * qin);
+        s.k = at(all.k, lo * kin);
+        s.q_out = at(all.q_out, lo * (size_t)s.n_q * D * e);
+        s.k_out = at(all.k_out, lo * kin);
+        if (all.positions) s.positions = all.positions + lo;
+        else s.pos0 = all.pos0 + (int)lo;
+        s.attn_proj = at(all.attn_proj, lo * row);
+        s.xn_ffn = at(all.xn_ffn, lo * row);
+        s.gate = at(all.gate, lo * ff);
+        s.up = at(all.up, lo * ff);
+        s.act = at(all.act, lo * ff);
+        s.ffn_proj = at(all.ffn_proj, lo * row);
+        s.x_out = at(all.x_out, lo * row);
+        s.xn_next = at(all.xn_next, lo * row);
+        return b200_host_layer_sweep(c, &s);
+    });
+}
+
 }  // extern "C"

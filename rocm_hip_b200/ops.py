@@ -455,16 +455,30 @@ class HostRows:
                     qk_norm=1, freq_factors=None, embd_scale=1.0):
         """b200_host_layer_sweep: the layer's six ops in one call; rows in host memory, the residual stream stays on
         the device between the kernels of a chunk."""
+        a = self._sweep_args(locals())
+        _check("b200_host_layer_sweep", self._lib.b200_host_layer_sweep(self._ctx, C.byref(a)))
+
+    def _sweep_args(self, kw):
+        """The b200_layer_sweep structure from layer_sweep's arguments (table_dev may be None: a group passes its own)."""
+        g = kw.get
         v = lambda a: self._h(a).value if a is not None else None
-        a = _lib.b200_layer_sweep(
-            elem=self._elem(xn_attn), T=T, qtype=qtype, table_dev=table_dev.data_ptr(), row_bytes=row_bytes, vocab=vocab,
+        (qtype, row_bytes, vocab, tokens, E, w_attn_norm, w_ffn_norm, w_next_norm, eps, xn_attn, qfull, k, q_out, k_out, q_norm,
+         k_norm, n_q, n_kv, head_dim, n_rot, freq_base, attn_proj, xn_ffn, gate, up, FF, act, ffn_proj, x_out, xn_next, T,
+         rot_pairs, positions, pos0, gated, qk_norm, freq_factors, embd_scale) = (g(n) for n in (
+            "qtype", "row_bytes", "vocab", "tokens", "E", "w_attn_norm", "w_ffn_norm", "w_next_norm", "eps", "xn_attn", "qfull",
+            "k", "q_out", "k_out", "q_norm", "k_norm", "n_q", "n_kv", "head_dim", "n_rot", "freq_base", "attn_proj", "xn_ffn",
+            "gate", "up", "FF", "act", "ffn_proj", "x_out", "xn_next", "T", "rot_pairs", "positions", "pos0", "gated", "qk_norm",
+            "freq_factors", "embd_scale"))
+        table_dev = g("table_dev")
+        return _lib.b200_layer_sweep(
+            elem=self._elem(xn_attn), T=T, qtype=qtype, table_dev=table_dev.data_ptr() if table_dev is not None else None,
+            row_bytes=row_bytes, vocab=vocab,
             tokens=v(tokens), E=E, embd_scale=embd_scale, w_attn_norm=v(w_attn_norm), w_ffn_norm=v(w_ffn_norm),
             w_next_norm=v(w_next_norm), eps=eps, xn_attn=v(xn_attn), qfull=v(qfull), k=v(k), q_out=v(q_out), k_out=v(k_out),
             q_norm=v(q_norm), k_norm=v(k_norm), n_q=n_q, n_kv=n_kv, head_dim=head_dim, n_rot=n_rot, rot_pairs=rot_pairs,
             positions=v(positions), pos0=pos0, freq_base=freq_base, gated=gated, qk_norm=qk_norm,
             freq_factors=v(freq_factors), attn_proj=v(attn_proj), xn_ffn=v(xn_ffn), gate=v(gate), up=v(up), FF=FF,
             act=v(act), ffn_proj=v(ffn_proj), x_out=v(x_out), xn_next=v(xn_next))
-        _check("b200_host_layer_sweep", self._lib.b200_host_layer_sweep(self._ctx, C.byref(a)))
 
 
 class HostGroup(HostRows):
@@ -501,6 +515,15 @@ class HostGroup(HostRows):
         _check("b200_host_group_qk_norm_rope", self._lib.b200_host_group_qk_norm_rope(
             self._ctx, self._elem(ref), h(qfull), h(k), h(q_norm), h(k_norm), h(q_out), h(k_out), n_q, n_kv, head_dim,
             n_rot, rot_pairs, h(positions), pos0, T, freq_base, eps, gated, qk_norm, h(freq_factors)))
+
+    def layer_sweep(self, *, tables_dev, **kw):
+        """b200_host_group_layer_sweep: layer_sweep's arguments with one CUDA table per device instead of table_dev."""
+        assert len(tables_dev) == self.size
+        kw.setdefault("rot_pairs", 0), kw.setdefault("positions", None), kw.setdefault("pos0", 0), kw.setdefault("gated", 0)
+        kw.setdefault("qk_norm", 1), kw.setdefault("freq_factors", None), kw.setdefault("embd_scale", 1.0)
+        a = self._sweep_args(dict(kw, table_dev=None))
+        ptrs = (C.c_void_p * self.size)(*[t.data_ptr() for t in tables_dev])
+        _check("b200_host_group_layer_sweep", self._lib.b200_host_group_layer_sweep(self._ctx, C.byref(a), ptrs))
 
     def embed_rows(self, qtype, tables_dev, row_bytes, vocab, tokens, out, E, T, scale=1.0):
         h = self._h

@@ -70,6 +70,25 @@ def test_group_equals_single_device(ops, single, G):
         with pytest.raises(ops.LayerOpError) as err:
             grp.embed_rows(ops.QT_Q8_0, tabs, table.shape[1], vocab, ids, e1, E, Te)
         assert err.value.code == 1 and np.array_equal(e1, before)
+        ids[Te - 1] = 5
+
+        # the whole layer sweep: rows, positions (pos0 + the global row) and the per-device tables follow the ranges
+        Ts, FF = 517, 1536
+        f = lambda name, *shape: synth.normal(3, name, 0, int(np.prod(shape))).reshape(shape)
+        qs, ks, p1, p2, gs, us = f("s.q", Ts, nq * D), f("s.k", Ts, nkv * D), f("s.p1", Ts, E), f("s.p2", Ts, E), f("s.g", Ts, FF), f("s.u", Ts, FF)
+        w1, w2, w3 = (synth.normal(3, n_, 0, E, 1.0, 0.1) for n_ in ("s.w1", "s.w2", "s.w3"))
+        outs = []
+        for runner, tab_kw in ((grp, dict(tables_dev=tabs)), (single, dict(table_dev=tabs[0]))):
+            o = [np.zeros((Ts, E), np.float32), np.zeros((Ts, nq * D), np.float32), np.zeros((Ts, nkv * D), np.float32),
+                 np.zeros((Ts, E), np.float32), np.zeros((Ts, FF), np.float32), np.zeros((Ts, E), np.float32), np.zeros((Ts, E), np.float32)]
+            runner.layer_sweep(qtype=ops.QT_Q8_0, row_bytes=table.shape[1], vocab=vocab, tokens=ids[:Ts], E=E, w_attn_norm=w1,
+                               w_ffn_norm=w2, w_next_norm=w3, eps=1e-6, xn_attn=o[0], qfull=qs, k=ks, q_out=o[1], k_out=o[2],
+                               q_norm=qn, k_norm=kn, n_q=nq, n_kv=nkv, head_dim=D, n_rot=D, freq_base=1e6, attn_proj=p1,
+                               xn_ffn=o[3], gate=gs, up=us, FF=FF, act=o[4], ffn_proj=p2, x_out=o[5], xn_next=o[6], T=Ts,
+                               pos0=123, **tab_kw)
+            outs.append(o)
+        for a_, b_ in zip(*outs):
+            assert a_.any() and np.array_equal(a_.view(np.uint32), b_.view(np.uint32))
         assert torch.cuda.current_device() == 0            # the caller's device is left as it was
     finally:
         grp.close()
