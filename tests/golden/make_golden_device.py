@@ -246,11 +246,13 @@ def attn_prep(lib, out, f):
     D): q / k norm + RoPE, the Hadamard rotation, FP16 / Q8_0 / Q4_0 cache rows. 'exact' cases switch the norm and the
     RoPE off, so every stored byte follows from the inputs by exactly rounded steps; 'chain' cases run everything."""
     vp, ci, cf, cll = C.c_void_p, C.c_int, C.c_float, C.c_longlong
-    for tag, D, nq, nkv, T, chain, gated, kvq in (
-            ("exact_q8", 128, 4, 2, 3, 0, 0, 1), ("exact_q4", 128, 4, 2, 3, 0, 0, 2), ("exact_q8_rot", 128, 4, 2, 3, 0, 0, 1 | 4),
-            ("exact_q4_rot", 256, 2, 1, 2, 0, 0, 2 | 4), ("exact_q8_rot512", 512, 2, 1, 2, 0, 0, 1 | 4),
-            ("chain_f16", 128, 4, 2, 5, 1, 0, 0), ("chain_gated_f16", 256, 2, 1, 3, 1, 1, 0), ("chain_q8_rot", 128, 4, 2, 4, 1, 0, 1 | 4),
-            ("chain_q4_rot", 64, 2, 2, 3, 1, 0, 2 | 4)):
+    for tag, D, nq, nkv, T, chain, gated, kvq, pos0 in (
+            ("exact_q8", 128, 4, 2, 3, 0, 0, 1, 7), ("exact_q4", 128, 4, 2, 3, 0, 0, 2, 7), ("exact_q8_rot", 128, 4, 2, 3, 0, 0, 1 | 4, 7),
+            ("exact_q4_rot", 256, 2, 1, 2, 0, 0, 2 | 4, 7), ("exact_q8_rot512", 512, 2, 1, 2, 0, 0, 1 | 4, 7),
+            ("chain_f16", 128, 4, 2, 5, 1, 0, 0, 7), ("chain_gated_f16", 256, 2, 1, 3, 1, 1, 0, 7),
+            ("chain_q8_rot", 128, 4, 2, 4, 1, 0, 1 | 4, 7), ("chain_q4_rot", 64, 2, 2, 3, 1, 0, 2 | 4, 7),
+            # the position the reference's own test compares its kernel with its CPU ops at (tests/forward_verify.cpp:835-853)
+            ("chain_pos2499", 128, 4, 2, 2, 1, 0, 0, 2499)):
         qs = 2 * D if gated else D
         q, k, v = f(tag + ".q", T, nq * qs) * 2, f(tag + ".k", T, nkv * D) * 3, f(tag + ".v", T, nkv * D) * 3
         if not chain:
@@ -261,7 +263,7 @@ def attn_prep(lib, out, f):
         qn, kn = f(tag + ".qn", D, mean=1.0, std=0.1), f(tag + ".kn", D, mean=1.0, std=0.1)
         n_vals, kq = nkv * D, kvq & 3
         kv_stride = n_vals if kq == 0 else n_vals * (17 if kq == 1 else 9) // 32      # in 2-byte units
-        pos0, n_ctx = 7, 16
+        n_ctx = pos0 + T + 2
         K, V = np.full(n_ctx * kv_stride, 0x5A5A, np.uint16), np.full(n_ctx * kv_stride, 0x5A5A, np.uint16)
         q_out = np.zeros((T, nq * D), np.float32)
         n_rot = D if chain else 0

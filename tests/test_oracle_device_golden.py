@@ -229,6 +229,20 @@ def test_attn_prep_chain_against_the_reference_kernel(tag):
         assert untouched(G[f"prep_{tag}_{name}"])
 
 
+def test_attn_prep_at_the_position_the_reference_tests():
+    """tests/forward_verify.cpp:835-853,903-906 compares the reference's attn_prep kernel with its CPU ops at position
+    2499 to 1e-3, because the kernel forms the angles in fp32 where the CPU code (and this build) forms them in double:
+    the same comparison here, the reference's kernel against the checker that follows its CPU code (measured: 6e-5)."""
+    tag = "chain_pos2499"
+    D, nq, nkv, T, gated, kvq, pos0, rows, untouched = _prep(tag)
+    assert pos0 == 2499
+    wq, wk = oracle.qk_norm_rope(G[f"prep_{tag}_q"], G[f"prep_{tag}_k"], G[f"prep_{tag}_qn"], G[f"prep_{tag}_kn"], nq, nkv, D, D, 0,
+                                 None, pos0, 1e6, 1e-6)
+    close_rows(G[f"prep_{tag}_q_out"].reshape(-1, D), wq.reshape(-1, D), 1e-3)
+    close_rows(oracle.f16_to_f32(rows(G[f"prep_{tag}_K"])).reshape(-1, D), wk.reshape(-1, D), 2e-3)
+    assert untouched(G[f"prep_{tag}_K"]) and untouched(G[f"prep_{tag}_V"])
+
+
 @pytest.mark.skipif(not os.path.exists(os.path.join(os.path.dirname(oracle.__file__), "_ref", "libref_emul.so")),
                     reason="the emulated reference kernels are built only where the reference's sources are present")
 def test_fixtures_regenerate_identically(tmp_path, monkeypatch):
