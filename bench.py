@@ -436,11 +436,14 @@ def emit(line):
         os.write(_REAL_STDOUT, data)
 
 
-def kernel_table(sw, per_kernel_ms, world, peak):
+def kernel_table(sw, per_kernel_ms, world, peak, median=None, best=None):
+    """Per kernel: mean launch time over the timed launches (ms; the figures derive from it), and their median and
+    best, max over ranks each."""
     rows = []
-    for (name, _, nbytes, nrows, unit), ms in zip(sw.kernels, per_kernel_ms):
+    for i, ((name, _, nbytes, nrows, unit), ms) in enumerate(zip(sw.kernels, per_kernel_ms)):
         gbs = nbytes / (ms * 1e-3) / 1e9
-        rows.append({"name": name, "ms": ms, "rows_per_s": nrows * world / (ms * 1e-3), "rows": unit,
+        extra = {"ms_median": median[i], "ms_best": best[i]} if median and best else {}
+        rows.append({"name": name, "ms": ms, **extra, "rows_per_s": nrows * world / (ms * 1e-3), "rows": unit,
                      "algorithmic_bytes_per_gpu": nbytes, "gbs_per_gpu": gbs, "gbs_all_gpus": gbs * world,
                      "frac_of_measured_peak": gbs / peak, "frac_of_8tbs": gbs / NOMINAL_HBM_GBS})
     return rows
@@ -533,9 +536,11 @@ def main():
         barrier()
         if clocks:
             clocks.mark_end()
-        per_kernel = [sum(e[j][0].elapsed_time(e[j][1]) for e in ev) / len(ev) for j in range(nk)]
-        red = max_over_ranks([start.elapsed_time(end) / steps] + per_kernel)
-        return red[0], red[1:]
+        times = [sorted(e[j][0].elapsed_time(e[j][1]) for e in ev) for j in range(nk)]
+        per_kernel = [sum(t) / len(t) for t in times]
+        red = max_over_ranks([start.elapsed_time(end) / steps] + per_kernel + [t[len(t) // 2] for t in times] + [t[0] for t in times])
+        time_sweeps.median, time_sweeps.best = red[1 + nk:1 + 2 * nk], red[1 + 2 * nk:]
+        return red[0], red[1:1 + nk]
 
     # ---- the headline workload
     lo, T, T_total = rank_rows(args.tokens or wl["T"])
@@ -549,6 +554,7 @@ def main():
         sw.step()
     launches0 = ops.launch_count()
     ms_step, per_kernel_ms = time_sweeps(sw, args.steps, reps, clocks=clocks)
+    head_median, head_best = time_sweeps.median, time_sweeps.best
     clk = clocks.stop()
     launches = ops.launch_count() - launches0
     # A sweep of a few microseconds per kernel is bound by launch latency: it is also timed as replays of a CUDA graph
@@ -576,7 +582,7 @@ def main():
         ms_step = graph_ms
     if not wl.get("moe"):
         assert int(sw.bad.item()) == 2**31 - 1
-    kernels = kernel_table(sw, per_kernel_ms, world, peak)
+    kernels = kernel_table(sw, per_kernel_ms, world, peak, head_median, head_best)
     dom = next(k for k in kernels if k["name"] == sw.dominant)
     ratio, ratio_src = dram_traffic_ratio("swiglu_bf16" if wl["dtype"] == "bf16" else "swiglu_f32")
     roof = {"kernel": dom["name"], "bound": "hbm", "achieved": dom["gbs_per_gpu"], "peak": peak, "unit": "GB/s",
@@ -678,7 +684,7 @@ def main():
             sweep_ms = max_over_ranks([start.elapsed_time(end)])[0] / n_rep
             others[name] = {"workload": w2["name"], "dtype": w2["dtype"], "token_rows_total": T2_total, "token_rows_per_gpu": T2,
                             "sweep_ms_graph_replay": sweep_ms, "rows_per_s": T2_total / (sweep_ms * 1e-3),
-                            "kernels": kernel_table(s2, pk, world, peak),
+                            "kernels": kernel_table(s2, pk, world, peak, time_sweeps.median, time_sweeps.best),
                             "timing": "per kernel: CUDA events around single launches, L2 flushed (384 MB rewritten) "
                                       "before each; sweep: 50 CUDA-graph replays back to back; same_bytes_copy_ms: a plain "
                                       "device copy of the kernel's algorithmic bytes timed the same way"}

@@ -6,7 +6,12 @@
 #include "hip_runtime.h"
 
 #ifdef __cplusplus
-struct __half { uint16_t x; };
+struct __half {
+    uint16_t x;
+    __half() = default;
+    __half(float f);                 // (__half)value, rounding to nearest even
+    operator float() const;          // (float)h
+};
 
 inline __half __float2half(float f) {
     uint32_t u;
@@ -67,6 +72,8 @@ inline __half2 __hsub2(__half2 a, __half2 b) {
 inline __half2 __hadd2(__half2 a, __half2 b) {
     return __half2{__float2half(__half2float(a.x) + __half2float(b.x)), __float2half(__half2float(a.y) + __half2float(b.y))};
 }
+inline __half::__half(float f) : x(__float2half(f).x) {}
+inline __half::operator float() const { return __half2float(*this); }
 inline uint16_t __half_as_ushort(__half h) { return h.x; }
 inline __half __ushort_as_half(uint16_t x) { __half h; h.x = x; return h; }
 #endif

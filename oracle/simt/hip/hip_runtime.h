@@ -99,6 +99,9 @@ inline T __shfl_xor(T v, int mask, int width = 32) {
     const int l = simt_self.lane, s = l ^ mask;
     return simt_exchange(v, (s / width == l / width) ? s : l);
 }
+// (the *_sync spellings take a lane mask first: every lane of the wave takes part here)
+template <typename T>
+inline T __shfl_xor_sync(unsigned long long, T v, int mask, int width = 32) { return __shfl_xor(v, mask, width); }
 template <typename T>
 inline T __shfl_up(T v, unsigned delta, int width = 32) {
     const int l = simt_self.lane, s = l - (int)delta;

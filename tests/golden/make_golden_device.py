@@ -133,6 +133,7 @@ def main():
 
     neighbours(lib, out, f)
     attn_prep(lib, out, f)
+    phase3(lib, out)
     np.savez_compressed(os.path.join(OUT, "device_ops.npz"), **out)
     print("wrote device_ops.npz:", len(out), "arrays,", os.path.getsize(os.path.join(OUT, "device_ops.npz")) // 1024, "KB")
 
@@ -275,6 +276,38 @@ def attn_prep(lib, out, f):
         out.update({f"prep_{tag}_q": q, f"prep_{tag}_k": k, f"prep_{tag}_v": v, f"prep_{tag}_qn": qn, f"prep_{tag}_kn": kn,
                     f"prep_{tag}_q_out": q_out, f"prep_{tag}_K": K, f"prep_{tag}_V": V,
                     f"prep_{tag}_cfg": np.array([D, nq, nkv, T, chain, gated, kvq, pos0, kv_stride], np.int32)})
+
+
+def phase3(lib, out):
+    """The FP16 component kernels on the inputs of the reference's own test programs: "rmsnorm" (src/layernorm.hip) on
+    the sweep of tests/layernorm_verify.cpp:64-66,139 (LCG seed 7 per shape, eps 1e-5, grid = tokens, block = 32) and
+    "rope_rotate_half" (src/rope_embedding.hip) on the sweep of tests/rope_verify.cpp:69-81,152-164 (seed 13, positions
+    from the second LCG, theta 1e4, tables built in double and stored fp32)."""
+    from oracle import oracle
+    vp, ci, cf = C.c_void_p, C.c_int, C.c_float
+    for tokens, embd in ((8, 17), (32, 64), (5, 4096), (1, 96), (7, 48)):
+        rng = oracle.Lcg(7)
+        x = np.array([rng.rnd(-3.0, 3.0) for _ in range(tokens * embd)], dtype=np.float32)
+        gam = np.array([rng.rnd(0.5, 1.5) for _ in range(embd)], dtype=np.float32)
+        xh, gh = oracle.f32_to_f16(x).reshape(tokens, embd), oracle.f32_to_f16(gam)
+        y, y1 = np.zeros_like(xh), np.zeros_like(xh)
+        launch(lib, "rmsnorm", (tokens, 1), 32, [vp(xh.ctypes.data), vp(gh.ctypes.data), vp(y.ctypes.data), ci(tokens), ci(embd), cf(1e-5)])
+        launch(lib, "rmsnorm", (tokens, 1), 32, [vp(xh.ctypes.data), vp(None), vp(y1.ctypes.data), ci(tokens), ci(embd), cf(1e-5)])
+        out.update({f"p3norm_{tokens}x{embd}_x": xh, f"p3norm_{tokens}x{embd}_gamma": gh, f"p3norm_{tokens}x{embd}_y": y,
+                    f"p3norm_{tokens}x{embd}_y_nogamma": y1})
+    state, pos = 99, []
+    for _ in range(64):
+        state = (state * 1664525 + 1013904223) & 0xFFFFFFFF
+        pos.append(1 + (state >> 8) % 4096)
+    pos = np.array(pos, dtype=np.int32)
+    for rows, dim in ((16, 16), (5, 32), (64, 128)):
+        rng = oracle.Lcg(13)
+        x = oracle.f32_to_f16(np.array([rng.rnd(-3.0, 3.0) for _ in range(rows * dim)], dtype=np.float32)).reshape(rows, dim)
+        c, s = oracle.rope_tables(pos[:rows], dim, 10000.0)
+        y = np.zeros_like(x)
+        launch(lib, "rope_rotate_half", (rows, 1), 32, [vp(x.ctypes.data), vp(c.ctypes.data), vp(s.ctypes.data), vp(y.ctypes.data),
+                                                        ci(rows), ci(dim // 2)])
+        out.update({f"p3rope_{rows}x{dim}_x": x, f"p3rope_{rows}x{dim}_c": c, f"p3rope_{rows}x{dim}_s": s, f"p3rope_{rows}x{dim}_y": y})
 
 
 if __name__ == "__main__":

@@ -139,3 +139,27 @@ def test_norm_rope_into_the_fp16_cache(ops, tag):
     for got, want in ((K, G[f"prep_{tag}_K"]), (V, G[f"prep_{tag}_V"])):
         a, b = host(got).view(np.float16).astype(np.float32), want.view(np.float16).astype(np.float32)
         assert np.all(np.abs(rows(a) - rows(b)) <= np.abs(rows(b)) * 2.0 ** -10 + 1e-7)
+
+
+def test_fp16_component_kernels(ops):
+    """gpu_rmsnorm_f16 / gpu_rope_rotate_half_f16 on the inputs of the reference's test programs against what the
+    reference's own kernels gave (one fp16 step: the sums run in different orders)."""
+    def ulps(a, b):
+        k = lambda u: np.where(u.astype(np.int32) & 0x8000, -(u.astype(np.int32) & 0x7FFF), u.astype(np.int32))
+        return int(np.abs(k(a) - k(b)).max())
+    f16 = torch.float16
+    for t, e in ((8, 17), (32, 64), (5, 4096), (1, 96), (7, 48)):
+        x, gam = dev(G[f"p3norm_{t}x{e}_x"], f16), dev(G[f"p3norm_{t}x{e}_gamma"], f16)
+        y = torch.empty_like(x)
+        ops.gpu_rmsnorm_f16(x, gam, y, t, e, 1e-5)
+        torch.cuda.synchronize()
+        assert ulps(host(y), G[f"p3norm_{t}x{e}_y"]) <= 1
+        ops.gpu_rmsnorm_f16(x, None, y, t, e, 1e-5)
+        torch.cuda.synchronize()
+        assert ulps(host(y), G[f"p3norm_{t}x{e}_y_nogamma"]) <= 1
+    for r, d in ((16, 16), (5, 32), (64, 128)):
+        x = dev(G[f"p3rope_{r}x{d}_x"], f16)
+        y = torch.empty_like(x)
+        ops.gpu_rope_rotate_half_f16(x, dev(G[f"p3rope_{r}x{d}_c"]), dev(G[f"p3rope_{r}x{d}_s"]), y, r, d // 2)
+        torch.cuda.synchronize()
+        assert ulps(host(y), G[f"p3rope_{r}x{d}_y"]) <= 1

@@ -243,6 +243,28 @@ def test_attn_prep_at_the_position_the_reference_tests():
     assert untouched(G[f"prep_{tag}_K"]) and untouched(G[f"prep_{tag}_V"])
 
 
+def _f16_ulps(a, b):
+    k = lambda u: np.where(u.astype(np.int32) & 0x8000, -(u.astype(np.int32) & 0x7FFF), u.astype(np.int32))
+    return int(np.abs(k(a) - k(b)).max())
+
+
+def test_fp16_component_kernels_on_their_test_programs_inputs():
+    """The reference's "rmsnorm" and "rope_rotate_half" kernels (src/layernorm.hip, src/rope_embedding.hip) on the
+    sweeps of its own test programs: the checkers restate those programs' CPU loops (a sequential fp32 sum where the
+    kernel sums 32 strided partials), so the norm agrees to one fp16 step and the rotation to the bit; both pass the
+    programs' rule (tests/layernorm_verify.cpp:40-43)."""
+    bad = lambda g, r: np.abs(g - r) > 0.01 * np.maximum(np.abs(g), np.abs(r)) + 1e-4
+    for t, e in ((8, 17), (32, 64), (5, 4096), (1, 96), (7, 48)):
+        x, gam = G[f"p3norm_{t}x{e}_x"], G[f"p3norm_{t}x{e}_gamma"]
+        for got, want in ((oracle.rmsnorm_f16(x, gam, 1e-5), G[f"p3norm_{t}x{e}_y"]),
+                          (oracle.rmsnorm_f16(x, None, 1e-5), G[f"p3norm_{t}x{e}_y_nogamma"])):
+            assert _f16_ulps(got, want) <= 1
+            assert not bad(oracle.f16_to_f32(got), oracle.f16_to_f32(want)).any()
+    for r, d in ((16, 16), (5, 32), (64, 128)):
+        got = oracle.rope_rotate_half_f16(G[f"p3rope_{r}x{d}_x"], G[f"p3rope_{r}x{d}_c"], G[f"p3rope_{r}x{d}_s"])
+        assert np.array_equal(got, G[f"p3rope_{r}x{d}_y"])
+
+
 @pytest.mark.skipif(not os.path.exists(os.path.join(os.path.dirname(oracle.__file__), "_ref", "libref_emul.so")),
                     reason="the emulated reference kernels are built only where the reference's sources are present")
 def test_fixtures_regenerate_identically(tmp_path, monkeypatch):
