@@ -26,6 +26,16 @@ namespace b200 {
 // product is undefined, so there is nothing to match there).
 __device__ __forceinline__ int rint_small(float t) { return (int)__float_as_uint(__fadd_rn(t, 12582912.0f)) - 0x4B400000; }
 
+// Four such values as the int8 quadruple a quantiser stores: the low byte of each sum is the value's two's-complement
+// byte already (the constant's low byte is 0), so the four sums are packed without being turned into integers first;
+// their integer sum is one dot product with four ones.
+__device__ __forceinline__ uint32_t rint4_packed(float t0, float t1, float t2, float t3) {
+    const uint32_t b0 = __float_as_uint(__fadd_rn(t0, 12582912.0f)), b1 = __float_as_uint(__fadd_rn(t1, 12582912.0f));
+    const uint32_t b2 = __float_as_uint(__fadd_rn(t2, 12582912.0f)), b3 = __float_as_uint(__fadd_rn(t3, 12582912.0f));
+    return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+}
+__device__ __forceinline__ int sum_int8x4(uint32_t packed) { return __dp4a((int)packed, 0x01010101, 0); }
+
 
 struct Q8Side {
     int8_t* q0;
@@ -172,16 +182,14 @@ __device__ __forceinline__ void q8v_phase_a(const float (&y)[NV][4], const unsig
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         const float id0 = __shfl_sync(0xffffffffu, quot, (lane & 24) + j);
-        int q[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) q[e] = live[j] ? rint_small(__fmul_rn(y[j][e], id0)) : 0;
-        int sum0 = (q[0] + q[1]) + (q[2] + q[3]);
+        const uint32_t q4 = live[j] ? rint4_packed(__fmul_rn(y[j][0], id0), __fmul_rn(y[j][1], id0), __fmul_rn(y[j][2], id0),
+                                                   __fmul_rn(y[j][3], id0))
+                                    : 0u;
+        int sum0 = sum_int8x4(q4);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 4);
-        if (live[j])
-            *reinterpret_cast<uint32_t*>(o.q0 + i[j]) =
-                __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+        if (live[j]) *reinterpret_cast<uint32_t*>(o.q0 + i[j]) = q4;
         if (r == NV + j) { my_sum = sum0; my_i = i[j]; my_live = live[j]; }
     }
     if (my_live) {   // (only lanes NV .. 2 NV - 1 of a group: this lane holds amax / 127 of its block in quot)
@@ -206,16 +214,16 @@ __device__ __forceinline__ void q8v_phase_b(const float (&y)[NV][4], const unsig
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         const float iscale = __shfl_sync(0xffffffffu, isc, j);
-        int q[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e)   // min(127, rint(t)) = rint(min(t, 127))
-            q[e] = (live[j] && blk[j].am != 0u) ? rint_small(fminf(__fmul_rn(iscale, y[j][e]), 127.0f)) : 0;
-        int s16 = (q[0] + q[1]) + (q[2] + q[3]);
+        // min(127, rint(t)) = rint(min(t, 127))
+        const uint32_t q4 = (live[j] && blk[j].am != 0u)
+                                ? rint4_packed(fminf(__fmul_rn(iscale, y[j][0]), 127.0f), fminf(__fmul_rn(iscale, y[j][1]), 127.0f),
+                                               fminf(__fmul_rn(iscale, y[j][2]), 127.0f), fminf(__fmul_rn(iscale, y[j][3]), 127.0f))
+                                : 0u;
+        int s16 = sum_int8x4(q4);
         s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
         s16 += __shfl_xor_sync(0xffffffffu, s16, 2);
         if (live[j]) {
-            *reinterpret_cast<uint32_t*>(o.qK + i[j]) =
-                __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+            *reinterpret_cast<uint32_t*>(o.qK + i[j]) = q4;
             if ((lane & 3) == 0) o.bsK[i[j] >> 4] = s16;
             if (lane == j && first_half[j]) o.dK[i[j] >> 8] = dk;
         }
