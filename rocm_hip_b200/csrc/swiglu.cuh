@@ -8,8 +8,11 @@
 //
 // fp32 rows use the accurate expf and an IEEE division (within ~2 ulp of the CPU reference). 16-bit rows use
 // ex2.approx and rcp.approx: their ~1e-6 relative error is far inside half a bf16 ulp (2e-3), so the rounded result
-// differs from the rounded reference only when the exact value sits on a rounding boundary, by one ulp. The
-// non-flushing rcp keeps the tiny results of very negative gates instead of cutting them to zero.
+// differs from the rounded reference only when the exact value sits on a rounding boundary, by one ulp. The tiny
+// results of very negative gates (below -87, where 1 + e exceeds 2^126 and its reciprocal is subnormal) are kept, not
+// cut to zero, without the non-flushing reciprocal's range handling (six more instructions per value): the
+// reciprocal is taken of (1 + e) / 16, which stays normal for every finite e, and the gate carries the 1 / 16
+// (powers of two: the same mantissas, so the same bits wherever nothing is subnormal).
 
 #ifndef B200_SWIGLU_CUH
 #define B200_SWIGLU_CUH
@@ -24,16 +27,16 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     if constexpr (FAST) {
         float e, r;
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(g, -1.4426950408889634f)));
-        asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(__fadd_rn(1.0f, e)));
-        return __fmul_rn(__fmul_rn(g, r), u);
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__fmaf_rn(e, 0.0625f, 0.0625f)));   // 16 / (1 + e)
+        return __fmul_rn(__fmul_rn(__fmul_rn(g, 0.0625f), r), u);
     } else {
         return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
     }
 }
 
 // SiLU(g) * u on packed pairs. FAST (16-bit rows): ex2.approx / rcp.approx, the scalings and products two-wide.
-// ex2 flushes subnormal results to zero (they only occur for gates above 87, where 1 + e is 1 either way); rcp does
-// not, so that a gate below -87 still yields its tiny product instead of zero.
+// ex2 flushes subnormal results to zero (they only occur for gates above 87, where 1 + e is 1 either way); the
+// reciprocal's argument is scaled so that a gate below -87 still yields its tiny product instead of zero.
 template <bool FAST>
 __device__ __forceinline__ f2 silu_mul2(f2 g, f2 u) {
     float g0, g1;
@@ -43,10 +46,9 @@ __device__ __forceinline__ f2 silu_mul2(f2 g, f2 u) {
         upk2(mul2(g, pk2(-1.4426950408889634f, -1.4426950408889634f)), t0, t1);
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(t0));
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(t1));
-        upk2(add2(pk2(e0, e1), pk2(1.0f, 1.0f)), t0, t1);
-        asm("rcp.approx.f32 %0, %1;" : "=f"(r0) : "f"(t0));
-        asm("rcp.approx.f32 %0, %1;" : "=f"(r1) : "f"(t1));
-        return mul2(mul2(g, pk2(r0, r1)), u);
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(__fmaf_rn(e0, 0.0625f, 0.0625f)));   // 16 / (1 + e)
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(__fmaf_rn(e1, 0.0625f, 0.0625f)));
+        return mul2(mul2(mul2(g, pk2(0.0625f, 0.0625f)), pk2(r0, r1)), u);
     } else {
         float u0, u1;
         upk2(u, u0, u1);
