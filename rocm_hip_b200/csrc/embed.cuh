@@ -168,9 +168,20 @@ k_embed_rows_sliced(const uint8_t* table, size_t row_bytes, int vocab, const int
     uint8_t* sm = stage[wid];
     const int nb = E / 32, S = (nb + SB - 1) / SB;
     const long long warp0 = (long long)blockIdx.x * EMBED_WARPS + wid, nwarps = (long long)gridDim.x * EMBED_WARPS;
-    for (long long i = warp0; i < T * S; i += nwarps) {
-        const long long t = i / S;
-        const int b0 = (int)(i - t * S) * SB, cb = min(SB, nb - b0);
+    const long long total = T * S;
+    const bool small = total <= 0xffffffffLL;   // (uniform) the slice index fits 32 bits: a 32-bit division finds its row
+    for (long long i = warp0; i < total; i += nwarps) {
+        long long t;
+        int si;
+        if (small) {
+            const unsigned iu = (unsigned)i, tu = iu / (unsigned)S;
+            t = tu;
+            si = (int)(iu - tu * (unsigned)S);
+        } else {
+            t = i / S;
+            si = (int)(i - t * S);
+        }
+        const int b0 = si * SB, cb = min(SB, nb - b0);
         const int tok = tokens[t];
         OUT* o = out + (size_t)t * E + (size_t)b0 * 32;
         if (tok < 0 || tok >= vocab) {
