@@ -107,3 +107,23 @@ def test_hip_shim_headers_compile_alone(tmp_path):
         r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", f"-I{ROOT}/include", "-I/usr/local/cuda/include"] + defs + [str(src)],
                            capture_output=True, text=True)
         assert r.returncode == 0, r.stderr
+
+
+def test_sources_name_none_of_the_closed_calls():
+    """No tracked source names a batched-memcpy runtime call or a TMA / bulk load with cluster multicast (calls that have
+    hung or faulted B200s), and every ncu command line in the tracked notes leaves the clocks alone."""
+    import subprocess
+    files = subprocess.run(["git", "ls-files"], cwd=ROOT, capture_output=True, text=True).stdout.split()
+    closed = ["Memcpy" + "BatchAsync", "Memcpy3D" + "BatchAsync", ".multicast" + "::cluster"]
+    for f in files:
+        if f.endswith((".npz", ".json", ".so")) or not os.path.isfile(os.path.join(ROOT, f)):
+            continue
+        text = open(os.path.join(ROOT, f), errors="ignore").read()
+        if not f.endswith(".md"):
+            for word in closed:
+                assert word not in text, (f, word)
+        if f.startswith("profiles/"):
+            for line in text.splitlines():
+                s = line.strip()
+                if s.startswith("ncu --") and not s.startswith("ncu --list"):
+                    assert "--clock-control none" in s, (f, s)
